@@ -1,0 +1,27 @@
+// Entry points of the fused attention (Backend.flashAttention / flashAttentionBackward,
+// packages/core/src/interfaces.ts:127-135): pick the kernel family for the storage type.
+#include "common.cuh"
+
+namespace alpha {
+int attn_f32_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf lse, const alpha_attn_params_t *p);
+int attn_f32_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_o, alpha_buf lse, alpha_buf dq,
+                 alpha_buf dk, alpha_buf dv, const alpha_attn_params_t *p);
+}  // namespace alpha
+
+using namespace alpha;
+
+extern "C" {
+
+int alpha_flash_attn_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf lse,
+                         const alpha_attn_params_t *p) {
+  ALPHA_REQUIRE_INIT();
+  return attn_f32_fwd(q, k, v, o, lse, p);
+}
+
+int alpha_flash_attn_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_o, alpha_buf lse, alpha_buf dq,
+                         alpha_buf dk, alpha_buf dv, const alpha_attn_params_t *p) {
+  ALPHA_REQUIRE_INIT();
+  return attn_f32_bwd(q, k, v, o, d_o, lse, dq, dk, dv, p);
+}
+
+}  // extern "C"

@@ -1,0 +1,194 @@
+// Softmax cross-entropy: forward, backward, and the fused forward+backward used by the
+// train step.  HBM-bound on the [N, V] logits.
+//
+// Reference semantics: packages/tensor/src/cpu_ref.ts:543-563 (loss = mean_i(lse_i -
+// logit_i[target_i])) and packages/autograd/src/ops.ts:702-729 (grad = (softmax - onehot) *
+// g / N).  The reference's GPU path reads the summed loss back to divide by N and reads the
+// upstream scalar on the host (packages/helios/src/backend.ts:2704,4511-4515); here both
+// stay on the device.
+//
+// One block per row.  The row is staged once in shared memory with 16-byte loads (V*e
+// bytes: 100 KB for V=50257 in bf16), so the fused kernel reads each logit from HBM once
+// and writes each gradient once: algorithmic bytes per row = V*e read + V*e written.
+// Row losses go to a scratch vector and are averaged by one block in index order.
+#include "common.cuh"
+
+namespace alpha {
+
+constexpr int CE_THREADS = 512;
+
+// mode bit 0: write the row loss; bit 1: write dlogits.
+template <typename T, bool STAGE>
+__global__ void __launch_bounds__(CE_THREADS) ce_rows_kernel(const T *__restrict__ logits,
+                                                             const int32_t *__restrict__ targets, T *dlogits,
+                                                             float *__restrict__ row_loss,
+                                                             const float *__restrict__ grad_out_dev, float grad_scale,
+                                                             int64_t N, int V, int64_t ld, int mode) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float red[32];
+  T *row_s = reinterpret_cast<T *>(smem_raw);
+  constexpr int VEC = Vec16<T>::N;
+  const float gs = (grad_out_dev ? grad_out_dev[0] : 1.f) * grad_scale / (float)N;
+  for (int64_t r = blockIdx.x; r < N; r += gridDim.x) {
+    const T *row = logits + r * ld;
+    const int nvec = V / VEC;
+    float mx = -INFINITY;
+    if (STAGE) {
+      for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+        Vec16<T> v;
+        v.load(row + i * VEC);
+        v.store(row_s + i * VEC);
+        float f[VEC];
+        v.get(f);
+#pragma unroll
+        for (int j = 0; j < VEC; j++) mx = fmaxf(mx, f[j]);
+      }
+      for (int c = nvec * VEC + threadIdx.x; c < V; c += CE_THREADS) {
+        const T t = row[c];
+        row_s[c] = t;
+        mx = fmaxf(mx, to_f32(t));
+      }
+    } else {
+      for (int c = threadIdx.x; c < V; c += CE_THREADS) mx = fmaxf(mx, to_f32(row[c]));
+    }
+    mx = block_max(mx, red);  // also orders the shared-memory row before it is re-read
+    const T *src = STAGE ? row_s : row;
+    float s = 0.f;
+    if (STAGE) {
+      for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+        Vec16<T> v;
+        v.load(src + i * VEC);
+        float f[VEC];
+        v.get(f);
+#pragma unroll
+        for (int j = 0; j < VEC; j++) s += __expf(f[j] - mx);
+      }
+      for (int c = nvec * VEC + threadIdx.x; c < V; c += CE_THREADS) s += __expf(to_f32(src[c]) - mx);
+    } else {
+      for (int c = threadIdx.x; c < V; c += CE_THREADS) s += expf(to_f32(src[c]) - mx);
+    }
+    s = block_sum(s, red);
+    const int tgt = targets[r];
+    if ((mode & 1) && threadIdx.x == 0) {
+      const float lt = (tgt >= 0 && tgt < V) ? to_f32(src[tgt]) : 0.f;
+      row_loss[r] = (mx + logf(s)) - lt;
+    }
+    if (mode & 2) {
+      const float inv = 1.f / s;
+      T *drow = dlogits + r * ld;
+      if (STAGE) {
+        for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+          Vec16<T> v;
+          v.load(src + i * VEC);
+          float f[VEC];
+          v.get(f);
+#pragma unroll
+          for (int j = 0; j < VEC; j++) {
+            const float p = __expf(f[j] - mx) * inv;
+            f[j] = (p - ((i * VEC + j) == tgt ? 1.f : 0.f)) * gs;
+          }
+          v.set(f);
+          v.store(drow + i * VEC);
+        }
+        for (int c = nvec * VEC + threadIdx.x; c < V; c += CE_THREADS) {
+          const float p = __expf(to_f32(src[c]) - mx) * inv;
+          drow[c] = from_f32<T>((p - (c == tgt ? 1.f : 0.f)) * gs);
+        }
+      } else {
+        for (int c = threadIdx.x; c < V; c += CE_THREADS) {
+          const float p = expf(to_f32(src[c]) - mx) * inv;
+          drow[c] = from_f32<T>((p - (c == tgt ? 1.f : 0.f)) * gs);
+        }
+      }
+    }
+    __syncthreads();  // the staged row is overwritten by the next iteration
+  }
+}
+
+__global__ void __launch_bounds__(1024) ce_mean_kernel(const float *__restrict__ row_loss, int64_t N,
+                                                       float *__restrict__ out) {
+  __shared__ float red[32];
+  float s = 0.f;
+  for (int64_t i = threadIdx.x; i < N; i += blockDim.x) s += row_loss[i];
+  s = block_sum(s, red);
+  if (threadIdx.x == 0) out[0] = s / (float)N;
+}
+
+template <typename T>
+static int ce_launch(alpha_buf logits, alpha_buf targets, alpha_buf dlogits, alpha_buf loss_mean, alpha_buf grad_out,
+                     float grad_scale, int64_t N, int64_t V, int64_t ld, int mode) {
+  if (N == 0 || V == 0) {
+    if ((mode & 1) && loss_mean) ALPHA_CUDA(cudaMemsetAsync(ptr<void>(loss_mean), 0, 4, g_stream));
+    return 0;
+  }
+  ALPHA_CHECK(V < (1ll << 31), "cross entropy: V too large");
+  ProfScope prof(PROF_CE, (double)N * V * sizeof(T) * ((mode & 2) ? 2.0 : 1.0));
+  void *row_loss = nullptr;
+  if (mode & 1)
+    if (pool_alloc((size_t)N * sizeof(float), &row_loss)) return 1;
+  constexpr int VEC = Vec16<T>::N;
+  const size_t row_bytes = ((size_t)V * sizeof(T) + 15) & ~size_t(15);
+  // The fp32 path (parity mode) keeps full-precision expf; the staged path uses the fast
+  // exponential (2 ulp), which is far inside bf16 resolution.
+  const bool stage = sizeof(T) == 2 && row_bytes <= 200 * 1024 && ld % VEC == 0 && (logits & 15) == 0 &&
+                     (!(mode & 2) || (dlogits & 15) == 0);
+  const int grid = grid_for(N, 1, stage ? 2 : 4);
+  if (stage) {
+    static bool attr_set = false;
+    if (!attr_set) {
+      ALPHA_CUDA(cudaFuncSetAttribute(ce_rows_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      attr_set = true;
+    }
+    ce_rows_kernel<T, true><<<grid, CE_THREADS, row_bytes, g_stream>>>(
+        ptr<T>(logits), ptr<int32_t>(targets), ptr<T>(dlogits), (float *)row_loss,
+        grad_out ? ptr<float>(grad_out) : nullptr, grad_scale, N, (int)V, ld, mode);
+  } else {
+    ce_rows_kernel<T, false><<<grid, CE_THREADS, 0, g_stream>>>(
+        ptr<T>(logits), ptr<int32_t>(targets), ptr<T>(dlogits), (float *)row_loss,
+        grad_out ? ptr<float>(grad_out) : nullptr, grad_scale, N, (int)V, ld, mode);
+  }
+  if (mode & 1) {
+    g_launches++;
+    ce_mean_kernel<<<1, 1024, 0, g_stream>>>((const float *)row_loss, N, ptr<float>(loss_mean));
+    pool_free(row_loss);
+  }
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+}  // namespace alpha
+
+using namespace alpha;
+
+extern "C" {
+
+int alpha_cross_entropy_fwd(alpha_buf logits, alpha_buf targets, alpha_buf loss_mean, int64_t N, int64_t V, int64_t ld,
+                            int dtype) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(ld >= V, "alpha_cross_entropy_fwd: ld < V");
+  if (dtype == ALPHA_F32) return ce_launch<float>(logits, targets, 0, loss_mean, 0, 1.f, N, V, ld, 1);
+  if (dtype == ALPHA_BF16) return ce_launch<__nv_bfloat16>(logits, targets, 0, loss_mean, 0, 1.f, N, V, ld, 1);
+  return set_error("alpha_cross_entropy_fwd: unsupported dtype %d", dtype);
+}
+
+int alpha_cross_entropy_bwd(alpha_buf logits, alpha_buf targets, alpha_buf grad_out_scalar, alpha_buf dlogits,
+                            int64_t N, int64_t V, int64_t ld, int dtype) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(ld >= V, "alpha_cross_entropy_bwd: ld < V");
+  if (dtype == ALPHA_F32) return ce_launch<float>(logits, targets, dlogits, 0, grad_out_scalar, 1.f, N, V, ld, 2);
+  if (dtype == ALPHA_BF16)
+    return ce_launch<__nv_bfloat16>(logits, targets, dlogits, 0, grad_out_scalar, 1.f, N, V, ld, 2);
+  return set_error("alpha_cross_entropy_bwd: unsupported dtype %d", dtype);
+}
+
+int alpha_softmax_ce_fwd_bwd(alpha_buf logits, alpha_buf targets, alpha_buf dlogits, alpha_buf loss_mean, int64_t N,
+                             int64_t V, int64_t ld, float grad_scale, int dtype) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(ld >= V, "alpha_softmax_ce_fwd_bwd: ld < V");
+  if (dtype == ALPHA_F32) return ce_launch<float>(logits, targets, dlogits, loss_mean, 0, grad_scale, N, V, ld, 3);
+  if (dtype == ALPHA_BF16)
+    return ce_launch<__nv_bfloat16>(logits, targets, dlogits, loss_mean, 0, grad_scale, N, V, ld, 3);
+  return set_error("alpha_softmax_ce_fwd_bwd: unsupported dtype %d", dtype);
+}
+
+}  // extern "C"

@@ -1,0 +1,418 @@
+// LayerNorm / RMSNorm forward and backward.  HBM-bound: each row is read once with 16-byte
+// loads into registers (one warp per row), statistics by warp shuffles in two passes over
+// the registers, outputs stored with 16-byte stores.
+//
+// Reference semantics: packages/tensor/src/cpu_ref.ts:387-420 (forward: biased variance,
+// y = (x-mean)*rsqrt(var+eps)*w + b) and packages/autograd/src/ops.ts:523-569 (backward:
+// dx = rstd*(dy - (sum(dy) + xhat*sum(dy*xhat))/dim) with dy = g*w; dw = sum_rows g*xhat;
+// db = sum_rows g).  Weights, biases and their gradients are always f32.
+//
+// Backward reduces dw/db in two deterministic stages: every block keeps per-lane column
+// sums over the rows it walks, writes one partial row to scratch, and a second kernel adds
+// the partial rows in block order.  Algorithmic bytes per row: forward 2*dim*e, backward
+// 3*dim*e (e = element size) — the scratch adds 2*grid*dim*4 bytes per call.
+#include "common.cuh"
+
+namespace alpha {
+
+constexpr int LN_WARPS = 4;
+
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_warp(const T *__restrict__ x, const float *__restrict__ w,
+                                                             const float *__restrict__ b, T *__restrict__ y,
+                                                             int64_t rows, int dim, float eps) {
+  constexpr int V = Vec16<T>::N;
+  const int lane = threadIdx.x & 31;
+  const int nvec = dim / V;
+  const int64_t warp_global = (int64_t)blockIdx.x * LN_WARPS + (threadIdx.x >> 5);
+  const int64_t warp_stride = (int64_t)gridDim.x * LN_WARPS;
+  for (int64_t r = warp_global; r < rows; r += warp_stride) {
+    float xv[NV][V];
+    const T *xr = x + r * dim;
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * 32 + lane;
+      if (iv < nvec) {
+        Vec16<T> t;
+        t.load(xr + iv * V);
+        t.get(xv[v]);
+#pragma unroll
+        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+      }
+    }
+    s = warp_sum(s);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+        if (v * 32 + lane < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            const float d = xv[v][j] - mean;
+            q += d * d;
+          }
+        }
+      q = warp_sum(q);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    T *yr = y + r * dim;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * 32 + lane;
+      if (iv < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          const int c = iv * V + j;
+          o[j] = (xv[v][j] - mean) * rstd * w[c] + (RMS ? 0.f : b[c]);
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(yr + iv * V);
+      }
+    }
+  }
+}
+
+// Backward, one warp per row, persistent over rows.  part: [gridDim.x, 2, dim] f32.
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_warp(const T *__restrict__ x, const float *__restrict__ w,
+                                                             const T *__restrict__ g, T *__restrict__ dx,
+                                                             float *__restrict__ part, int64_t rows, int dim,
+                                                             float eps) {
+  constexpr int V = Vec16<T>::N;
+  extern __shared__ float sm[];  // [LN_WARPS][2][dim]
+  const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  const int nvec = dim / V;
+  float dw_acc[NV][V], db_acc[NV][V], wv[NV][V];
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int iv = v * 32 + lane;
+#pragma unroll
+    for (int j = 0; j < V; j++) {
+      dw_acc[v][j] = 0.f;
+      db_acc[v][j] = 0.f;
+      wv[v][j] = iv < nvec ? w[iv * V + j] : 0.f;
+    }
+  }
+  const int64_t warp_global = (int64_t)blockIdx.x * LN_WARPS + wid;
+  const int64_t warp_stride = (int64_t)gridDim.x * LN_WARPS;
+  for (int64_t r = warp_global; r < rows; r += warp_stride) {
+    float xv[NV][V], gv[NV][V];
+    const T *xr = x + r * dim, *gr = g + r * dim;
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * 32 + lane;
+      if (iv < nvec) {
+        Vec16<T> t, u;
+        t.load(xr + iv * V);
+        u.load(gr + iv * V);
+        t.get(xv[v]);
+        u.get(gv[v]);
+#pragma unroll
+        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+      }
+    }
+    s = warp_sum(s);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+        if (v * 32 + lane < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            const float d = xv[v][j] - mean;
+            q += d * d;
+          }
+        }
+      q = warp_sum(q);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    float sum1 = 0.f, sum2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++)
+      if (v * 32 + lane < nvec) {
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          const float xhat = (xv[v][j] - mean) * rstd;
+          const float dy = gv[v][j] * wv[v][j];
+          dw_acc[v][j] += gv[v][j] * xhat;
+          db_acc[v][j] += gv[v][j];
+          sum1 += dy;
+          sum2 += dy * xhat;
+          xv[v][j] = xhat;  // keep xhat
+          gv[v][j] = dy;    // keep dy
+        }
+      }
+    sum1 = warp_sum(sum1);
+    sum2 = warp_sum(sum2);
+    if (RMS) sum1 = 0.f;  // no mean subtraction in RMSNorm
+    T *dr = dx + r * dim;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * 32 + lane;
+      if (iv < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) o[j] = rstd * (gv[v][j] - (sum1 + xv[v][j] * sum2) / dim);
+        Vec16<T> t;
+        t.set(o);
+        t.store(dr + iv * V);
+      }
+    }
+  }
+  // block-level reduce of the per-warp column sums, fixed warp order
+  float *my = sm + (size_t)wid * 2 * dim;
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int iv = v * 32 + lane;
+    if (iv < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; j++) {
+        my[iv * V + j] = dw_acc[v][j];
+        my[dim + iv * V + j] = db_acc[v][j];
+      }
+    }
+  }
+  __syncthreads();
+  float *out = part + (size_t)blockIdx.x * 2 * dim;
+  for (int c = threadIdx.x; c < 2 * dim; c += blockDim.x) {
+    float a = 0.f;
+#pragma unroll
+    for (int k = 0; k < LN_WARPS; k++) a += sm[(size_t)k * 2 * dim + c];
+    out[c] = a;
+  }
+}
+
+// dw[c] (+)= sum_p part[p][0][c]; db[c] (+)= sum_p part[p][1][c]
+__global__ void __launch_bounds__(256) ln_reduce_partials(const float *__restrict__ part, float *dw, float *db,
+                                                          int n_part, int dim, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= 2 * dim) return;
+  float a = 0.f;
+  for (int p = 0; p < n_part; p++) a += part[(size_t)p * 2 * dim + c];
+  float *dst = c < dim ? dw + c : (db ? db + (c - dim) : nullptr);
+  if (dst) *dst = accumulate ? *dst + a : a;
+}
+
+// ── generic fallback (any dim / alignment): one block per row, scalar accesses ──────────
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256) ln_fwd_block(const T *x, const float *w, const float *b, T *y, int64_t rows,
+                                                    int dim, float eps) {
+  __shared__ float red[32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T *xr = x + r * dim;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = to_f32(xr[c]);
+      s += RMS ? v * v : v;
+    }
+    s = block_sum(s, red);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+      for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        const float d = to_f32(xr[c]) - mean;
+        q += d * d;
+      }
+      q = block_sum(q, red);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    for (int c = threadIdx.x; c < dim; c += blockDim.x)
+      y[r * dim + c] = from_f32<T>((to_f32(xr[c]) - mean) * rstd * w[c] + (RMS ? 0.f : b[c]));
+  }
+}
+
+// dx per row; also stores (mean, rstd) per row for the column kernel.
+template <typename T, bool RMS>
+__global__ void __launch_bounds__(256) ln_bwd_block(const T *x, const float *w, const T *g, T *dx, float *stats,
+                                                    int64_t rows, int dim, float eps) {
+  __shared__ float red[32];
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+    const T *xr = x + r * dim, *gr = g + r * dim;
+    float s = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float v = to_f32(xr[c]);
+      s += RMS ? v * v : v;
+    }
+    s = block_sum(s, red);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+      for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+        const float d = to_f32(xr[c]) - mean;
+        q += d * d;
+      }
+      q = block_sum(q, red);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    float s1 = 0.f, s2 = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float dy = to_f32(gr[c]) * w[c];
+      s1 += dy;
+      s2 += dy * (to_f32(xr[c]) - mean) * rstd;
+    }
+    s1 = block_sum(s1, red);
+    s2 = block_sum(s2, red);
+    if (RMS) s1 = 0.f;
+    for (int c = threadIdx.x; c < dim; c += blockDim.x) {
+      const float xhat = (to_f32(xr[c]) - mean) * rstd;
+      const float dy = to_f32(gr[c]) * w[c];
+      dx[r * dim + c] = from_f32<T>(rstd * (dy - (s1 + xhat * s2) / dim));
+    }
+    if (threadIdx.x == 0) {
+      stats[2 * r] = mean;
+      stats[2 * r + 1] = rstd;
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128) ln_dwdb_cols(const T *x, const T *g, const float *stats, float *dw, float *db,
+                                                    int64_t rows, int dim, int accumulate) {
+  const int c = blockIdx.x * blockDim.x + threadIdx.x;
+  if (c >= dim) return;
+  float a = 0.f, bsum = 0.f;
+  for (int64_t r = 0; r < rows; r++) {
+    const float gv = to_f32(g[r * dim + c]);
+    a += gv * (to_f32(x[r * dim + c]) - stats[2 * r]) * stats[2 * r + 1];
+    bsum += gv;
+  }
+  dw[c] = accumulate ? dw[c] + a : a;
+  if (db) db[c] = accumulate ? db[c] + bsum : bsum;
+}
+
+template <typename T, bool RMS>
+static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows, int64_t dim, float eps) {
+  if (rows == 0 || dim == 0) return 0;
+  ProfScope prof(PROF_NORM, 2.0 * rows * dim * sizeof(T));
+  constexpr int V = Vec16<T>::N;
+  const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
+  if (fast) {
+    const int nv = (int)((dim / V + 31) / 32);
+    const int grid = grid_for(rows, LN_WARPS, 16);
+#define LN_FWD_CASE(NV)                                                                                     \
+  case NV:                                                                                                  \
+    ln_fwd_warp<T, NV, RMS><<<grid, LN_WARPS * 32, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b),  \
+                                                                  ptr<T>(y), rows, (int)dim, eps);           \
+    break;
+    switch (nv) {
+      LN_FWD_CASE(1) LN_FWD_CASE(2) LN_FWD_CASE(3) LN_FWD_CASE(4) LN_FWD_CASE(5) LN_FWD_CASE(6) LN_FWD_CASE(7)
+      LN_FWD_CASE(8)
+    }
+#undef LN_FWD_CASE
+  } else {
+    ln_fwd_block<T, RMS><<<grid_for(rows, 1, 8), 256, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b),
+                                                                     ptr<T>(y), rows, (int)dim, eps);
+  }
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+template <typename T, bool RMS>
+static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, alpha_buf db, int64_t rows,
+                    int64_t dim, float eps, int accumulate) {
+  if (dim == 0) return 0;
+  if (rows == 0) {
+    if (!accumulate) {
+      ALPHA_CUDA(cudaMemsetAsync(ptr<void>(dw), 0, dim * 4, g_stream));
+      if (db) ALPHA_CUDA(cudaMemsetAsync(ptr<void>(db), 0, dim * 4, g_stream));
+    }
+    return 0;
+  }
+  ProfScope prof(PROF_NORM, 3.0 * rows * dim * sizeof(T));
+  constexpr int V = Vec16<T>::N;
+  const size_t smem = (size_t)LN_WARPS * 2 * dim * sizeof(float);
+  const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && dim / V <= 32 * 8 &&
+                    smem <= 48 * 1024;
+  if (fast) {
+    const int nv = (int)((dim / V + 31) / 32);
+    int grid = grid_for(rows, LN_WARPS, 4);
+    void *part = nullptr;
+    if (pool_alloc((size_t)grid * 2 * dim * sizeof(float), &part)) return 1;
+#define LN_BWD_CASE(NV)                                                                                    \
+  case NV:                                                                                                 \
+    ln_bwd_warp<T, NV, RMS><<<grid, LN_WARPS * 32, smem, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),   \
+                                                                     ptr<T>(dx), (float *)part, rows,       \
+                                                                     (int)dim, eps);                        \
+    break;
+    switch (nv) {
+      LN_BWD_CASE(1) LN_BWD_CASE(2) LN_BWD_CASE(3) LN_BWD_CASE(4) LN_BWD_CASE(5) LN_BWD_CASE(6) LN_BWD_CASE(7)
+      LN_BWD_CASE(8)
+    }
+#undef LN_BWD_CASE
+    g_launches++;
+    ln_reduce_partials<<<(unsigned)((2 * dim + 255) / 256), 256, 0, g_stream>>>(
+        (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
+    pool_free(part);
+  } else {
+    void *stats = nullptr;
+    if (pool_alloc((size_t)rows * 2 * sizeof(float), &stats)) return 1;
+    ln_bwd_block<T, RMS><<<grid_for(rows, 1, 8), 256, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g), ptr<T>(dx),
+                                                                     (float *)stats, rows, (int)dim, eps);
+    g_launches++;
+    ln_dwdb_cols<T><<<(unsigned)((dim + 127) / 128), 128, 0, g_stream>>>(ptr<T>(x), ptr<T>(g), (const float *)stats,
+                                                                         ptr<float>(dw), db ? ptr<float>(db) : nullptr,
+                                                                         rows, (int)dim, accumulate);
+    pool_free(stats);
+  }
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+}  // namespace alpha
+
+using namespace alpha;
+
+extern "C" {
+
+int alpha_layernorm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows, int64_t dim, float eps,
+                        int dtype) {
+  ALPHA_REQUIRE_INIT();
+  if (dtype == ALPHA_F32) return norm_fwd<float, false>(x, w, b, y, rows, dim, eps);
+  if (dtype == ALPHA_BF16) return norm_fwd<__nv_bfloat16, false>(x, w, b, y, rows, dim, eps);
+  return set_error("alpha_layernorm_fwd: unsupported dtype %d", dtype);
+}
+
+int alpha_layernorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, alpha_buf db, int64_t rows,
+                        int64_t dim, float eps, int dtype, int accumulate) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(dw != 0 && db != 0, "alpha_layernorm_bwd: dw and db are required");
+  if (dtype == ALPHA_F32) return norm_bwd<float, false>(x, w, g, dx, dw, db, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, false>(x, w, g, dx, dw, db, rows, dim, eps, accumulate);
+  return set_error("alpha_layernorm_bwd: unsupported dtype %d", dtype);
+}
+
+int alpha_rmsnorm_fwd(alpha_buf x, alpha_buf w, alpha_buf y, int64_t rows, int64_t dim, float eps, int dtype) {
+  ALPHA_REQUIRE_INIT();
+  if (dtype == ALPHA_F32) return norm_fwd<float, true>(x, w, 0, y, rows, dim, eps);
+  if (dtype == ALPHA_BF16) return norm_fwd<__nv_bfloat16, true>(x, w, 0, y, rows, dim, eps);
+  return set_error("alpha_rmsnorm_fwd: unsupported dtype %d", dtype);
+}
+
+int alpha_rmsnorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, int64_t rows, int64_t dim,
+                      float eps, int dtype, int accumulate) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(dw != 0, "alpha_rmsnorm_bwd: dw is required");
+  if (dtype == ALPHA_F32) return norm_bwd<float, true>(x, w, g, dx, dw, 0, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, true>(x, w, g, dx, dw, 0, rows, dim, eps, accumulate);
+  return set_error("alpha_rmsnorm_bwd: unsupported dtype %d", dtype);
+}
+
+}  // extern "C"

@@ -1,0 +1,212 @@
+"""Train step — host-side mirror of the step body of ``packages/train/src/trainer.ts``.
+
+Per optimizer step (trainer.ts:1146-1784): learning-rate schedule (:1088-1096,
+:1150-1158); micro-step loop = forward, backward, tape clear (:1188-1273), the loss kept on
+the device when accumulating (:1210-1226); gradient norm from one ``totalSumOfSquares``
+(:1346-1350); clip folded into the optimizer's ``gradScale`` with the gradients left
+untouched (:1297, :1650-1656); ``optimizer.stepParamEntries`` (:1761-1762); zero-grad by
+dropping the buffers (:1776-1780).
+
+Two ways to finish a step:
+* ``fused=False`` — the reference's order of host reads: loss, then the squared norm, then
+  the clip coefficient on the host and one ``adamwStep`` per tensor.
+* ``fused=True``  — nothing is read back inside the step: the squared norm stays on the
+  device, one multi-tensor AdamW launch derives the clip coefficient from it, and the
+  loss / norm scalars are returned as device tensors that the caller may read later.
+
+Data parallel (no reference counterpart): with a ``DataParallel`` object every rank runs
+the same step on its own batch; gradients are summed across ranks as they become final
+during backward, 1/world is folded into ``gradScale`` next to 1/accum.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+
+import numpy as np
+
+from .autograd import Param, Tape
+from .backend import CudaBackend, TensorData
+from .gpt import ModelConfig, collectParamEntries, gptForward, initGPT
+from .optimizers import AdamW
+from .rng import SeededRng
+
+
+@dataclass
+class TrainConfig:
+    """packages/core/src/types.ts:66-142 (fields the step uses) with the reference defaults."""
+    iters: int = 1000
+    batchSize: int = 64
+    lr: float = 3e-4
+    lrMin: float = 0.0
+    warmupIters: int = 0
+    beta1: float = 0.9
+    beta2: float = 0.95
+    eps: float = 1e-8
+    weightDecay: float = 0.1
+    gradClip: float = 1.0
+    seed: int = 42
+    gradAccumSteps: int = 1
+
+
+def noDecayNames(cfg: ModelConfig) -> set:
+    """apps/cli/src/commands/train.ts:320-331 (``lmHead`` is decayed: the set names the
+    non-existent ``lmHead.weight``)."""
+    s = {"wte", "wpe", "lnF.weight", "lnF.bias", "lmHead.weight"}
+    for i in range(cfg.nLayer):
+        for ln in ("ln1", "ln2"):
+            s.add(f"layer.{i}.{ln}.weight")
+            s.add(f"layer.{i}.{ln}.bias")
+    return s
+
+
+def learningRate(tc: TrainConfig, step: int) -> float:
+    """trainer.ts:1088-1096,1150-1158; ``step`` is 0-based."""
+    total = tc.iters
+    warmup = tc.warmupIters if tc.warmupIters > 0 else (0 if tc.warmupIters < 0 else min(2000, total // 5))
+    lr_min = tc.lr / 10 if (tc.lrMin or 0) == 0 else tc.lrMin
+    denom = max(1, total - warmup)
+    if step < warmup:
+        base = lr_min + (tc.lr - lr_min) * (step + 1) / warmup
+    else:
+        decay = (step - warmup) / denom
+        base = lr_min + (tc.lr - lr_min) * 0.5 * (1 + math.cos(math.pi * decay))
+    return max(lr_min * 0.1, base)
+
+
+class DataParallel:
+    """One rank of a data-parallel job: NCCL communicator inside the library, gradients
+    all-reduced on its side stream as soon as backward has finalised them."""
+
+    def __init__(self, backend: CudaBackend, world: int, rank: int, unique_id: bytes):
+        import ctypes as C
+        from ._lib import check
+        self.backend, self.world, self.rank = backend, world, rank
+        buf = C.create_string_buffer(unique_id, 128)
+        check(backend.lib.alpha_comm_init_rank(world, rank, buf))
+
+    @staticmethod
+    def new_unique_id() -> bytes:
+        import ctypes as C
+        from . import _lib as L
+        from ._lib import check
+        buf = C.create_string_buffer(128)
+        check(L.load().alpha_comm_unique_id(buf))
+        return buf.raw
+
+    def allreduce(self, grad: TensorData) -> None:
+        from ._lib import check
+        check(self.backend.lib.alpha_comm_allreduce_sum(grad.ptr, grad.size, self.backend._code(grad.dtype)))
+
+    def wait(self) -> None:
+        from ._lib import check
+        check(self.backend.lib.alpha_comm_wait())
+
+
+class Trainer:
+    def __init__(self, backend: CudaBackend, modelConfig: ModelConfig, trainConfig: TrainConfig,
+                 params=None, attention: str = "fused", fused: bool = True, dp: DataParallel | None = None,
+                 release: bool = True):
+        self.B, self.mc, self.tc = backend, modelConfig, trainConfig
+        if params is None:
+            rng = SeededRng(trainConfig.seed)
+            params = initGPT(modelConfig, backend, rng)
+        self.params = params
+        self.entries = collectParamEntries(params)
+        self.opt = AdamW(backend, lr=trainConfig.lr, beta1=trainConfig.beta1, beta2=trainConfig.beta2,
+                         eps=trainConfig.eps, weightDecay=trainConfig.weightDecay,
+                         noDecayNames=noDecayNames(modelConfig))
+        self.tape = Tape()
+        self.attention, self.fused, self.dp = attention, fused, dp
+        self.step_index = 0
+        self.releaseFn = backend.releaseGpuTensor if release else None
+
+    # ── one optimizer step ────────────────────────────────────────────────────
+    def train_step(self, batches, read_back: bool = True) -> dict:
+        """batches: one (tokens, targets) pair of int32 [B, T] TensorData per micro-step.
+        Returns loss / gradNorm / lr / clipCoef — floats when ``read_back``, else the loss
+        and squared-norm device tensors under "lossTensor" / "sumSqTensor"."""
+        B, tc = self.B, self.tc
+        accum = len(batches)
+        world = self.dp.world if self.dp else 1
+        lr = learningRate(tc, self.step_index)
+        self.opt.setLr(lr)
+        B.resetStepOps()
+        loss_acc = None
+        loss_td = None
+        for mi, (tokens, targets) in enumerate(batches):
+            out = gptForward(self.mc, self.params, B, self.tape, tokens, targets, training=True,
+                             attention=self.attention, release=self.releaseFn)
+            loss = out["loss"]
+            if accum > 1:                                      # trainer.ts:1210-1226
+                scaled = B.scale(loss.data, 1 / accum)
+                if loss_acc is None:
+                    loss_acc = scaled
+                else:
+                    B.addInplace(loss_acc, scaled)
+            else:
+                loss_td = B.clone(loss.data) if self.releaseFn else loss.data
+            last = mi == accum - 1
+            self._backward(loss, allreduce=last and self.dp is not None)
+            self.tape.clear(self.releaseFn)
+        if accum > 1:
+            loss_td = loss_acc
+        if self.dp is not None:
+            self.dp.wait()
+
+        grad_scale = 1.0 / (accum * world)
+        grads = [v.grad for _, v in self.entries if v.grad is not None]
+        sumsq = B.totalSumOfSquares(grads)
+        result = {"lr": lr}
+        if self.fused:
+            self.opt.stepParamEntries(self.entries, grad_scale, fused=True,
+                                      clipSumSq=sumsq if tc.gradClip > 0 else None, maxNorm=tc.gradClip)
+            if read_back:
+                gnorm = math.sqrt(float(sumsq.item())) * abs(grad_scale)
+                result.update(loss=loss_td.item(), gradNorm=gnorm,
+                              clipCoef=(tc.gradClip / gnorm if tc.gradClip > 0 and gnorm > tc.gradClip else 1.0))
+            else:
+                result.update(lossTensor=loss_td, sumSqTensor=sumsq)
+        else:
+            loss_val = loss_td.item()                          # trainer.ts:1247
+            gnorm = math.sqrt(float(sumsq.item())) * abs(grad_scale)   # :1348-1349
+            clip, eff = 1.0, grad_scale
+            if tc.gradClip > 0 and gnorm > tc.gradClip:       # :1650-1656
+                clip = tc.gradClip / gnorm
+                eff *= clip
+            if math.isfinite(loss_val) and math.isfinite(gnorm):
+                self.opt.stepParamEntries(self.entries, eff)
+            result.update(loss=loss_val, gradNorm=gnorm, clipCoef=clip)
+        for _, v in self.entries:                              # trainer.ts:1776-1780
+            v.grad = None
+        self.step_index += 1
+        result["gpuOps"] = B.gpuOpsThisStep
+        return result
+
+    def _backward(self, loss, allreduce: bool) -> None:
+        if not allreduce:
+            self.tape.backward(loss, self.B, self.releaseFn)
+            return
+        # Count how many tape entries feed each parameter: its gradient is final once the
+        # last of them has run, and can be handed to the collective while backward goes on.
+        pending: dict[int, int] = {}
+        by_id: dict[int, Param] = {}
+        for e in self.tape.entries:
+            for v in e.inputs:
+                if isinstance(v, Param):
+                    pending[v.id] = pending.get(v.id, 0) + 1
+                    by_id[v.id] = v
+        dp = self.dp
+
+        def on_entry_done(entry):
+            for v in entry.inputs:
+                if isinstance(v, Param) and v.id in pending:
+                    pending[v.id] -= 1
+                    if pending[v.id] == 0 and v.grad is not None:
+                        dp.allreduce(v.grad)
+                        del pending[v.id]
+        self.tape.backward(loss, self.B, self.releaseFn, onEntryDone=on_entry_done)
+
+    # ── state exchange with the host (checkpointing needs exactly this) ───────
+    def host_params(self) -> dict:
+        return {n: np.array(v.data.data, dtype=np.float32) for n, v in self.entries}

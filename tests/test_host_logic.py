@@ -1,0 +1,110 @@
+"""Host layer (tape, model graph, trainer, optimizer wiring) on CPU with a numpy backend,
+checked against the oracle.  No CUDA code runs here; the CUDA path is covered by the
+``-m gpu`` tests."""
+import numpy as np
+import pytest
+
+from alpha2_b200.autograd import Tape
+from alpha2_b200.gpt import ModelConfig, gptForward, initGPT
+from alpha2_b200.rng import SeededRng
+from alpha2_b200.trainer import TrainConfig, Trainer, learningRate, noDecayNames
+from oracle import gpt as ogpt
+from oracle import train as otrain
+from oracle.cpu_ref import SeededRng as OracleRng
+from tests.fake_backend import NumpyBackend, T
+
+
+def _oracle_cfg(mc: ModelConfig):
+    return ogpt.ModelConfig(**{k: getattr(mc, k) for k in
+                               ("vocabSize", "blockSize", "nLayer", "nEmbd", "nHead", "ffnActivation", "ffnDim",
+                                "softCap", "tied", "norm", "rope", "init")})
+
+
+CASES = {
+    "gelu_ln": dict(),
+    "tied": dict(tied=True, init="plain"),
+    "swiglu_rms_rope": dict(ffnActivation="swiglu", ffnDim=48, norm="rms", rope=True, softCap=0.0),
+}
+
+
+@pytest.mark.parametrize("case", list(CASES))
+@pytest.mark.parametrize("route", ["fused", "standard", "flash"])
+def test_trainer_matches_oracle(case, route):
+    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=2, nEmbd=32, nHead=4, **CASES[case])
+    tc = TrainConfig(iters=8, batchSize=3, gradClip=0.7, seed=5)
+    oc = otrain.TrainConfig(iters=8, batchSize=3, gradClip=0.7, seed=5)
+    B = NumpyBackend()
+    tr = Trainer(B, mc, tc, attention=route, fused=(route == "fused"))
+    ref = otrain.Trainer(_oracle_cfg(mc), oc)
+    for n, v in ref.P.items():                       # identical seeded init on both sides
+        assert np.array_equal(v.data, tr.params[n].data.data), n
+    batches = otrain.uniform_batches(3, 4, 3, 16, 64)
+    for i in range(4):
+        tok, tgt = batches[i]
+        a = tr.train_step([(T(tok, "i32"), T(tgt, "i32"))])
+        b = ref.train_step([batches[i]])
+        assert abs(a["loss"] - b["loss"]) < 2e-5, (i, a, b)
+        assert abs(a["gradNorm"] - b["gradNorm"]) < 2e-5 * max(1, b["gradNorm"])
+        assert abs(a["lr"] - b["lr"]) < 1e-15
+    for n, v in ref.P.items():
+        got = tr.params[n].data.data
+        err = np.linalg.norm(got - v.data) / max(np.linalg.norm(v.data), 1e-12)
+        assert err < 2e-5, (n, err)
+
+
+def test_grad_accumulation_matches_oracle():
+    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=1, nEmbd=32, nHead=4)
+    tc = TrainConfig(iters=5, batchSize=2, seed=9)
+    tr = Trainer(NumpyBackend(), mc, tc)
+    ref = otrain.Trainer(_oracle_cfg(mc), otrain.TrainConfig(iters=5, batchSize=2, seed=9))
+    bs = otrain.uniform_batches(1, 2, 2, 16, 64)
+    a = tr.train_step([(T(t, "i32"), T(g, "i32")) for t, g in bs])
+    b = ref.train_step(bs)
+    assert abs(a["loss"] - b["loss"]) < 2e-5 and abs(a["gradNorm"] - b["gradNorm"]) < 2e-5
+
+
+def test_release_count_is_constant_across_steps():
+    """packages/tests/src/memory-leak.test.ts:149 — the number of explicit releases per step
+    must not grow from step to step."""
+    mc = ModelConfig(vocabSize=32, blockSize=8, nLayer=1, nEmbd=16, nHead=2)
+    B = NumpyBackend()
+    tr = Trainer(B, mc, TrainConfig(iters=5, batchSize=2))
+    tok, tgt = otrain.uniform_batches(0, 1, 2, 8, 32)[0]
+    counts = []
+    for _ in range(4):
+        before = B.released
+        tr.train_step([(T(tok, "i32"), T(tgt, "i32"))])
+        counts.append(B.released - before)
+    assert counts[1] == counts[2] == counts[3] and counts[1] > 0
+    assert tr.tape.size == 0
+
+
+def test_raw_reshape_route_differs_from_cpu_path():
+    """The reference's flash route reshapes [B,T,E] to [B*H,T,D] without a transpose
+    (gpt.ts:250-254), which is a different function from its CPU path."""
+    mc = ModelConfig(vocabSize=32, blockSize=8, nLayer=1, nEmbd=16, nHead=4)
+    B = NumpyBackend()
+    P = initGPT(mc, B, SeededRng(3))
+    for p in P.values():
+        if len(p.data.shape) == 2:
+            p.data._host = p.data.data * np.float32(8)
+    tok, tgt = otrain.uniform_batches(0, 1, 2, 8, 32)[0]
+    loss = {}
+    for route in ("standard", "flash", "flash_raw_reshape"):
+        out = gptForward(mc, P, B, Tape(), T(tok, "i32"), T(tgt, "i32"), attention=route)
+        loss[route] = out["loss"].data.item()
+    assert abs(loss["standard"] - loss["flash"]) < 1e-5
+    assert abs(loss["standard"] - loss["flash_raw_reshape"]) > 1e-4
+
+
+def test_schedule_and_decay_set_match_oracle():
+    tc, oc = TrainConfig(iters=50, lr=1e-3), otrain.TrainConfig(iters=50, lr=1e-3)
+    assert [learningRate(tc, s) for s in range(50)] == [otrain.lr_at(oc, s) for s in range(50)]
+    mc = ModelConfig(nLayer=3)
+    assert noDecayNames(mc) == otrain.no_decay_names(_oracle_cfg(mc))
+
+
+def test_product_rng_equals_oracle_rng():
+    a, b = SeededRng(77), OracleRng(77)
+    assert [a.next() for _ in range(10)] == [b.next() for _ in range(10)]
+    assert np.array_equal(a.fill_gauss((7, 9), 0.02), b.fill_gauss((7, 9), 0.02))
