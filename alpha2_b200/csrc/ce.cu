@@ -74,6 +74,8 @@ __global__ void __launch_bounds__(CE_THREADS) ce_rows_kernel(const T *__restrict
       row_loss[r] = (mx + logf(s)) - lt;
     }
     if (mode & 2) {
+      // dlogits may alias logits: the target logit above must be read before anyone writes
+      if (!STAGE) __syncthreads();
       const float inv = 1.f / s;
       T *drow = dlogits + r * ld;
       if (STAGE) {
