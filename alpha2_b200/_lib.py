@@ -104,6 +104,7 @@ SIGNATURES = {
     "alpha_flash_attn_bwd": [_B, _B, _B, _B, _B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_rope": [_B, _B, _L, _L, _L, _L, _L, _F, _I, _I],
     "alpha_cross_entropy_fwd": [_B, _B, _B, _L, _L, _L, _I],
+    "alpha_cross_entropy_fwd_noalloc": [_B, _B, _B, _L, _L, _L, _I],
     "alpha_cross_entropy_bwd": [_B, _B, _B, _B, _L, _L, _L, _I],
     "alpha_softmax_ce_fwd_bwd": [_B, _B, _B, _B, _L, _L, _L, _F, _I],
     "alpha_adamw": [_B, _B, _B, _B, _L, _F, _F, _F, _F, _F, _F, _F, _F, _I, _B],

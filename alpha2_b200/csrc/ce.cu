@@ -194,3 +194,76 @@ int alpha_softmax_ce_fwd_bwd(alpha_buf logits, alpha_buf targets, alpha_buf dlog
 }
 
 }  // extern "C"
+
+// ── cross-entropy forward without any allocation ─────────────────────────────
+// For hosts that fix their device-memory budget at start-up and must not reach the CUDA
+// allocator afterwards: an evaluation hook running beside a trainer that has already
+// claimed the rest of HBM (a late cudaMalloc may fail there), or a latency-bound loop that
+// forbids driver allocation calls once warm because cudaMalloc/cudaFree synchronise the
+// device.  The per-row losses, which alpha_cross_entropy_fwd keeps in pool memory, live
+// here in a fixed device array that is part of the library image: every GPU that loads the
+// library carries these 256 KiB until the process exits.
+namespace alpha {
+
+constexpr int64_t CE_NOALLOC_MAX_ROWS = 65536;
+static __device__ __align__(256) float g_ce_noalloc_row_loss[CE_NOALLOC_MAX_ROWS];
+
+// In host code the array's name is only a handle for the runtime, not an address a kernel
+// can use; the device address is looked up once per device, with that device current.
+constexpr int CE_NOALLOC_MAX_DEVICES = 64;
+static float *g_ce_noalloc_dev_ptr[CE_NOALLOC_MAX_DEVICES] = {nullptr};
+
+static int ce_noalloc_scratch(float **out) {
+  int dev = -1;
+  ALPHA_CUDA(cudaGetDevice(&dev));
+  ALPHA_CHECK(dev >= 0 && dev < CE_NOALLOC_MAX_DEVICES, "alpha_cross_entropy_fwd_noalloc: device ordinal %d out of range",
+              dev);
+  if (g_ce_noalloc_dev_ptr[dev] == nullptr) {
+    void *p = nullptr;
+    cudaError_t e = cudaGetSymbolAddress(&p, g_ce_noalloc_row_loss);
+    if (e != cudaSuccess || p == nullptr) {
+      cudaGetLastError();
+      return set_error("alpha_cross_entropy_fwd_noalloc: cudaGetSymbolAddress -> %s", cudaGetErrorString(e));
+    }
+    g_ce_noalloc_dev_ptr[dev] = static_cast<float *>(p);
+  }
+  *out = g_ce_noalloc_dev_ptr[dev];
+  return 0;
+}
+
+template <typename T>
+static int ce_noalloc_launch(alpha_buf logits, alpha_buf targets, alpha_buf loss_mean, float *row_loss, int64_t N,
+                             int64_t V, int64_t ld) {
+  // Same row kernel as alpha_cross_entropy_fwd (loss only, rows re-read from L2 instead of
+  // staged in shared memory), then the same fixed-order mean.  Rows [0, N) of the array are
+  // written before they are read and nothing beyond N is read, so stale contents left by an
+  // earlier call do not matter and nothing has to be cleared.
+  ce_rows_kernel<T, false><<<grid_for(N, 1, 4), CE_THREADS, 0, g_stream>>>(
+      ptr<T>(logits), ptr<int32_t>(targets), nullptr, row_loss, nullptr, 1.f, N, (int)V, ld, 1);
+  g_launches++;
+  ce_mean_kernel<<<1, 1024, 0, g_stream>>>(row_loss, N, ptr<float>(loss_mean));
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+}  // namespace alpha
+
+extern "C" int alpha_cross_entropy_fwd_noalloc(alpha_buf logits, alpha_buf targets, alpha_buf loss_mean, int64_t N,
+                                               int64_t V, int64_t ld, int dtype) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(ld >= V, "alpha_cross_entropy_fwd_noalloc: ld < V");
+  ALPHA_CHECK(N >= 0 && V >= 0 && V < (1ll << 31), "alpha_cross_entropy_fwd_noalloc: bad sizes");
+  ALPHA_CHECK(N <= CE_NOALLOC_MAX_ROWS,
+              "alpha_cross_entropy_fwd_noalloc: N = %lld rows exceeds the fixed scratch of %lld rows; "
+              "use alpha_cross_entropy_fwd or split the batch",
+              (long long)N, (long long)CE_NOALLOC_MAX_ROWS);
+  ALPHA_CHECK(dtype == ALPHA_F32 || dtype == ALPHA_BF16, "alpha_cross_entropy_fwd_noalloc: unsupported dtype %d", dtype);
+  if (N == 0 || V == 0) {
+    ALPHA_CUDA(cudaMemsetAsync(ptr<void>(loss_mean), 0, 4, g_stream));
+    return 0;
+  }
+  float *row_loss = nullptr;
+  if (ce_noalloc_scratch(&row_loss)) return 1;  // first call on a device: resolves the array's address
+  if (dtype == ALPHA_F32) return ce_noalloc_launch<float>(logits, targets, loss_mean, row_loss, N, V, ld);
+  return ce_noalloc_launch<__nv_bfloat16>(logits, targets, loss_mean, row_loss, N, V, ld);
+}

@@ -267,6 +267,24 @@ int alpha_cross_entropy_bwd(alpha_buf logits, alpha_buf targets, alpha_buf grad_
 int alpha_softmax_ce_fwd_bwd(alpha_buf logits, alpha_buf targets, alpha_buf dlogits,
                              alpha_buf loss_mean, int64_t N, int64_t V, int64_t ld,
                              float grad_scale, int dtype);
+/* This entry has no counterpart in the reference.  It computes what
+ * alpha_cross_entropy_fwd computes — loss_mean (f32[1]) = mean over rows of
+ * (logsumexp(row) - row[target]) — but never allocates: no cudaMalloc/cudaFree, no pool
+ * memory.  It is meant for hosts that settle their device-memory budget at start-up and may
+ * not touch the CUDA allocator later: a loss-evaluation hook next to a trainer that already
+ * owns the rest of HBM (where a late cudaMalloc can simply fail), or a latency-bound loop
+ * that bans driver allocation calls after warm-up because they synchronise the device.
+ * The per-row losses go to a fixed array inside the library image (65536 floats = 256 KiB,
+ * held by every GPU that loads the library until the process exits), so N must be
+ * <= 65536; larger N is rejected with an error, nothing is computed.  The caller still
+ * provides logits, targets and loss_mean.  The first call on a device looks up the array's
+ * device address (a one-off set-up): make that first call before starting any stream
+ * capture.  All calls share the one array and it keeps whatever the previous call left;
+ * that is harmless for consecutive calls (rows [0, N) are rewritten before they are read),
+ * but two calls whose kernels overlap on the GPU — other streams, other host threads
+ * driving their own work — race on it and must be serialised by the caller. */
+int alpha_cross_entropy_fwd_noalloc(alpha_buf logits, alpha_buf targets, alpha_buf loss_mean,
+                                    int64_t N, int64_t V, int64_t ld, int dtype);
 
 /* ── optimizer ───────────────────────────────────────────────────────────────────────
  * Backend.adamwStep (interfaces.ts:149-150; packages/train/src/optimizers.ts:84-92):

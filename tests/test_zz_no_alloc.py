@@ -1,0 +1,72 @@
+"""alpha_cross_entropy_fwd_noalloc — the cross-entropy forward for callers that cannot allocate.
+
+Some hosts hand out all of their device memory at start-up and must stay away from the
+CUDA allocator afterwards (an evaluation hook beside a trainer that owns the rest of HBM; a
+latency-bound loop that bans cudaMalloc after warm-up because it synchronises the device).
+For them the library offers one entry point whose scratch — the per-row losses — is a
+fixed 65536-float array inside the library image instead of pool memory.
+
+Checked here, through the C ABI only: on two calls in a row the new entry gives the loss
+of the existing alpha_cross_entropy_fwd on the same inputs (f32 to 1e-6 relative, bf16
+storage to 1e-5: the existing bf16 path may use the fast exponential); stale scratch from
+a larger earlier call does not leak into a smaller later one; the library's allocation
+counters do not move during the calls; and a batch beyond the fixed size is refused with
+an error that names the limit.  This file sorts last so that a failure here cannot hide
+other tests under ``-x``; it also passes when run alone in a fresh process.
+"""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def B():
+    from alpha2_b200.backend import CudaBackend
+    return CudaBackend(0)
+
+
+def _mem(B):
+    s = B.gpuMemStats()
+    return s["allocs"], s["deviceMallocs"], s["bytesInUse"]
+
+
+@pytest.mark.parametrize("dtype,tol", [("f32", 1e-6), ("bf16", 1e-5)])
+def test_noalloc_cross_entropy_matches_existing_entry(B, dtype, tol):
+    from alpha2_b200 import _lib as L
+    from alpha2_b200._lib import check
+    lib = B.lib
+    code = L.DTYPE_CODE[dtype]
+    rng = np.random.default_rng(5)
+    cases = [(700, 1000), (96, 50257), (33, 257)]          # the last one is smaller than the one before it
+    for (N, V) in cases:
+        logits = B.upload((rng.standard_normal((N, V)) * 2).astype(np.float32), dtype)
+        targets = B.upload(rng.integers(0, V, N).astype(np.int32), "i32")
+        want = B.zeros((), "f32")
+        check(lib.alpha_cross_entropy_fwd(logits.ptr, targets.ptr, want.ptr, N, V, V, code))
+        got1, got2 = B.full((), -1.0), B.full((), -2.0)   # caller-owned outputs, made before the calls
+        B.syncGpu()
+        before = _mem(B)
+        check(lib.alpha_cross_entropy_fwd_noalloc(logits.ptr, targets.ptr, got1.ptr, N, V, V, code))
+        check(lib.alpha_cross_entropy_fwd_noalloc(logits.ptr, targets.ptr, got2.ptr, N, V, V, code))
+        B.syncGpu()
+        assert _mem(B) == before                           # no pool traffic, no cudaMalloc
+        w = want.item()
+        assert np.isfinite(w) and w > 0
+        assert abs(got1.item() - w) <= tol * abs(w), (N, V, got1.item(), w)
+        assert abs(got2.item() - w) <= tol * abs(w), (N, V, got2.item(), w)
+
+
+def test_noalloc_rejects_more_rows_than_the_fixed_scratch(B):
+    from alpha2_b200._lib import AlphaCudaError, check
+    out = B.full((), 7.0)
+    with pytest.raises(AlphaCudaError, match="65536"):
+        check(B.lib.alpha_cross_entropy_fwd_noalloc(out.ptr, out.ptr, out.ptr, 65537, 4, 4, 0))
+    B.syncGpu()
+    assert out.item() == 7.0                               # nothing ran
+    # empty batch: defined result, still no allocation
+    check(B.lib.alpha_cross_entropy_fwd_noalloc(out.ptr, out.ptr, out.ptr, 0, 4, 4, 0))
+    out.invalidate_host()                                  # re-read the device value
+    assert out.item() == 0.0
