@@ -1,0 +1,202 @@
+"""Op microbenchmark over the C ABI (BASELINE configuration 2: the train-step ops alone).
+
+    python -m alpha2_b200.opbench [--op NAME ...] [--iters 10] [--json]
+
+Ops and shapes (bf16 inputs, fp32 accumulation): GEMM forward / dX / dW at
+[16384x768]x[768x{2304,3072}], [16384x3072]x[3072x768] and the lm head [16384x768]x[768x50257]
+with A, B ~ N(0, 0.02); causal flash attention forward+backward at B=8, H=12, T=1024, D=64
+with q, k, v, dO ~ N(0, 1); fused softmax-cross-entropy on logits [16384, 50257] ~ N(0, 1);
+plus LayerNorm, AdamW and the embedding scatter-add at the train-step sizes.
+
+Every launch is timed alone with CUDA events on the library's stream after 3 warm-up
+launches; a 256 MiB buffer is overwritten between launches so that each one starts with a
+cold L2.  Printed per op: mean device time, achieved TFLOP/s or GB/s from the algorithmic
+work, and the fraction of the measured peak (MEASURED_PEAKS.json: burst figures, since the
+kernel runs alone).
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes as C
+import json
+import math
+import os
+
+import numpy as np
+
+from . import _lib as L
+from ._lib import check
+from .backend import CudaBackend
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return d["bf16_tflops"], d["hbm_gbs"], "measured"
+    return 1590.0, 6650.0, "fallback"
+
+
+class Bench:
+    def __init__(self, iters: int):
+        self.B = CudaBackend(0)
+        self.lib = self.B.lib
+        self.iters = iters
+        buf = C.c_uint64()
+        check(self.lib.alpha_alloc(256 << 20, C.byref(buf)))
+        self.flush_ptr = buf.value
+        self.ev = [C.c_uint64(), C.c_uint64()]
+        for e in self.ev:
+            check(self.lib.alpha_event_create(C.byref(e)))
+        self.rng = np.random.default_rng(0)
+
+    def normal(self, shape, std, dtype="bf16"):
+        n = int(np.prod(shape))
+        # large tensors: tile a 4M-element block (the statistics are what matters here)
+        block = (self.rng.standard_normal(min(n, 1 << 22)) * std).astype(np.float32)
+        reps = -(-n // block.size)
+        arr = np.tile(block, reps)[:n].reshape(shape)
+        return self.B.upload(arr, dtype)
+
+    def time(self, fn) -> float:
+        for _ in range(3):
+            fn()
+        total = 0.0
+        for _ in range(self.iters):
+            check(self.lib.alpha_memset(self.flush_ptr, 1, 256 << 20))
+            check(self.lib.alpha_event_record(self.ev[0].value))
+            fn()
+            check(self.lib.alpha_event_record(self.ev[1].value))
+            check(self.lib.alpha_event_sync(self.ev[1].value))
+            ms = C.c_float()
+            check(self.lib.alpha_event_elapsed_ms(self.ev[0].value, self.ev[1].value, C.byref(ms)))
+            total += ms.value
+        self.B.checkAsyncError()
+        return total / self.iters
+
+
+def gemm_case(b: Bench, layout: str, M: int, N: int, K: int, out_dtype: str = "bf16", epilogue: int = L.EPI_NONE):
+    B = b.B
+    shapes = {"nt": ((M, K), (N, K)), "nn": ((M, K), (K, N)), "tn": ((K, M), (K, N))}[layout]
+    A, Bm = b.normal(shapes[0], 0.02), b.normal(shapes[1], 0.02)
+    ldc = (N + 63) // 64 * 64
+    Cc = B._new((M, ldc), out_dtype)
+    aux = B._new((M, ldc), out_dtype) if epilogue != L.EPI_NONE else None
+    code = {"nt": L.GEMM_NT, "nn": L.GEMM_NN, "tn": L.GEMM_TN}[layout]
+    lda, ldb = shapes[0][1], shapes[1][1]
+
+    def fn():
+        check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cc.ptr, M, N, K, lda, ldb, ldc, L.BF16, L.DTYPE_CODE[out_dtype],
+                               epilogue, aux.ptr if aux is not None else 0, ldc, 0))
+    ms = b.time(fn)
+    return {"ms": ms, "work": 2.0 * M * N * K, "kind": "flop"}
+
+
+def attn_case(b: Bench, Bn=8, H=12, T=1024, D=64, backward=False, dtype="bf16"):
+    B = b.B
+    E = H * D
+    qkv = b.normal((Bn * T, 3 * E), 1.0, dtype)
+    dout = b.normal((Bn * T, E), 1.0, dtype)
+    scale = 1 / math.sqrt(D)
+    out, lse = B.attentionQkv(qkv, Bn, T, H, scale, 0.0)
+    if not backward:
+        ms = b.time(lambda: B.attentionQkv(qkv, Bn, T, H, scale, 0.0))
+        return {"ms": ms, "work": 4.0 * Bn * H * T * T * D, "kind": "flop"}
+    ms = b.time(lambda: B.attentionQkvBackward(qkv, out, dout, lse, Bn, T, H, scale, 0.0))
+    return {"ms": ms, "work": 8.0 * Bn * H * T * T * D, "kind": "flop"}
+
+
+def ce_case(b: Bench, N=16384, V=50257):
+    B = b.B
+    ld = (V + 63) // 64 * 64
+    logits = b.normal((N, ld), 1.0)
+    targets = B.upload(b.rng.integers(0, V, N).astype(np.int32), "i32")
+    loss = B._new((), "f32")
+
+    def fn():
+        check(B.lib.alpha_softmax_ce_fwd_bwd(logits.ptr, targets.ptr, logits.ptr, loss.ptr, N, V, ld, 1.0, L.BF16))
+    return {"ms": b.time(fn), "work": 2.0 * N * V * 2, "kind": "byte"}
+
+
+def layernorm_case(b: Bench, rows=16384, dim=768, backward=False):
+    B = b.B
+    x, g = b.normal((rows, dim), 1.0), b.normal((rows, dim), 1.0)
+    w, bias = B.ones((dim,)), B.zeros((dim,))
+    if not backward:
+        return {"ms": b.time(lambda: B.layerNorm(x, w, bias, 1e-5)), "work": 2.0 * rows * dim * 2, "kind": "byte"}
+    return {"ms": b.time(lambda: B.layerNormBackward(x, w, g, 1e-5)), "work": 3.0 * rows * dim * 2, "kind": "byte"}
+
+
+def adamw_case(b: Bench, n=124_000_000):
+    B = b.B
+    p, m, v = B.zeros((n,)), B.zeros((n,)), B.zeros((n,))
+    g = B.zeros((n,))
+    sh = B.zeros((n,), "bf16")
+    fn = lambda: B.adamwStepMulti([(p, g, m, v, 0.1, sh)], 3e-4, 0.9, 0.95, 1e-8, 0.1, 0.05, 1.0)
+    return {"ms": b.time(fn), "work": 30.0 * n, "kind": "byte"}
+
+
+def embedding_bwd_case(b: Bench, N=16384, V=50257, E=768):
+    B = b.B
+    p = 1.0 / np.power(np.arange(1, V + 1, dtype=np.float64), 1.1)
+    cdf = np.cumsum(p / p.sum())
+    idx = B.upload(np.minimum(np.searchsorted(cdf, b.rng.random(N)), V - 1).astype(np.int32), "i32")
+    g = b.normal((N, E), 1.0)
+    return {"ms": b.time(lambda: B.embeddingBackward(idx, g, V, out=None)), "work": N * E * 2.0 + V * E * 4.0,
+            "kind": "byte"}
+
+
+M = 16384
+CASES = {
+    "gemm_fwd_qkv": lambda b: gemm_case(b, "nt", M, 2304, 768),
+    "gemm_fwd_fc1": lambda b: gemm_case(b, "nt", M, 3072, 768),
+    "gemm_fwd_fc1_gelu": lambda b: gemm_case(b, "nt", M, 3072, 768, epilogue=L.EPI_GELU),
+    "gemm_fwd_fc2": lambda b: gemm_case(b, "nt", M, 768, 3072),
+    "gemm_fwd_head": lambda b: gemm_case(b, "nt", M, 50257, 768),
+    "gemm_dx_qkv": lambda b: gemm_case(b, "nn", M, 768, 2304),
+    "gemm_dx_fc1": lambda b: gemm_case(b, "nn", M, 768, 3072),
+    "gemm_dx_fc2": lambda b: gemm_case(b, "nn", M, 3072, 768),
+    "gemm_dx_head": lambda b: gemm_case(b, "nn", M, 768, 50257),
+    "gemm_dw_qkv": lambda b: gemm_case(b, "tn", 2304, 768, M, "f32"),
+    "gemm_dw_fc1": lambda b: gemm_case(b, "tn", 3072, 768, M, "f32"),
+    "gemm_dw_fc2": lambda b: gemm_case(b, "tn", 768, 3072, M, "f32"),
+    "gemm_dw_head": lambda b: gemm_case(b, "tn", 50304, 768, M, "f32"),
+    "attn_fwd": lambda b: attn_case(b),
+    "attn_bwd": lambda b: attn_case(b, backward=True),
+    "softmax_ce": lambda b: ce_case(b),
+    "layernorm_fwd": lambda b: layernorm_case(b),
+    "layernorm_bwd": lambda b: layernorm_case(b, backward=True),
+    "adamw": lambda b: adamw_case(b),
+    "embedding_bwd": lambda b: embedding_bwd_case(b),
+}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--op", action="append", choices=sorted(CASES), help="default: all")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--json", action="store_true")
+    args = ap.parse_args()
+    tf_peak, gb_peak, src = _peaks()
+    b = Bench(args.iters)
+    rows = []
+    for name in (args.op or list(CASES)):
+        r = CASES[name](b)
+        if r["kind"] == "flop":
+            ach = r["work"] / (r["ms"] * 1e-3) / 1e12
+            rows.append({"op": name, "ms": r["ms"], "achieved": ach, "unit": "TFLOP/s", "frac": ach / tf_peak})
+        else:
+            ach = r["work"] / (r["ms"] * 1e-3) / 1e9
+            rows.append({"op": name, "ms": r["ms"], "achieved": ach, "unit": "GB/s", "frac": ach / gb_peak})
+    if args.json:
+        print(json.dumps({"peaks": src, "rows": rows}))
+    else:
+        print(f"# peaks: {src} (bf16 {tf_peak} TFLOP/s burst, HBM {gb_peak} GB/s)")
+        for r in rows:
+            print(f"{r['op']:20s} {r['ms']:9.4f} ms  {r['achieved']:9.1f} {r['unit']:8s} {100 * r['frac']:5.1f}% of peak")
+
+
+if __name__ == "__main__":
+    main()
