@@ -1,0 +1,797 @@
+// Causal flash attention for bf16 on the tcgen05 tensor cores (head dim 64).
+//
+// Contract and math: Backend.flashAttention / flashAttentionBackward
+// (packages/core/src/interfaces.ts:127-135; packages/helios/src/kernels/attention.ts:427-477,
+// 552-558 forward, :1217-1231, 1411-1427 backward) — s = scale*q.k, optional soft cap
+// cap*tanh(s/cap), keys after the query masked, online softmax, O = P V, LSE = m + ln(l);
+// backward rebuilds P from LSE, D_i = dO_i.O_i, dS = P*(dP - D_i)*(1 - tanh^2)*scale.
+// q/k/v are read in place from the fused QKV projection through (batch, head, time)
+// strides by 4-D TMA tensor maps; O is written head-merged.
+//
+// Forward, one CTA per (batch, head, 128 queries); 192 threads:
+//   warp 0     TMA producer: Q once, then K (2 stages) and V (1 stage) per 128-key block
+//   warp 1     MMA issuer:   S = Q K^T  (128x128x64, both operands K-major) into TMEM,
+//                            O += P V   (128x64x128, P K-major from shared memory,
+//                                        V as an N-major operand read in place)
+//   warps 2-5  softmax: one query row per thread (= one TMEM lane): row max, exp2, row sum,
+//              P -> bf16 -> 128B-swizzled shared memory; O is rescaled in TMEM only when the
+//              running max has moved by more than 2^8 (the stale max keeps P <= 2^8).
+// Two CTAs fit on an SM (96 KB shared memory, 256 TMEM columns each), so one CTA's softmax
+// overlaps the other's MMAs.  No cluster, no multicast.  Every wait is bounded.
+// Model work: forward 4*B*H*T^2*D flop (causal tiles are skipped, so about half is executed).
+#include <string.h>
+
+#include <mutex>
+#include <unordered_map>
+
+#include "tc_common.cuh"
+
+namespace alpha {
+
+using namespace tc;
+
+constexpr int AT_THREADS = 192;
+constexpr int AT_TILE = 128 * 64 * 2;  // one 128-row x 64-col bf16 tile, 16 KB
+
+struct AttnTcArgs {
+  void *o;
+  float *lse;
+  int64_t o_sb, o_sh, o_st;
+  int H, T;
+  float scale, cap;
+  uint32_t *err;
+};
+
+// shared-memory map (bytes from the 1024-aligned base)
+constexpr int AF_Q = 0;
+constexpr int AF_K = AT_TILE;                 // 2 stages
+constexpr int AF_V = AF_K + 2 * AT_TILE;      // 1 stage
+constexpr int AF_P = AF_V + AT_TILE;          // 2 tiles: keys 0-63, 64-127
+constexpr int AF_BAR = AF_P + 2 * AT_TILE;
+constexpr int AF_TOTAL = AF_BAR + 128;
+constexpr int AF_DYN = AF_TOTAL + 1024;
+
+__global__ void __launch_bounds__(AT_THREADS, 2)
+attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                   const __grid_constant__ CUtensorMap tmap_v, AttnTcArgs a) {
+  extern __shared__ uint8_t at_smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar = sb + AF_BAR;
+  const uint32_t q_full = bar, k_full0 = bar + 8, k_empty0 = bar + 24, v_full = bar + 40, v_empty = bar + 48,
+                 s_full = bar + 56, p_ready = bar + 64, pv_done = bar + 72;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AF_BAR + 80);
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qb = (a.T + 127) / 128;
+  const int qb = n_qb - 1 - (int)blockIdx.x;  // long rows first
+  const int bh = blockIdx.y;
+  const int b = bh / a.H, h = bh - b * a.H;
+  const int q0 = qb * 128;
+  const int nb = qb + 1;  // key blocks 0..qb
+  constexpr uint32_t TMEM_COLS = 256;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(k_full0, 1); mbar_init(k_full0 + 8, 1);
+    mbar_init(k_empty0, 1); mbar_init(k_empty0 + 8, 1);
+    mbar_init(v_full, 1); mbar_init(v_empty, 1);
+    mbar_init(s_full, 1);
+    mbar_init(p_ready, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tO = tmem_base + 128;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+      mbar_expect_tx(q_full, AT_TILE);
+      tma_load_4d(sb + AF_Q, &tmap_q, q_full, 0, q0, h, b);
+      for (int j = 0; j < nb; j++) {
+        const int st = j & 1;
+        const uint32_t ph = (j >> 1) & 1;
+        if (!mbar_wait(k_empty0 + 8 * st, ph ^ 1, abort_flag)) break;
+        mbar_expect_tx(k_full0 + 8 * st, AT_TILE);
+        tma_load_4d(sb + AF_K + st * AT_TILE, &tmap_k, k_full0 + 8 * st, 0, j * 128, h, b);
+        if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(v_full, AT_TILE);
+        tma_load_4d(sb + AF_V, &tmap_v, v_full, 0, j * 128, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      auto issue_pv = [&](int j) -> bool {  // O (+)= P(j) V(j)
+        if (!mbar_wait(p_ready, j & 1, abort_flag)) return false;
+        if (!mbar_wait(v_full, j & 1, abort_flag)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+          const uint64_t adesc = make_smem_desc(sb + AF_P + (kk >> 2) * AT_TILE + (kk & 3) * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(sb + AF_V + kk * 2048, AT_TILE, 1024);
+          mma_bf16_ss(tO, adesc, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(v_empty);
+        mma_commit(pv_done);
+        return true;
+      };
+      for (int j = 0; j < nb && ok; j++) {
+        if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+        const int st = j & 1;
+        if (!mbar_wait(k_full0 + 8 * st, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) {
+          const uint64_t adesc = make_smem_desc(sb + AF_Q + kk * 32, 16, 1024);
+          const uint64_t bdesc = make_smem_desc(sb + AF_K + st * AT_TILE + kk * 32, 16, 1024);
+          mma_bf16_ss(tS, adesc, bdesc, idesc_qk, kk > 0 ? 1u : 0u);
+        }
+        mma_commit(k_empty0 + 8 * st);
+        mma_commit(s_full);
+      }
+      if (ok) issue_pv(nb - 1);
+    }
+  } else {
+    // ── softmax warps: thread <-> query row <-> TMEM lane ────────────────────
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    const bool capped = a.cap > 0.f;
+    const float c1 = capped ? a.scale / a.cap : a.scale * LOG2E;  // argument scale
+    const float c2 = a.cap * LOG2E;                               // capped: x2 = c2 * tanh(c1 * s)
+    float m_used = -INFINITY, l = 0.f;
+    bool ok = true;
+    uint8_t *p_row = smem + AF_P + row * 128;
+    for (int j = 0; j < nb && ok; j++) {
+      if (!mbar_wait(s_full, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const bool diag = (j == qb);
+      // pass 1: row max of the raw scores (the score transform is monotonic)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off + c * 32, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i++) {
+          const float s = __uint_as_float(r[i]);
+          if (!diag || c * 32 + i <= row) mx = fmaxf(mx, s);
+        }
+      }
+      const float m_blk = capped ? c2 * tanh_approx(c1 * mx) : c1 * mx;
+      const float m_new = fmaxf(m_used, m_blk);
+      const bool need = m_new > m_used + 8.f;  // also true while m_used is -inf
+      if (j > 0) {
+        if (!mbar_wait(pv_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, need)) {
+          const float alpha = need ? ex2_approx(m_used - m_new) : 1.f;
+          l *= alpha;
+#pragma unroll 1
+          for (int c = 0; c < 2; c++) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c * 32, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; i++) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tO + lane_off + c * 32, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      if (need) m_used = m_new;
+      // pass 2: P = exp2(x2 - m_used) -> bf16 -> swizzled shared memory
+      float lsum = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + lane_off + c * 32, r);
+        tmem_ld_wait();
+        uint32_t packed[16];
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          float p0, p1;
+          {
+            const float s = __uint_as_float(r[i]);
+            const float x2 = capped ? c2 * tanh_approx(c1 * s) : c1 * s;
+            p0 = (diag && c * 32 + i > row) ? 0.f : ex2_approx(x2 - m_used);
+          }
+          {
+            const float s = __uint_as_float(r[i + 1]);
+            const float x2 = capped ? c2 * tanh_approx(c1 * s) : c1 * s;
+            p1 = (diag && c * 32 + i + 1 > row) ? 0.f : ex2_approx(x2 - m_used);
+          }
+          const __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+          // the row sum uses the rounded values that the tensor core will multiply
+          const float2 back = __bfloat1622float2(pk);
+          lsum += back.x + back.y;
+          packed[i >> 1] = *reinterpret_cast<const uint32_t *>(&pk);
+        }
+        uint8_t *tile_row = p_row + (c >> 1) * AT_TILE;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
+          *reinterpret_cast<uint4 *>(tile_row + chunk * 16) =
+              make_uint4(packed[4 * q], packed[4 * q + 1], packed[4 * q + 2], packed[4 * q + 3]);
+        }
+      }
+      l += lsum;
+      fence_proxy_async();  // generic-proxy stores -> visible to the tensor core's reads
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_ready);
+    }
+    if (ok && mbar_wait(pv_done, (nb - 1) & 1, abort_flag)) {
+      tc_fence_after();
+      const int qi = q0 + row;
+      const float inv = 1.f / l;
+      __nv_bfloat16 *orow = (__nv_bfloat16 *)a.o + (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + (int64_t)qi * a.o_st;
+#pragma unroll 1
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (qi < a.T) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]) * inv;
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(orow + c * 32 + q * 8);
+          }
+        }
+      }
+      if (qi < a.T) a.lse[(int64_t)bh * a.T + qi] = (m_used + log2f(l)) * 0.6931471805599453f;
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 0xA7000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ── backward ────────────────────────────────────────────────────────────────
+// Two kernels, each output tile owned by one CTA (no atomics: gradients are reproducible):
+//   dK/dV kernel: CTA = (batch, head, 128 keys), loops over the query blocks at or after it;
+//   dQ    kernel: CTA = (batch, head, 128 queries), loops over the key blocks at or before it.
+// Per (query block, key block) pair both recompute S = Q K^T and dP = dO V^T on the tensor
+// cores into TMEM; the 128 "softmax" threads (one query row each) turn them into
+// P = exp2(x2 - lse2) and dS = P*(dP - D)*(1 - tanh^2)*scale, round to bf16 and store them as
+// [query rows][key columns] 128B-swizzled tiles.  That one layout serves both remaining
+// products: read K-major it is the A operand of dQ += dS K, read M-major it is the A operand
+// of dV += P^T dO and dK += dS^T Q (the tensor core transposes through the descriptor).
+// Q, dO, K, V tiles are likewise used both K-major (score products) and N-major (gradient
+// products) from the same bytes.
+struct AttnBwdArgs {
+  void *dq, *dk, *dv;
+  const float *lse, *delta;
+  int64_t q_sb, q_sh, q_st;
+  int H, T;
+  float scale, cap;
+  uint32_t *err;
+};
+
+// delta[bh*T + t] = sum_d dO[t,d] * O[t,d]; one warp per row (64 elements, 2 per lane)
+__global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 *__restrict__ o,
+                                                            const __nv_bfloat16 *__restrict__ d_o, float *delta,
+                                                            int64_t o_sb, int64_t o_sh, int64_t o_st, int H, int T,
+                                                            int64_t rows) {
+  const int lane = threadIdx.x & 31;
+  for (int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * 8) {
+    const int64_t bh = r / T;
+    const int t = (int)(r - bh * T);
+    const int b = (int)(bh / H), h = (int)(bh - (int64_t)b * H);
+    const int64_t off = b * o_sb + h * o_sh + (int64_t)t * o_st + lane * 2;
+    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(o + off));
+    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(d_o + off));
+    const float s = warp_sum(x.x * y.x + x.y * y.y);
+    if (lane == 0) delta[r] = s;
+  }
+}
+
+// One thread = one query row (TMEM lane).  Reads its S and dP rows, writes the bf16 P (optional)
+// and dS rows into the swizzled tiles.
+template <bool WRITE_P>
+__device__ __forceinline__ void bwd_row_math(uint32_t tS, uint32_t tdP, uint32_t lane_off, uint8_t *p_row,
+                                             uint8_t *ds_row, int row, bool diag, bool row_valid, float lse2,
+                                             float delta, float c1, float c2, bool capped, float scale) {
+#pragma unroll 1
+  for (int c = 0; c < 4; c++) {
+    uint32_t r[32], d[32];
+    tmem_ld_32x32(tS + lane_off + c * 32, r);
+    tmem_ld_32x32(tdP + lane_off + c * 32, d);
+    tmem_ld_wait();
+    uint32_t pp[16], dd[16];
+#pragma unroll
+    for (int i = 0; i < 32; i += 2) {
+      float p[2], ds[2];
+#pragma unroll
+      for (int u = 0; u < 2; u++) {
+        const float s = __uint_as_float(r[i + u]);
+        float x2, dcap = 1.f;
+        if (capped) {
+          const float th = tanh_approx(c1 * s);
+          x2 = c2 * th;
+          dcap = 1.f - th * th;
+        } else {
+          x2 = c1 * s;
+        }
+        const bool dead = !row_valid || (diag && c * 32 + i + u > row);
+        p[u] = dead ? 0.f : ex2_approx(x2 - lse2);
+        ds[u] = p[u] * (__uint_as_float(d[i + u]) - delta) * dcap * scale;
+      }
+      const __nv_bfloat162 pk = __floats2bfloat162_rn(p[0], p[1]);
+      const __nv_bfloat162 dk = __floats2bfloat162_rn(ds[0], ds[1]);
+      pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pk);
+      dd[i >> 1] = *reinterpret_cast<const uint32_t *>(&dk);
+    }
+#pragma unroll
+    for (int q = 0; q < 4; q++) {
+      const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
+      const int off = (c >> 1) * AT_TILE + chunk * 16;
+      if (WRITE_P) *reinterpret_cast<uint4 *>(p_row + off) = make_uint4(pp[4 * q], pp[4 * q + 1], pp[4 * q + 2], pp[4 * q + 3]);
+      *reinterpret_cast<uint4 *>(ds_row + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+    }
+  }
+}
+
+// shared-memory map of the dK/dV kernel
+constexpr int AK_K = 0;
+constexpr int AK_V = AT_TILE;
+constexpr int AK_Q = 2 * AT_TILE;              // 2 stages of (Q, dO)
+constexpr int AK_DO = AK_Q + 2 * AT_TILE;
+constexpr int AK_P = AK_DO + 2 * AT_TILE;      // 2 tiles
+constexpr int AK_DS = AK_P + 2 * AT_TILE;      // 2 tiles
+constexpr int AK_BAR = AK_DS + 2 * AT_TILE;
+constexpr int AK_DYN = AK_BAR + 128 + 1024;
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                       AttnBwdArgs a) {
+  extern __shared__ uint8_t at_smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar = sb + AK_BAR;
+  const uint32_t kv_full = bar, q_full0 = bar + 8, q_empty0 = bar + 24, sdp_full = bar + 40, pds_ready = bar + 48,
+                 acc_done = bar + 56;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 64);
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qb = (a.T + 127) / 128;
+  const int kb = blockIdx.x;            // key block; it has n_qb - kb query blocks to visit
+  const int bh = blockIdx.y;
+  const int b = bh / a.H, h = bh - b * a.H;
+  const int k0 = kb * 128;
+  const int n_it = n_qb - kb;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    mbar_init(kv_full, 1);
+    mbar_init(q_full0, 1); mbar_init(q_full0 + 8, 1);
+    mbar_init(q_empty0, 1); mbar_init(q_empty0 + 8, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(pds_ready, 4);
+    mbar_init(acc_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 320;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(kv_full, 2 * AT_TILE);
+      tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, k0, h, b);
+      tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, k0, h, b);
+      for (int it = 0; it < n_it; it++) {
+        const int st = it & 1;
+        if (!mbar_wait(q_empty0 + 8 * st, ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(q_full0 + 8 * st, 2 * AT_TILE);
+        const int q0 = (kb + it) * 128;
+        tma_load_4d(sb + AK_Q + st * AT_TILE, &tmap_q, q_full0 + 8 * st, 0, q0, h, b);
+        tma_load_4d(sb + AK_DO + st * AT_TILE, &tmap_do, q_full0 + 8 * st, 0, q0, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [q x k] = A[q,d] B[k,d]^T
+      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, true, true);      // [k x d] = A[q,k]^T B[q,d]
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      for (int it = 0; it < n_it && ok; it++) {
+        const int st = it & 1;
+        if (!mbar_wait(q_full0 + 8 * st, (it >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t qs = sb + AK_Q + st * AT_TILE, dos = sb + AK_DO + st * AT_TILE;
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          mma_bf16_ss(tS, make_smem_desc(qs + kk * 32, 16, 1024), make_smem_desc(sb + AK_K + kk * 32, 16, 1024), idesc_s,
+                      kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          mma_bf16_ss(tdP, make_smem_desc(dos + kk * 32, 16, 1024), make_smem_desc(sb + AK_V + kk * 32, 16, 1024),
+                      idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(sdp_full);
+        if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {  // 16 query rows per step
+          mma_bf16_ss(tdV, make_smem_desc(sb + AK_P + kk * 2048, AT_TILE, 1024), make_smem_desc(dos + kk * 2048, AT_TILE, 1024),
+                      idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {
+          mma_bf16_ss(tdK, make_smem_desc(sb + AK_DS + kk * 2048, AT_TILE, 1024), make_smem_desc(qs + kk * 2048, AT_TILE, 1024),
+                      idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(q_empty0 + 8 * st);
+        mma_commit(acc_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    const bool capped = a.cap > 0.f;
+    const float c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
+    const float c2 = a.cap * LOG2E;
+    bool ok = true;
+    for (int it = 0; it < n_it && ok; it++) {
+      const int qi = (kb + it) * 128 + row;
+      const bool valid = qi < a.T;
+      const float lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+      const float dl = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+      // sdp_full also means the gradient products of the previous iteration have finished
+      // reading the P / dS tiles (commits complete in issue order)
+      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      bwd_row_math<true>(tS, tdP, lane_off, smem + AK_P + row * 128, smem + AK_DS + row * 128, row, it == 0, valid,
+                         lse2, dl, c1, c2, capped, a.scale);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(pds_ready);
+    }
+    if (ok && mbar_wait(acc_done, (n_it - 1) & 1, abort_flag)) {
+      tc_fence_after();
+      const int kj = k0 + row;  // accumulator lanes are keys
+      const int64_t off = (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)kj * a.q_st;
+#pragma unroll 1
+      for (int which = 0; which < 2; which++) {
+        __nv_bfloat16 *dst = (__nv_bfloat16 *)(which ? a.dk : a.dv) + off;
+        const uint32_t tacc = which ? tdK : tdV;
+#pragma unroll 1
+        for (int c = 0; c < 2; c++) {
+          uint32_t r[32];
+          tmem_ld_32x32(tacc + lane_off + c * 32, r);
+          tmem_ld_wait();
+          if (kj < a.T) {
+#pragma unroll
+            for (int q = 0; q < 4; q++) {
+              float f[8];
+#pragma unroll
+              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+              Vec16<__nv_bfloat16> v;
+              v.set(f);
+              v.store(dst + c * 32 + q * 8);
+            }
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 0xA8000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// shared-memory map of the dQ kernel
+constexpr int AQ_Q = 0;
+constexpr int AQ_DO = AT_TILE;
+constexpr int AQ_K = 2 * AT_TILE;              // 2 stages of (K, V)
+constexpr int AQ_V = AQ_K + 2 * AT_TILE;
+constexpr int AQ_DS = AQ_V + 2 * AT_TILE;      // 2 tiles
+constexpr int AQ_BAR = AQ_DS + 2 * AT_TILE;
+constexpr int AQ_DYN = AQ_BAR + 128 + 1024;
+
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
+                      AttnBwdArgs a) {
+  extern __shared__ uint8_t at_smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar = sb + AQ_BAR;
+  const uint32_t q_full = bar, kv_full0 = bar + 8, kv_empty0 = bar + 24, sdp_full = bar + 40, ds_ready = bar + 48,
+                 dq_done = bar + 56;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 64);
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qb = (a.T + 127) / 128;
+  const int qb = n_qb - 1 - (int)blockIdx.x;  // long rows first
+  const int bh = blockIdx.y;
+  const int b = bh / a.H, h = bh - b * a.H;
+  const int q0 = qb * 128;
+  const int nb = qb + 1;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    mbar_init(kv_full0, 1); mbar_init(kv_full0 + 8, 1);
+    mbar_init(kv_empty0, 1); mbar_init(kv_empty0 + 8, 1);
+    mbar_init(sdp_full, 1);
+    mbar_init(ds_ready, 4);
+    mbar_init(dq_done, 1);
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * AT_TILE);
+      tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, q0, h, b);
+      tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, q0, h, b);
+      for (int j = 0; j < nb; j++) {
+        const int st = j & 1;
+        if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
+        tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
+        tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);     // [q x d] = A[q,k] B[k,d]
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      for (int j = 0; j < nb && ok; j++) {
+        const int st = j & 1;
+        if (!mbar_wait(kv_full0 + 8 * st, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t ks = sb + AQ_K + st * AT_TILE, vs = sb + AQ_V + st * AT_TILE;
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          mma_bf16_ss(tS, make_smem_desc(sb + AQ_Q + kk * 32, 16, 1024), make_smem_desc(ks + kk * 32, 16, 1024), idesc_s,
+                      kk > 0 ? 1u : 0u);
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++)
+          mma_bf16_ss(tdP, make_smem_desc(sb + AQ_DO + kk * 32, 16, 1024), make_smem_desc(vs + kk * 32, 16, 1024), idesc_s,
+                      kk > 0 ? 1u : 0u);
+        mma_commit(sdp_full);
+        if (!mbar_wait(ds_ready, j & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++) {  // 16 keys per step
+          mma_bf16_ss(tdQ, make_smem_desc(sb + AQ_DS + (kk >> 2) * AT_TILE + (kk & 3) * 32, 16, 1024),
+                      make_smem_desc(ks + kk * 2048, AT_TILE, 1024), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
+        }
+        mma_commit(kv_empty0 + 8 * st);
+        if (j == nb - 1) mma_commit(dq_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    const bool capped = a.cap > 0.f;
+    const float c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
+    const float c2 = a.cap * LOG2E;
+    const int qi = q0 + row;
+    const bool valid = qi < a.T;
+    const float lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+    const float dl = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; j++) {
+      if (!mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      bwd_row_math<false>(tS, tdP, lane_off, nullptr, smem + AQ_DS + row * 128, row, j == qb, valid, lse2, dl, c1, c2,
+                          capped, a.scale);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(ds_ready);
+    }
+    if (ok && mbar_wait(dq_done, 0, abort_flag)) {
+      tc_fence_after();
+      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st;
+#pragma unroll 1
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tdQ + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (valid) {
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            float f[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(dst + c * 32 + q * 8);
+          }
+        }
+      }
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 0xA9000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
+// ── host ────────────────────────────────────────────────────────────────────
+struct Tmap4Key {
+  uint64_t base, T, H, B, st, sh, sb;
+  uint32_t rows;
+  bool operator==(const Tmap4Key &o) const {
+    return base == o.base && T == o.T && H == o.H && B == o.B && st == o.st && sh == o.sh && sb == o.sb && rows == o.rows;
+  }
+};
+struct Tmap4Hash {
+  size_t operator()(const Tmap4Key &k) const {
+    uint64_t h = k.base * 0x9e3779b97f4a7c15ull ^ (k.T << 7) ^ (k.H << 23) ^ (k.B << 37) ^ (k.st * 31) ^ (k.sh * 131) ^
+                 (k.sb * 0xff51afd7ed558ccdull) ^ k.rows;
+    return (size_t)(h ^ (h >> 31));
+  }
+};
+static std::unordered_map<Tmap4Key, CUtensorMap, Tmap4Hash> g_tmaps4;
+static std::mutex g_tmap4_mu;
+
+static int get_tmap4(CUtensorMap *out, const void *base, const alpha_attn_params_t *p, int64_t st, int64_t sh, int64_t sb,
+                     uint32_t rows) {
+  Tmap4Key key{(uint64_t)(uintptr_t)base, (uint64_t)p->T, (uint64_t)p->heads, (uint64_t)p->batch, (uint64_t)st,
+               (uint64_t)sh, (uint64_t)sb, rows};
+  std::lock_guard<std::mutex> lk(g_tmap4_mu);
+  auto it = g_tmaps4.find(key);
+  if (it != g_tmaps4.end()) {
+    *out = it->second;
+    return 0;
+  }
+  if (encode_tmap_4d_bf16(out, base, 64, p->T, p->heads, p->batch, st, sh, sb, rows)) return 1;
+  if (g_tmaps4.size() > 4096) g_tmaps4.clear();
+  g_tmaps4[key] = *out;
+  return 0;
+}
+
+// The tensor-core path needs bf16 storage, head dim 64 and strides that TMA can describe.
+bool attn_tc_supported(const alpha_attn_params_t *p, alpha_buf q, alpha_buf k, alpha_buf v) {
+  if (p->dtype != ALPHA_BF16 || p->D != 64) return false;
+  if ((q | k | v) & 15) return false;
+  if (p->q_st % 8 || (p->heads > 1 && p->q_sh % 8) || (p->batch > 1 && p->q_sb % 8)) return false;
+  if (p->o_st % 8 || p->o_sh % 8 || p->o_sb % 8) return false;
+  if (p->batch * p->heads > 65535) return false;
+  return true;
+}
+
+int attn_tc_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf lse, const alpha_attn_params_t *p) {
+  if (p->batch * p->heads * p->T == 0) return 0;
+  ProfScope prof(PROF_ATTN_FWD, 4.0 * p->batch * p->heads * (double)p->T * p->T * p->D);
+  CUtensorMap tq, tk, tv;
+  if (get_tmap4(&tq, ptr<void>(q), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  if (get_tmap4(&tk, ptr<void>(k), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  if (get_tmap4(&tv, ptr<void>(v), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  AttnTcArgs a;
+  memset(&a, 0, sizeof(a));
+  a.o = ptr<void>(o);
+  a.lse = ptr<float>(lse);
+  a.o_sb = p->o_sb; a.o_sh = p->o_sh; a.o_st = p->o_st;
+  a.H = (int)p->heads; a.T = (int)p->T;
+  a.scale = p->scale; a.cap = p->soft_cap;
+  a.err = tc_error_word();
+  static bool attr = false;
+  if (!attr) {
+    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF_DYN));
+    attr = true;
+  }
+  dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
+  attn_tc_fwd_kernel<<<grid, AT_THREADS, AF_DYN, g_stream>>>(tq, tk, tv, a);
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_o, alpha_buf lse, alpha_buf dq,
+                alpha_buf dk, alpha_buf dv, const alpha_attn_params_t *p) {
+  if (p->batch * p->heads * p->T == 0) return 0;
+  ProfScope prof(PROF_ATTN_BWD, 8.0 * p->batch * p->heads * (double)p->T * p->T * p->D);
+  CUtensorMap tq, tk, tv, tdo;
+  if (get_tmap4(&tq, ptr<void>(q), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  if (get_tmap4(&tk, ptr<void>(k), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  if (get_tmap4(&tv, ptr<void>(v), p, p->q_st, p->q_sh, p->q_sb, 128)) return 1;
+  if (get_tmap4(&tdo, ptr<void>(d_o), p, p->o_st, p->o_sh, p->o_sb, 128)) return 1;
+  const int64_t rows = p->batch * p->heads * p->T;
+  void *delta = nullptr;
+  if (pool_alloc((size_t)rows * sizeof(float), &delta)) return 1;
+  attn_tc_delta_kernel<<<grid_for(rows, 8, 8), 256, 0, g_stream>>>(ptr<__nv_bfloat16>(o), ptr<__nv_bfloat16>(d_o),
+                                                                    (float *)delta, p->o_sb, p->o_sh, p->o_st,
+                                                                    (int)p->heads, (int)p->T, rows);
+  g_launches++;
+  AttnBwdArgs a;
+  memset(&a, 0, sizeof(a));
+  a.dq = ptr<void>(dq); a.dk = ptr<void>(dk); a.dv = ptr<void>(dv);
+  a.lse = ptr<float>(lse); a.delta = (const float *)delta;
+  a.q_sb = p->q_sb; a.q_sh = p->q_sh; a.q_st = p->q_st;
+  a.H = (int)p->heads; a.T = (int)p->T;
+  a.scale = p->scale; a.cap = p->soft_cap;
+  a.err = tc_error_word();
+  static bool attr = false;
+  if (!attr) {
+    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AK_DYN));
+    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AQ_DYN));
+    attr = true;
+  }
+  dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
+  attn_tc_bwd_dkv_kernel<<<grid, AT_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  g_launches++;
+  attn_tc_bwd_dq_kernel<<<grid, AT_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  pool_free(delta);
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+}  // namespace alpha

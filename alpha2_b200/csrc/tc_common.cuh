@@ -78,6 +78,23 @@ __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y), "r"(z)
       : "memory");
 }
+__device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map, uint32_t bar, int32_t c0, int32_t c1,
+                                            int32_t c2, int32_t c3) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2];"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+      : "memory");
+}
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float tanh_approx(float x) {
+  float y;
+  asm volatile("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap *map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
 }
@@ -168,6 +185,11 @@ int encode_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t inner, uint
                         uint32_t box_inner, uint32_t box_outer);
 int encode_tmap_3d_bf16(CUtensorMap *out, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1_elems,
                         uint64_t ld2_elems, uint32_t box0, uint32_t box1, uint32_t box2);
+
+// 4-D bf16 map for attention operands: dims (D, T, H, B) with element strides
+// (1, st, sh, sb); box (64, box_rows, 1, 1).
+int encode_tmap_4d_bf16(CUtensorMap *out, const void *base, uint64_t D, uint64_t T, uint64_t H, uint64_t Bn,
+                        uint64_t st, uint64_t sh, uint64_t sb, uint32_t box_rows);
 
 // Device-side error word set by any kernel whose bounded wait ran out (0 = none).
 uint32_t *tc_error_word();

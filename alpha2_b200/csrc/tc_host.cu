@@ -70,6 +70,32 @@ int encode_tmap_3d_bf16(CUtensorMap *out, const void *base, uint64_t d0, uint64_
   return 0;
 }
 
+int encode_tmap_4d_bf16(CUtensorMap *out, const void *base, uint64_t D, uint64_t T, uint64_t H, uint64_t Bn,
+                        uint64_t st, uint64_t sh, uint64_t sb, uint32_t box_rows) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return set_error("tensor map: cuTensorMapEncodeTiled is not available from this driver");
+  if (((uintptr_t)base & 15) != 0) return set_error("tensor map: base address %p is not 16-byte aligned", base);
+  if (D != 64) return set_error("tensor map: attention head dim must be 64 (one 128-byte swizzle row)");
+  // a dimension of extent 1 still needs a legal stride
+  if (H == 1 && (sh == 0 || (sh * 2) % 16 != 0)) sh = st * T;
+  if (Bn == 1 && (sb == 0 || (sb * 2) % 16 != 0)) sb = st * T;
+  if ((st * 2) % 16 != 0 || (sh * 2) % 16 != 0 || (sb * 2) % 16 != 0 || sh == 0 || sb == 0)
+    return set_error("tensor map: attention strides (%llu, %llu, %llu) must be non-zero multiples of 8 elements",
+                     (unsigned long long)st, (unsigned long long)sh, (unsigned long long)sb);
+  cuuint64_t dims[4] = {D, T, H, Bn};
+  cuuint64_t strides[3] = {st * 2, sh * 2, sb * 2};
+  cuuint32_t box[4] = {64, box_rows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void *>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS)
+    return set_error("cuTensorMapEncodeTiled (4d) failed (%d): T=%llu H=%llu B=%llu strides %llu/%llu/%llu", (int)r,
+                     (unsigned long long)T, (unsigned long long)H, (unsigned long long)Bn, (unsigned long long)st,
+                     (unsigned long long)sh, (unsigned long long)sb);
+  return 0;
+}
+
 static uint32_t *g_err_word = nullptr;
 
 uint32_t *tc_error_word() {

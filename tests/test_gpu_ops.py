@@ -453,10 +453,12 @@ def test_flash_attention_contract(B, cfg, dtype):
         assert rel_err(g[name].data, ref) < tol * 2, name
 
 
+@pytest.mark.parametrize("geom", [(2, 96, 4, 16), (2, 200, 3, 64), (1, 512, 2, 64)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_attention_on_fused_qkv(B, dtype):
-    """q/k/v read in place from [B*T, 3E]; output head-merged; gradients land in [B*T, 3E]."""
-    Bn, T, H, D = 2, 96, 4, 16
+def test_attention_on_fused_qkv(B, dtype, geom):
+    """q/k/v read in place from [B*T, 3E]; output head-merged; gradients land in [B*T, 3E].
+    Head dim 64 in bf16 is the tensor-core path (ragged T = 200 included)."""
+    Bn, T, H, D = geom
     E = H * D
     r = rng(21)
     qkv = r.standard_normal((Bn * T, 3 * E)).astype(f32)
