@@ -95,9 +95,9 @@ SIGNATURES = {
     "alpha_embedding_pos_fwd": [_B, _B, _B, _B, _L, _L, _L, _L, _I],
     "alpha_embedding_bwd": [_B, _B, _B, _L, _L, _L, _I, _I],
     "alpha_layernorm_fwd": [_B, _B, _B, _B, _L, _L, _F, _I],
-    "alpha_layernorm_bwd": [_B, _B, _B, _B, _B, _B, _L, _L, _F, _I, _I],
+    "alpha_layernorm_bwd": [_B, _B, _B, _B, _B, _B, _L, _L, _F, _I, _I, _B],
     "alpha_rmsnorm_fwd": [_B, _B, _B, _L, _L, _F, _I],
-    "alpha_rmsnorm_bwd": [_B, _B, _B, _B, _B, _L, _L, _F, _I, _I],
+    "alpha_rmsnorm_bwd": [_B, _B, _B, _B, _B, _L, _L, _F, _I, _I, _B],
     "alpha_gemm": [_I, _B, _B, _B, _L, _L, _L, _L, _L, _L, _I, _I, _I, _B, _L, _I],
     "alpha_gemm_batched_f32": [_I, _B, _B, _B, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L],
     "alpha_flash_attn_fwd": [_B, _B, _B, _B, _B, C.POINTER(AttnParams)],

@@ -37,10 +37,20 @@ class Variable:
 
 
 class _Entry:
-    __slots__ = ("output", "inputs", "backward", "cleanup")
+    __slots__ = ("output", "inputs", "backward", "cleanup", "in_place")
 
-    def __init__(self, output, inputs, backward, cleanup=None):
+    def __init__(self, output, inputs, backward, cleanup=None, in_place=False):
         self.output, self.inputs, self.backward, self.cleanup = output, inputs, backward, cleanup
+        self.in_place = in_place
+
+
+class _Accumulated:
+    """Returned by a backward closure in place of a gradient that it has already added into
+    the input's existing ``grad`` (fused accumulation); the tape then has nothing to add."""
+    __slots__ = ()
+
+
+ACCUMULATED = _Accumulated()
 
 
 def _exclusive(td: TensorData) -> bool:
@@ -54,8 +64,11 @@ class Tape:
     def __init__(self):
         self.entries: list[_Entry] = []
 
-    def record(self, output: Variable, inputs: Sequence[Variable], backward: Callable, cleanup: Callable | None = None):
-        self.entries.append(_Entry(output, list(inputs), backward, cleanup))
+    def record(self, output: Variable, inputs: Sequence[Variable], backward: Callable, cleanup: Callable | None = None,
+               in_place: bool = False):
+        """``in_place``: the closure takes a fifth argument, the inputs' current gradients, and
+        may add into them itself, returning ACCUMULATED for those inputs."""
+        self.entries.append(_Entry(output, list(inputs), backward, cleanup, in_place))
 
     @property
     def size(self) -> int:
@@ -82,13 +95,17 @@ class Tape:
                     onEntryDone(entry)
                 continue
             needs = [v.requiresGrad for v in entry.inputs]
-            grads = entry.backward(out_grad, backend, releaseTensor, needs)
+            if entry.in_place:
+                grads = entry.backward(out_grad, backend, releaseTensor, needs,
+                                       [v.grad if v.requiresGrad else None for v in entry.inputs])
+            else:
+                grads = entry.backward(out_grad, backend, releaseTensor, needs)
             uses: dict[int, int] = {}
             for v, g in zip(entry.inputs, grads):
-                if g is not None and v.requiresGrad:
+                if g is not None and g is not ACCUMULATED and v.requiresGrad:
                     uses[id(g)] = uses.get(id(g), 0) + 1
             for v, g in zip(entry.inputs, grads):
-                if g is None:
+                if g is None or g is ACCUMULATED:
                     continue
                 if not v.requiresGrad:
                     if id(g) not in uses:
@@ -137,9 +154,9 @@ class Ctx:
         self.tape, self.backend, self.dropoutRng, self.release = tape, backend, dropoutRng, release
 
 
-def _record(ctx, data, inputs, backward, cleanup=None) -> Variable:
+def _record(ctx, data, inputs, backward, cleanup=None, in_place=False) -> Variable:
     out = Variable(data, True)
-    ctx.tape.record(out, inputs, backward, cleanup)
+    ctx.tape.record(out, inputs, backward, cleanup, in_place)
     return out
 
 
@@ -356,10 +373,11 @@ def embedding(ctx, weight: Variable, indices: TensorData) -> Variable:
 def layerNorm(ctx, x, weight, bias, eps):
     xd, wd = x.data, weight.data
 
-    def bw(g, B, rel, n):
-        r = B.layerNormBackward(xd, wd, g, eps)
-        return [r["dx"], r["dw"], r["db"]]
-    return _record(ctx, ctx.backend.layerNorm(xd, wd, bias.data, eps), [x, weight, bias], bw)
+    def bw(g, B, rel, n, acc):
+        into = acc[0] if acc[0] is not None and acc[0].dtype == xd.dtype else None
+        r = B.layerNormBackward(xd, wd, g, eps, into) if into is not None else B.layerNormBackward(xd, wd, g, eps)
+        return [ACCUMULATED if into is not None else r["dx"], r["dw"], r["db"]]
+    return _record(ctx, ctx.backend.layerNorm(xd, wd, bias.data, eps), [x, weight, bias], bw, in_place=True)
 
 
 def dropout(ctx, a, p, training):
@@ -485,6 +503,25 @@ def linearAdd(ctx, x: Variable, w: Variable, residual: Variable) -> Variable:
     return _record(ctx, ctx.backend.matmulTransposedAdd(xd, wd, residual.data), [x, w, residual], bw)
 
 
+def mlpGelu(ctx, x: Variable, w1: Variable, w2: Variable, residual: Variable) -> Variable:
+    """residual + gelu(x @ w1^T) @ w2^T as one tape entry and two launches forward
+    (GELU and the residual add live in the GEMM epilogues).  Backward is five GEMMs and no
+    elementwise pass: d_pre = (g @ w2) * gelu'(pre) comes out of one GEMM epilogue."""
+    xd = x.data
+    w1d, w2d = _compute_weight(w1), _compute_weight(w2)
+    B0 = ctx.backend
+    pre, act = B0.matmulTransposedGelu(xd, w1d)
+    out = B0.matmulTransposedAdd(act, w2d, residual.data)
+
+    def bw(g, B, rel, needs):
+        dw2 = B.matmulTransposedA(g, act) if needs[2] else None
+        dpre = B.matmulGeluBackward(g, w2d, pre)
+        dx = B.matmul(dpre, w1d) if needs[0] else None
+        dw1 = B.matmulTransposedA(dpre, xd) if needs[1] else None
+        return [dx, dw1, dw2, g]
+    return _record(ctx, out, [x, w1, w2, residual], bw)
+
+
 def _compute_weight(w: Variable) -> TensorData:
     sh = getattr(w, "shadow", None)
     return sh if sh is not None else w.data
@@ -529,10 +566,11 @@ def ropeQk(ctx, qkv: Variable, Bn: int, T: int, H: int, theta: float = 10000.0) 
 def rmsNorm(ctx, x, weight, eps):
     xd, wd = x.data, weight.data
 
-    def bw(g, B, rel, n):
-        r = B.rmsNormBackward(xd, wd, g, eps)
-        return [r["dx"], r["dw"]]
-    return _record(ctx, ctx.backend.rmsNorm(xd, wd, eps), [x, weight], bw)
+    def bw(g, B, rel, n, acc):
+        into = acc[0] if acc[0] is not None and acc[0].dtype == xd.dtype else None
+        r = B.rmsNormBackward(xd, wd, g, eps, into) if into is not None else B.rmsNormBackward(xd, wd, g, eps)
+        return [ACCUMULATED if into is not None else r["dx"], r["dw"]]
+    return _record(ctx, ctx.backend.rmsNorm(xd, wd, eps), [x, weight], bw, in_place=True)
 
 
 def embeddingPos(ctx, wte: Variable, wpe: Variable, tokens: TensorData) -> Variable:
@@ -543,8 +581,12 @@ def embeddingPos(ctx, wte: Variable, wpe: Variable, tokens: TensorData) -> Varia
     vocab, dim = wte.data.shape
     out = B0.reshape(B0.embeddingPos(_compute_weight(wte), _compute_weight(wpe), tokens), (Bn * T, dim))
 
-    def bw(g, B, rel, needs):
-        dwte = B.embeddingBackward(tokens, g, vocab)
+    def bw(g, B, rel, needs, acc):
+        if acc[0] is not None and acc[0].dtype == "f32":     # tied head: add into the head's dW
+            B.embeddingBackward(tokens, g, vocab, out=acc[0])
+            dwte = ACCUMULATED
+        else:
+            dwte = B.embeddingBackward(tokens, g, vocab)
         gp = B.sum(B.reshape(g, (Bn, T * dim)), 0)          # [T*dim], storage dtype
         dwpe = B.reshape(gp, (T, dim))
         if dwpe.dtype != "f32":
@@ -554,7 +596,7 @@ def embeddingPos(ctx, wte: Variable, wpe: Variable, tokens: TensorData) -> Varia
             B.lib.alpha_d2d(full.ptr, dwpe.ptr, dwpe.nbytes)
             dwpe = full
         return [dwte, dwpe]
-    return _record(ctx, out, [wte, wpe], bw)
+    return _record(ctx, out, [wte, wpe], bw, in_place=True)
 
 
 def lmHeadLoss(ctx, x: Variable, w: Variable, targets: TensorData, gradScale: float = 1.0) -> Variable:

@@ -527,12 +527,16 @@ class CudaBackend:
                                            self._code(x.dtype)))
         return out
 
-    def layerNormBackward(self, x, weight, gradOutput, eps) -> dict:
+    def layerNormBackward(self, x, weight, gradOutput, eps, dxInto: TensorData | None = None) -> dict:
+        """``dxInto``: an existing gradient of x; the kernel adds dx to it in place (one pass
+        instead of a separate addInplace) and "dx" is that tensor."""
         dim = x.shape[-1]
-        dx = self._new(x.shape, x.dtype)
+        dx = dxInto if dxInto is not None else self._new(x.shape, x.dtype)
         dw, db = self._new(weight.shape, "f32"), self._new(weight.shape, "f32")
         check(self.lib.alpha_layernorm_bwd(x.ptr, weight.ptr, gradOutput.ptr, dx.ptr, dw.ptr, db.ptr,
-                                           x.size // dim, dim, float(eps), self._code(x.dtype), 0))
+                                           x.size // dim, dim, float(eps), self._code(x.dtype), 0,
+                                           dxInto.ptr if dxInto is not None else 0))
+        dx.invalidate_host()
         return {"dx": dx, "dw": dw, "db": db}
 
     def rmsNorm(self, x, weight, eps) -> TensorData:
@@ -542,11 +546,13 @@ class CudaBackend:
                                          self._code(x.dtype)))
         return out
 
-    def rmsNormBackward(self, x, weight, gradOutput, eps) -> dict:
+    def rmsNormBackward(self, x, weight, gradOutput, eps, dxInto: TensorData | None = None) -> dict:
         dim = x.shape[-1]
-        dx, dw = self._new(x.shape, x.dtype), self._new(weight.shape, "f32")
+        dx = dxInto if dxInto is not None else self._new(x.shape, x.dtype)
+        dw = self._new(weight.shape, "f32")
         check(self.lib.alpha_rmsnorm_bwd(x.ptr, weight.ptr, gradOutput.ptr, dx.ptr, dw.ptr, x.size // dim, dim,
-                                         float(eps), self._code(x.dtype), 0))
+                                         float(eps), self._code(x.dtype), 0, dxInto.ptr if dxInto is not None else 0))
+        dx.invalidate_host()
         return {"dx": dx, "dw": dw}
 
     def rope(self, x: TensorData, batch: int, T: int, heads: int, D: int, ld: int, col_offset: int = 0,

@@ -82,7 +82,7 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_fwd_warp(const T *__restrict
 // Backward, one warp per row, persistent over rows.  part: [gridDim.x, 2, dim] f32.
 template <typename T, int NV, bool RMS>
 __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_warp(const T *__restrict__ x, const float *__restrict__ w,
-                                                             const T *__restrict__ g, T *__restrict__ dx,
+                                                             const T *__restrict__ g, const T *dx_add, T *dx,
                                                              float *__restrict__ part, int64_t rows, int dim,
                                                              float eps) {
   constexpr int V = Vec16<T>::N;
@@ -165,6 +165,14 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_warp(const T *__restrict
         float o[V];
 #pragma unroll
         for (int j = 0; j < V; j++) o[j] = rstd * (gv[v][j] - (sum1 + xv[v][j] * sum2) / dim);
+        if (dx_add) {  // dx = dx_add + result (dx may alias dx_add: each element is read, then written, by one thread)
+          Vec16<T> u;
+          float e[V];
+          u.load(dx_add + r * dim + iv * V);
+          u.get(e);
+#pragma unroll
+          for (int j = 0; j < V; j++) o[j] += e[j];
+        }
         Vec16<T> t;
         t.set(o);
         t.store(dr + iv * V);
@@ -194,15 +202,25 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_warp(const T *__restrict
   }
 }
 
-// dw[c] (+)= sum_p part[p][0][c]; db[c] (+)= sum_p part[p][1][c]
+// dw[c] (+)= sum_p part[p][0][c]; db[c] (+)= sum_p part[p][1][c].  Block = 32 columns x 8 row
+// groups: each thread adds every 8th partial row of its column (independent loads), then the
+// 8 group sums are added in fixed order, so the result does not depend on scheduling.
 __global__ void __launch_bounds__(256) ln_reduce_partials(const float *__restrict__ part, float *dw, float *db,
                                                           int n_part, int dim, int accumulate) {
-  const int c = blockIdx.x * blockDim.x + threadIdx.x;
-  if (c >= 2 * dim) return;
+  __shared__ float sm[8][33];
+  const int c = blockIdx.x * 32 + threadIdx.x;
   float a = 0.f;
-  for (int p = 0; p < n_part; p++) a += part[(size_t)p * 2 * dim + c];
-  float *dst = c < dim ? dw + c : (db ? db + (c - dim) : nullptr);
-  if (dst) *dst = accumulate ? *dst + a : a;
+  if (c < 2 * dim)
+    for (int p = threadIdx.y; p < n_part; p += 8) a += part[(size_t)p * 2 * dim + c];
+  sm[threadIdx.y][threadIdx.x] = a;
+  __syncthreads();
+  if (threadIdx.y == 0 && c < 2 * dim) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < 8; k++) t += sm[k][threadIdx.x];
+    float *dst = c < dim ? dw + c : (db ? db + (c - dim) : nullptr);
+    if (dst) *dst = accumulate ? *dst + t : t;
+  }
 }
 
 // ── generic fallback (any dim / alignment): one block per row, scalar accesses ──────────
@@ -238,8 +256,8 @@ __global__ void __launch_bounds__(256) ln_fwd_block(const T *x, const float *w, 
 
 // dx per row; also stores (mean, rstd) per row for the column kernel.
 template <typename T, bool RMS>
-__global__ void __launch_bounds__(256) ln_bwd_block(const T *x, const float *w, const T *g, T *dx, float *stats,
-                                                    int64_t rows, int dim, float eps) {
+__global__ void __launch_bounds__(256) ln_bwd_block(const T *x, const float *w, const T *g, const T *dx_add, T *dx,
+                                                    float *stats, int64_t rows, int dim, float eps) {
   __shared__ float red[32];
   for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
     const T *xr = x + r * dim, *gr = g + r * dim;
@@ -274,7 +292,8 @@ __global__ void __launch_bounds__(256) ln_bwd_block(const T *x, const float *w, 
     for (int c = threadIdx.x; c < dim; c += blockDim.x) {
       const float xhat = (to_f32(xr[c]) - mean) * rstd;
       const float dy = to_f32(gr[c]) * w[c];
-      dx[r * dim + c] = from_f32<T>(rstd * (dy - (s1 + xhat * s2) / dim));
+      const float extra = dx_add ? to_f32(dx_add[r * dim + c]) : 0.f;
+      dx[r * dim + c] = from_f32<T>(rstd * (dy - (s1 + xhat * s2) / dim) + extra);
     }
     if (threadIdx.x == 0) {
       stats[2 * r] = mean;
@@ -326,8 +345,8 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
 }
 
 template <typename T, bool RMS>
-static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, alpha_buf db, int64_t rows,
-                    int64_t dim, float eps, int accumulate) {
+static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, alpha_buf dw, alpha_buf db,
+                    int64_t rows, int64_t dim, float eps, int accumulate) {
   if (dim == 0) return 0;
   if (rows == 0) {
     if (!accumulate) {
@@ -339,7 +358,8 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_b
   ProfScope prof(PROF_NORM, 3.0 * rows * dim * sizeof(T));
   constexpr int V = Vec16<T>::N;
   const size_t smem = (size_t)LN_WARPS * 2 * dim * sizeof(float);
-  const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && dim / V <= 32 * 8 &&
+  const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && (dx_add & 15) == 0 &&
+                    dim / V <= 32 * 8 &&
                     smem <= 48 * 1024;
   if (fast) {
     const int nv = (int)((dim / V + 31) / 32);
@@ -349,6 +369,7 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_b
 #define LN_BWD_CASE(NV)                                                                                    \
   case NV:                                                                                                 \
     ln_bwd_warp<T, NV, RMS><<<grid, LN_WARPS * 32, smem, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),   \
+                                                                     dx_add ? ptr<T>(dx_add) : nullptr,     \
                                                                      ptr<T>(dx), (float *)part, rows,       \
                                                                      (int)dim, eps);                        \
     break;
@@ -358,13 +379,14 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_b
     }
 #undef LN_BWD_CASE
     g_launches++;
-    ln_reduce_partials<<<(unsigned)((2 * dim + 255) / 256), 256, 0, g_stream>>>(
+    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, 8), 0, g_stream>>>(
         (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
     pool_free(part);
   } else {
     void *stats = nullptr;
     if (pool_alloc((size_t)rows * 2 * sizeof(float), &stats)) return 1;
-    ln_bwd_block<T, RMS><<<grid_for(rows, 1, 8), 256, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g), ptr<T>(dx),
+    ln_bwd_block<T, RMS><<<grid_for(rows, 1, 8), 256, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),
+                                                                     dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx),
                                                                      (float *)stats, rows, (int)dim, eps);
     g_launches++;
     ln_dwdb_cols<T><<<(unsigned)((dim + 127) / 128), 128, 0, g_stream>>>(ptr<T>(x), ptr<T>(g), (const float *)stats,
@@ -391,11 +413,11 @@ int alpha_layernorm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int6
 }
 
 int alpha_layernorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, alpha_buf db, int64_t rows,
-                        int64_t dim, float eps, int dtype, int accumulate) {
+                        int64_t dim, float eps, int dtype, int accumulate, alpha_buf dx_add) {
   ALPHA_REQUIRE_INIT();
   ALPHA_CHECK(dw != 0 && db != 0, "alpha_layernorm_bwd: dw and db are required");
-  if (dtype == ALPHA_F32) return norm_bwd<float, false>(x, w, g, dx, dw, db, rows, dim, eps, accumulate);
-  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, false>(x, w, g, dx, dw, db, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_F32) return norm_bwd<float, false>(x, w, g, dx_add, dx, dw, db, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, false>(x, w, g, dx_add, dx, dw, db, rows, dim, eps, accumulate);
   return set_error("alpha_layernorm_bwd: unsupported dtype %d", dtype);
 }
 
@@ -407,11 +429,11 @@ int alpha_rmsnorm_fwd(alpha_buf x, alpha_buf w, alpha_buf y, int64_t rows, int64
 }
 
 int alpha_rmsnorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw, int64_t rows, int64_t dim,
-                      float eps, int dtype, int accumulate) {
+                      float eps, int dtype, int accumulate, alpha_buf dx_add) {
   ALPHA_REQUIRE_INIT();
   ALPHA_CHECK(dw != 0, "alpha_rmsnorm_bwd: dw is required");
-  if (dtype == ALPHA_F32) return norm_bwd<float, true>(x, w, g, dx, dw, 0, rows, dim, eps, accumulate);
-  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, true>(x, w, g, dx, dw, 0, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_F32) return norm_bwd<float, true>(x, w, g, dx_add, dx, dw, 0, rows, dim, eps, accumulate);
+  if (dtype == ALPHA_BF16) return norm_bwd<__nv_bfloat16, true>(x, w, g, dx_add, dx, dw, 0, rows, dim, eps, accumulate);
   return set_error("alpha_rmsnorm_bwd: unsupported dtype %d", dtype);
 }
 

@@ -233,8 +233,7 @@ def _block_fused(ctx: Ctx, cfg: ModelConfig, x: Variable, P: GPTParams, i: int, 
         gate = ag.linear(ctx, ln2, P[f"{pre}.mlp.fc_gate"])
         up = ag.linear(ctx, ln2, P[f"{pre}.mlp.fc_up"])
         return ag.linearAdd(ctx, ag.siluMul(ctx, gate, up), P[f"{pre}.mlp.fc_proj"], x)
-    h = ag.linearGelu(ctx, ln2, P[f"{pre}.mlp.fc1"])
-    return ag.linearAdd(ctx, h, P[f"{pre}.mlp.fc2"], x)
+    return ag.mlpGelu(ctx, ln2, P[f"{pre}.mlp.fc1"], P[f"{pre}.mlp.fc2"], x)
 
 
 def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: Tape, tokens: TensorData,

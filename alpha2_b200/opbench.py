@@ -78,14 +78,16 @@ class Bench:
 
 
 def gemm_case(b: Bench, layout: str, M: int, N: int, K: int, out_dtype: str = "bf16", epilogue: int = L.EPI_NONE):
+    """Operands are allocated with leading dimensions padded to a multiple of 64 elements (as
+    the train step lays out the logits), the logical extents stay M, N, K."""
     B = b.B
-    shapes = {"nt": ((M, K), (N, K)), "nn": ((M, K), (K, N)), "tn": ((K, M), (K, N))}[layout]
-    A, Bm = b.normal(shapes[0], 0.02), b.normal(shapes[1], 0.02)
-    ldc = (N + 63) // 64 * 64
+    pad = lambda n: (n + 63) // 64 * 64
+    logical = {"nt": ((M, K), (N, K)), "nn": ((M, K), (K, N)), "tn": ((K, M), (K, N))}[layout]
+    lda, ldb, ldc = pad(logical[0][1]), pad(logical[1][1]), pad(N)
+    A, Bm = b.normal((logical[0][0], lda), 0.02), b.normal((logical[1][0], ldb), 0.02)
     Cc = B._new((M, ldc), out_dtype)
     aux = B._new((M, ldc), out_dtype) if epilogue != L.EPI_NONE else None
     code = {"nt": L.GEMM_NT, "nn": L.GEMM_NN, "tn": L.GEMM_TN}[layout]
-    lda, ldb = shapes[0][1], shapes[1][1]
 
     def fn():
         check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cc.ptr, M, N, K, lda, ldb, ldc, L.BF16, L.DTYPE_CODE[out_dtype],
@@ -162,7 +164,7 @@ CASES = {
     "gemm_dw_qkv": lambda b: gemm_case(b, "tn", 2304, 768, M, "f32"),
     "gemm_dw_fc1": lambda b: gemm_case(b, "tn", 3072, 768, M, "f32"),
     "gemm_dw_fc2": lambda b: gemm_case(b, "tn", 768, 3072, M, "f32"),
-    "gemm_dw_head": lambda b: gemm_case(b, "tn", 50304, 768, M, "f32"),
+    "gemm_dw_head": lambda b: gemm_case(b, "tn", 50257, 768, M, "f32"),
     "attn_fwd": lambda b: attn_case(b),
     "attn_bwd": lambda b: attn_case(b, backward=True),
     "softmax_ce": lambda b: ce_case(b),

@@ -190,13 +190,17 @@ int alpha_embedding_bwd(alpha_buf indices, alpha_buf grad, alpha_buf dw, int64_t
  * asked for by the 350M configuration): y = x * rsqrt(mean(x^2)+eps) * w. */
 int alpha_layernorm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows,
                         int64_t dim, float eps, int dtype);
+/* dx_add: 0, or a tensor shaped like x that is added to the result (dx = dx_add + ...; dx may
+ * alias dx_add) — the residual stream's gradient is accumulated in the same pass instead of
+ * by a separate addInplace (packages/autograd/src/tape.ts:116-127 does the latter). */
 int alpha_layernorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw,
                         alpha_buf db, int64_t rows, int64_t dim, float eps, int dtype,
-                        int accumulate_dwdb);
+                        int accumulate_dwdb, alpha_buf dx_add);
 int alpha_rmsnorm_fwd(alpha_buf x, alpha_buf w, alpha_buf y, int64_t rows, int64_t dim,
                       float eps, int dtype);
 int alpha_rmsnorm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx, alpha_buf dw,
-                      int64_t rows, int64_t dim, float eps, int dtype, int accumulate_dw);
+                      int64_t rows, int64_t dim, float eps, int dtype, int accumulate_dw,
+                      alpha_buf dx_add);
 
 /* ── GEMM ────────────────────────────────────────────────────────────────────────────
  * Backend.matmul (interfaces.ts:53; cpu_ref.ts:166-258), matmulTransposed (:111) and

@@ -118,6 +118,9 @@ class NumpyBackend:
     def matmulTransposedAdd(self, a, b, r):
         return self._o(r.data + a.data.astype(f64) @ b.data.astype(f64).T)
 
+    def matmulGeluBackward(self, g, w, pre):
+        return self._o((g.data.astype(f64) @ w.data.astype(f64)) * _gelu_grad(pre.data.astype(f64)))
+
     # reductions
     def sum(self, a, axis=None, keepdims=False):
         return self._o(np.sum(a.data.astype(f64), axis=axis, keepdims=keepdims))
@@ -140,6 +143,10 @@ class NumpyBackend:
     def embeddingBackward(self, idx, g, vocab, out=None):
         dw = np.zeros((vocab, g.shape[-1]), f64)
         np.add.at(dw, idx.data.reshape(-1), g.data.reshape(-1, g.shape[-1]).astype(f64))
+        if out is not None:
+            self.ops += 1
+            out._host = (out.data.astype(f64) + dw).astype(f32)
+            return out
         return self._o(dw)
 
     def _ln_stats(self, x, eps, rms):
@@ -152,7 +159,7 @@ class NumpyBackend:
         m, r = self._ln_stats(X, eps, False)
         return self._o((X - m) * r * w.data + b.data)
 
-    def layerNormBackward(self, x, w, g, eps, rms=False):
+    def layerNormBackward(self, x, w, g, eps, dxInto=None, rms=False):
         X, G = x.data.astype(f64), g.data.astype(f64)
         dim = X.shape[-1]
         m, r = self._ln_stats(X, eps, rms)
@@ -161,6 +168,11 @@ class NumpyBackend:
         s1 = 0.0 if rms else dy.sum(-1, keepdims=True)
         s2 = (dy * xhat).sum(-1, keepdims=True)
         dx = r * (dy - (s1 + xhat * s2) / dim)
+        if dxInto is not None:
+            self.ops += 1
+            dxInto._host = (dxInto.data.astype(f64) + dx).astype(f32)
+            return {"dx": dxInto, "dw": self._o((G * xhat).reshape(-1, dim).sum(0)),
+                    "db": self._o(G.reshape(-1, dim).sum(0))}
         return {"dx": self._o(dx), "dw": self._o((G * xhat).reshape(-1, dim).sum(0)),
                 "db": self._o(G.reshape(-1, dim).sum(0))}
 
@@ -169,8 +181,8 @@ class NumpyBackend:
         _, r = self._ln_stats(X, eps, True)
         return self._o(X * r * w.data)
 
-    def rmsNormBackward(self, x, w, g, eps):
-        r = self.layerNormBackward(x, w, g, eps, rms=True)
+    def rmsNormBackward(self, x, w, g, eps, dxInto=None):
+        r = self.layerNormBackward(x, w, g, eps, dxInto, rms=True)
         return {"dx": r["dx"], "dw": r["dw"]}
 
     def rope(self, x, batch, Tn, heads, D, ld, col_offset=0, theta=10000.0, inverse=False):
