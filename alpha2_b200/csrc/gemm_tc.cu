@@ -44,14 +44,30 @@ struct GemmTcArgs {
   int tiles_m, tiles_n, splits, kb_per_split, kblocks;
   int out_f32;           // 1: C is fp32, 0: bf16
   int epilogue, accumulate;
+  int tma_epi;           // 1: outputs (and epilogue operands) move through shared memory with TMA
   uint32_t *err;
 };
+
+// tanh-approximation GELU with the hardware tanh (MUFU): the epilogues run on bf16 data, whose
+// resolution (2^-8) is far coarser than tanh.approx's error.
+__device__ __forceinline__ float gelu_fast(float x) {
+  const float c = 0.7978845608028654f;
+  return 0.5f * x * (1.f + tc::tanh_approx(c * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float gelu_grad_fast(float x) {
+  const float c = 0.7978845608028654f;
+  const float t = tc::tanh_approx(c * (x + 0.044715f * x * x * x));
+  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * x * x);
+}
 
 template <int BN>
 struct GemmSmemLayout {
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_BYTES = BN * GBK * 2;
-  static constexpr int BAR_OFF = GSTAGES * (A_BYTES + B_BYTES);
+  // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), 128B-swizzled TMA boxes
+  static constexpr int STAGE_OFF = GSTAGES * (A_BYTES + B_BYTES);
+  static constexpr int STAGE_BYTES = 4 * 2 * 4096;
+  static constexpr int BAR_OFF = STAGE_OFF + STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256;  // barriers + tmem base + abort flag
   static constexpr int DYN = TOTAL + 1024;     // slack to align the base to 1024 B
 };
@@ -152,9 +168,96 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmTcArgs &g, const 
   }
 }
 
+// Epilogue of one 128 x BN tile for one warp (32 accumulator rows) through shared memory.
+// Direct register->global stores make every lane write its own row, 32 cache lines per
+// instruction, and were measured to cost a third of the kernel on the K = 768 shapes; here
+// each warp stages 32 rows x 128 bytes in a 128B-swizzled buffer (conflict-free 16-byte
+// writes) and one lane hands the box to the TMA unit, which writes full lines and clips at
+// the matrix edge.  Epilogue operands (residual, saved pre-activation) arrive the same way
+// by a TMA load into the buffer the result will leave from.  Two buffers per warp: they
+// alternate (plain / ADD / GELU') or hold the pre-activation and the activation (GELU).
+template <typename OutT, int BN>
+__device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUtensorMap *tmap_c,
+                                                  const CUtensorMap *tmap_aux, uint32_t t_row, int row0, int n0,
+                                                  int lane, uint8_t *stage, uint32_t stage_u32, uint32_t aux_bar,
+                                                  uint32_t &aux_phase, uint32_t &chunk_count,
+                                                  volatile uint32_t *abort_flag) {
+  constexpr int CH = 128 / (int)sizeof(OutT);  // columns per staged chunk (64 bf16 / 32 f32)
+  constexpr int V = Vec16<OutT>::N;
+  const bool gelu = g.epilogue == ALPHA_EPI_GELU;
+  const bool has_in = g.epilogue == ALPHA_EPI_ADD || g.epilogue == ALPHA_EPI_GELU_BWD;
+  const uint32_t sw = (uint32_t)(lane & 7);
+#pragma unroll 1
+  for (int c = 0; c < BN / CH; c++) {
+    const int col0 = n0 + c * CH;
+    if (col0 >= g.N) break;  // warp-uniform
+    const int buf = gelu ? 1 : (int)(chunk_count & 1);
+    chunk_count++;
+    if (lane == 0) {  // the buffer(s) about to be written must have been read out by their last store
+      if (gelu) bulk_wait_read<0>(); else bulk_wait_read<1>();
+    }
+    __syncwarp();
+    uint8_t *bp = stage + buf * 4096 + lane * 128;
+    const uint32_t bu = stage_u32 + buf * 4096;
+    if (has_in && lane == 0) {
+      mbar_expect_tx(aux_bar, 4096);
+      tma_load_2d(bu, tmap_aux, aux_bar, col0, row0);
+    }
+    float v[CH];
+#pragma unroll
+    for (int k = 0; k < CH / 32; k++) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c * CH + k * 32, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int i = 0; i < 32; i++) v[k * 32 + i] = __uint_as_float(r[i]);
+    }
+    if (has_in) {
+      if (!mbar_wait(aux_bar, aux_phase, abort_flag)) return false;
+      aux_phase ^= 1;
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        Vec16<OutT> t;
+        float x[V];
+        t.load(reinterpret_cast<const OutT *>(bp + ((q ^ sw) << 4)));
+        t.get(x);
+#pragma unroll
+        for (int j = 0; j < V; j++)
+          v[q * V + j] = g.epilogue == ALPHA_EPI_ADD ? v[q * V + j] + x[j] : v[q * V + j] * gelu_grad_fast(x[j]);
+      }
+    }
+    if (gelu) {  // buffer 0 takes the pre-activation, buffer 1 the activation
+      uint8_t *ap = stage + lane * 128;
+#pragma unroll
+      for (int q = 0; q < 8; q++) {
+        Vec16<OutT> t;
+        t.set(&v[q * V]);
+        t.store(reinterpret_cast<OutT *>(ap + ((q ^ sw) << 4)));
+      }
+#pragma unroll
+      for (int j = 0; j < CH; j++) v[j] = gelu_fast(v[j]);
+    }
+#pragma unroll
+    for (int q = 0; q < 8; q++) {
+      Vec16<OutT> t;
+      t.set(&v[q * V]);
+      t.store(reinterpret_cast<OutT *>(bp + ((q ^ sw) << 4)));
+    }
+    fence_proxy_async();
+    __syncwarp();
+    if (lane == 0) {
+      if (gelu) tma_store_2d(tmap_aux, stage_u32, col0, row0);
+      tma_store_2d(tmap_c, bu, col0, row0);
+      bulk_commit();
+    }
+  }
+  return true;
+}
+
 template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b, GemmTcArgs g) {
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, GemmTcArgs g) {
   using L = GemmSmemLayout<BN>;
   extern __shared__ uint8_t smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -167,7 +270,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   auto empty_bar = [&](int s) { return bar_base + 8u * (GSTAGES + s); };
   auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * GSTAGES + s); };
   auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * GSTAGES + 2 + s); };
-  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * GSTAGES + 4));
+  auto aux_bar = [&](int q) { return bar_base + 8u * (2 * GSTAGES + 4 + q); };  // one per epilogue warp
+  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * GSTAGES + 8));
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -178,6 +282,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
+    for (int q = 0; q < 4; q++) mbar_init(aux_bar(q), 1);
     for (int s = 0; s < 2; s++) {
       mbar_init(tfull_bar(s), 1);
       mbar_init(tempty_bar(s), 4);
@@ -275,6 +380,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
     const int quad = warp & 3;  // the TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
+    uint8_t *stage = smem + L::STAGE_OFF + quad * 8192;
+    const uint32_t stage_u32 = smem_base + L::STAGE_OFF + quad * 8192;
+    uint32_t aux_phase = 0, chunk_count = 0;
+    if (g.tma_epi && lane == 0) {
+      tma_prefetch_desc(&tmap_c);
+      if (g.epilogue != ALPHA_EPI_NONE) tma_prefetch_desc(&tmap_aux);
+    }
     for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
       int split, mt, nt;
       tile_coords(g, tile, split, mt, nt);
@@ -287,6 +399,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       const int64_t row = (int64_t)m0 + row_in_tile;
       const bool row_ok = row < g.M;
       const uint32_t t_row = tmem_base + acc * BN + ((uint32_t)(quad * 32) << 16);
+      if (g.tma_epi) {
+        const int row0 = m0 + quad * 32;
+        if (row0 < g.M) {  // warp-uniform: a quadrant entirely below the matrix has nothing to store
+          ok = g.out_f32 ? epilogue_tile_tma<float, BN>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage, stage_u32,
+                                                        aux_bar(quad), aux_phase, chunk_count, abort_flag)
+                         : epilogue_tile_tma<__nv_bfloat16, BN>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
+                                                                stage_u32, aux_bar(quad), aux_phase, chunk_count,
+                                                                abort_flag);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        continue;
+      }
       GemmTcArgs gl = g;
       if (g.splits > 1) gl.C = (float *)g.C + (int64_t)split * g.M * g.N;  // workspace slab, ldc = N
 #pragma unroll 1
@@ -305,6 +431,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       __syncwarp();
       if (lane == 0) mbar_arrive(tempty_bar(acc));
     }
+    if (g.tma_epi && lane == 0) bulk_wait<0>();  // all stores have left shared memory and landed
   }
 
   // ── teardown ─────────────────────────────────────────────────────────────
@@ -374,15 +501,31 @@ static int get_tmap(CUtensorMap *out, const void *base, uint64_t inner, uint64_t
   return 0;
 }
 
+static int get_tmap_out(CUtensorMap *out, const void *base, int dtype, uint64_t inner, uint64_t outer, uint64_t ld) {
+  // key: box_inner carries the dtype (64 bf16 / 32 f32 columns), box_outer = 32 rows marks an output map
+  TmapKey key{(uint64_t)(uintptr_t)base, inner, outer, ld, dtype == ALPHA_F32 ? 32u : 64u, 32u};
+  std::lock_guard<std::mutex> lk(g_tmap_mu);
+  auto it = g_tmaps.find(key);
+  if (it != g_tmaps.end()) {
+    *out = it->second;
+    return 0;
+  }
+  if (encode_tmap_2d_out(out, base, dtype, inner, outer, ld, 32)) return 1;
+  if (g_tmaps.size() > 4096) g_tmaps.clear();
+  g_tmaps[key] = *out;
+  return 0;
+}
+
 template <int BN, bool A_MN, bool B_MN>
-static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const GemmTcArgs &g, int grid) {
+static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_, const CUtensorMap &tx,
+                          const GemmTcArgs &g, int grid) {
   using L = GemmSmemLayout<BN>;
   static bool attr = false;
   if (!attr) {
     ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     attr = true;
   }
-  gemm_tc_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, g);
+  gemm_tc_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -438,12 +581,26 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
     g.aux_in = ptr<void>(aux); g.aux_out = ptr<void>(aux); g.ld_aux = ld_aux;
     if (epilogue != ALPHA_EPI_NONE) ALPHA_CHECK(aux != 0, "alpha_gemm: epilogue %d needs an aux buffer", epilogue);
   }
+  // Outputs leave through shared memory + TMA stores when the layout allows a tensor map
+  // (16-byte aligned base and rows) and nothing has to be read back from C.
+  CUtensorMap tcm, txm;
+  memset(&tcm, 0, sizeof(tcm));
+  memset(&txm, 0, sizeof(txm));
+  const size_t oes = dtype_size(out_dtype);
+  g.tma_epi = 0;
+  if (splits == 1 && !accumulate && (C & 15) == 0 && (ldc * oes) % 16 == 0 &&
+      (epilogue == ALPHA_EPI_NONE || ((aux & 15) == 0 && (ld_aux * oes) % 16 == 0))) {
+    if (get_tmap_out(&tcm, ptr<void>(C), out_dtype, N, M, ldc)) return 1;
+    if (epilogue != ALPHA_EPI_NONE && get_tmap_out(&txm, ptr<void>(aux), out_dtype, N, M, ld_aux)) return 1;
+    g.tma_epi = 1;
+  }
   const int total = tiles * splits;
   const int grid = total < g_sm_count ? total : g_sm_count;
   int rc;
-#define GEMM_VARIANT(BNV)                                                                     \
-  (a_mn ? launch_variant<BNV, true, true>(ta, tb, g, grid)                                    \
-        : (b_mn ? launch_variant<BNV, false, true>(ta, tb, g, grid) : launch_variant<BNV, false, false>(ta, tb, g, grid)))
+#define GEMM_VARIANT(BNV)                                                                               \
+  (a_mn ? launch_variant<BNV, true, true>(ta, tb, tcm, txm, g, grid)                                    \
+        : (b_mn ? launch_variant<BNV, false, true>(ta, tb, tcm, txm, g, grid)                           \
+                : launch_variant<BNV, false, false>(ta, tb, tcm, txm, g, grid)))
   rc = BN == 256 ? GEMM_VARIANT(256) : GEMM_VARIANT(128);
 #undef GEMM_VARIANT
   if (rc == 0 && splits > 1) {

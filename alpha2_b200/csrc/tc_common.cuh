@@ -85,6 +85,24 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 2-D tiled TMA store shared -> global (bulk-group completion).  Elements outside the
+// tensor's extents are not written.  x follows the same 16-byte rule as loads and must not
+// be negative.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t src, int32_t x, int32_t y) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];"
+               ::"l"(map), "r"(src), "r"(x), "r"(y)
+               : "memory");
+}
+__device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until at most N of this thread's bulk groups still have to *read* their source.
+template <int N>
+__device__ __forceinline__ void bulk_wait_read() {
+  asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory");
+}
+template <int N>
+__device__ __forceinline__ void bulk_wait() {
+  asm volatile("cp.async.bulk.wait_group %0;" ::"n"(N) : "memory");
+}
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm volatile("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -183,6 +201,10 @@ __host__ __device__ constexpr uint32_t make_idesc_bf16(int M, int N, bool a_mn_m
 //   inner/outer: extents in elements; ld_elems: elements between consecutive outer indices.
 int encode_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t inner, uint64_t outer, uint64_t ld_elems,
                         uint32_t box_inner, uint32_t box_outer);
+// 2-D map of an output / epilogue-operand matrix (bf16 or f32), 128-byte swizzle; the
+// inner box must span exactly 128 bytes.
+int encode_tmap_2d_out(CUtensorMap *out, const void *base, int dtype, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                       uint32_t box_outer);
 int encode_tmap_3d_bf16(CUtensorMap *out, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1_elems,
                         uint64_t ld2_elems, uint32_t box0, uint32_t box1, uint32_t box2);
 

@@ -50,6 +50,24 @@ int encode_tmap_2d_bf16(CUtensorMap *out, const void *base, uint64_t inner, uint
   return 0;
 }
 
+int encode_tmap_2d_out(CUtensorMap *out, const void *base, int dtype, uint64_t inner, uint64_t outer, uint64_t ld_elems,
+                       uint32_t box_outer) {
+  EncodeTiledFn enc = get_encode();
+  if (!enc) return set_error("tensor map: cuTensorMapEncodeTiled is not available from this driver");
+  const uint64_t es = dtype == ALPHA_F32 ? 4 : 2;
+  if (((uintptr_t)base & 15) != 0 || (ld_elems * es) % 16 != 0)
+    return set_error("tensor map: output base / leading dimension not 16-byte aligned");
+  cuuint64_t dims[2] = {inner, outer};
+  cuuint64_t strides[1] = {ld_elems * es};
+  cuuint32_t box[2] = {(cuuint32_t)(128 / es), box_outer};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(out, dtype == ALPHA_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2,
+                   const_cast<void *>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return set_error("cuTensorMapEncodeTiled (output) failed (%d)", (int)r);
+  return 0;
+}
+
 int encode_tmap_3d_bf16(CUtensorMap *out, const void *base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t ld1_elems,
                         uint64_t ld2_elems, uint32_t box0, uint32_t box1, uint32_t box2) {
   EncodeTiledFn enc = get_encode();
