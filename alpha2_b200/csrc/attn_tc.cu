@@ -298,21 +298,36 @@ struct AttnBwdArgs {
   uint32_t *err;
 };
 
-// delta[bh*T + t] = sum_d dO[t,d] * O[t,d]; one warp per row (64 elements, 2 per lane)
+// delta[bh*T + t] = sum_d dO[t,d] * O[t,d]; eight threads per row (64 elements), one 16-byte
+// load of O and of dO each, shuffle-sum inside the group of eight; rows are walked grid-stride
+// so that many loads are in flight per SM.
 __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 *__restrict__ o,
                                                             const __nv_bfloat16 *__restrict__ d_o, float *delta,
                                                             int64_t o_sb, int64_t o_sh, int64_t o_st, int H, int T,
                                                             int64_t rows) {
-  const int lane = threadIdx.x & 31;
-  for (int64_t r = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5); r < rows; r += (int64_t)gridDim.x * 8) {
-    const int64_t bh = r / T;
-    const int t = (int)(r - bh * T);
-    const int b = (int)(bh / H), h = (int)(bh - (int64_t)b * H);
-    const int64_t off = b * o_sb + h * o_sh + (int64_t)t * o_st + lane * 2;
-    const float2 x = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(o + off));
-    const float2 y = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(d_o + off));
-    const float s = warp_sum(x.x * y.x + x.y * y.y);
-    if (lane == 0) delta[r] = s;
+  const int sub = threadIdx.x & 7;
+  const int64_t stride = (int64_t)gridDim.x * 32;
+  for (int64_t r0 = (int64_t)blockIdx.x * 32; r0 < rows; r0 += stride) {  // warp-uniform trip count
+    const int64_t r = r0 + (threadIdx.x >> 3);
+    float s = 0.f;
+    if (r < rows) {
+      const int64_t bh = r / T;
+      const int t = (int)(r - bh * T);
+      const int b = (int)(bh / H), h = (int)(bh - (int64_t)b * H);
+      const int64_t off = b * o_sb + h * o_sh + (int64_t)t * o_st + sub * 8;
+      Vec16<__nv_bfloat16> vo, vd;
+      vo.load(o + off);
+      vd.load(d_o + off);
+      float x[8], y[8];
+      vo.get(x);
+      vd.get(y);
+#pragma unroll
+      for (int i = 0; i < 8; i++) s += x[i] * y[i];
+    }
+    s += __shfl_xor_sync(0xffffffffu, s, 4);
+    s += __shfl_xor_sync(0xffffffffu, s, 2);
+    s += __shfl_xor_sync(0xffffffffu, s, 1);
+    if (sub == 0 && r < rows) delta[r] = s;
   }
 }
 
@@ -767,7 +782,7 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   const int64_t rows = p->batch * p->heads * p->T;
   void *delta = nullptr;
   if (pool_alloc((size_t)rows * sizeof(float), &delta)) return 1;
-  attn_tc_delta_kernel<<<grid_for(rows, 8, 8), 256, 0, g_stream>>>(ptr<__nv_bfloat16>(o), ptr<__nv_bfloat16>(d_o),
+  attn_tc_delta_kernel<<<grid_for(rows, 32, 16), 256, 0, g_stream>>>(ptr<__nv_bfloat16>(o), ptr<__nv_bfloat16>(d_o),
                                                                     (float *)delta, p->o_sb, p->o_sh, p->o_st,
                                                                     (int)p->heads, (int)p->T, rows);
   g_launches++;

@@ -187,6 +187,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   const bool gelu = g.epilogue == ALPHA_EPI_GELU;
   const bool has_in = g.epilogue == ALPHA_EPI_ADD || g.epilogue == ALPHA_EPI_GELU_BWD;
   const uint32_t sw = (uint32_t)(lane & 7);
+  const uint64_t policy = l2_policy_evict_first();
 #pragma unroll 1
   for (int c = 0; c < BN / CH; c++) {
     const int col0 = n0 + c * CH;
@@ -246,8 +247,8 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
     fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
-      if (gelu) tma_store_2d(tmap_aux, stage_u32, col0, row0);
-      tma_store_2d(tmap_c, bu, col0, row0);
+      if (gelu) tma_store_2d_hint(tmap_aux, stage_u32, col0, row0, policy);
+      tma_store_2d_hint(tmap_c, bu, col0, row0, policy);
       bulk_commit();
     }
   }
@@ -451,12 +452,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
 }
 
-// C (+)= sum_s ws[s]  — split order is fixed, so the result is reproducible.
+// C (+)= sum_s ws[s]  — split order is fixed, so the result is reproducible.  ws holds
+// `splits` dense [M, N] fp32 slabs; four columns per thread when the rows allow it.
 template <typename OutT>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restrict__ ws, OutT *C, int64_t M, int64_t N,
-                                                            int64_t ldc, int splits, int accumulate) {
+                                                            int64_t ldc, int splits, int accumulate, int vec4) {
   const int64_t total = M * N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  if (vec4) {
+    const int64_t n4 = total / 4;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+      float4 s = reinterpret_cast<const float4 *>(ws)[i];
+      for (int k = 1; k < splits; k++) {
+        const float4 t = reinterpret_cast<const float4 *>(ws + (int64_t)k * total)[i];
+        s.x += t.x; s.y += t.y; s.z += t.z; s.w += t.w;
+      }
+      const int64_t e = i * 4, m = e / N, n = e - m * N;
+      OutT *dst = C + m * ldc + n;
+      float o[4] = {s.x, s.y, s.z, s.w};
+#pragma unroll
+      for (int j = 0; j < 4; j++) dst[j] = from_f32<OutT>(accumulate ? to_f32(dst[j]) + o[j] : o[j]);
+    }
+    return;
+  }
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += stride) {
     float s = 0.f;
     for (int k = 0; k < splits; k++) s += ws[(int64_t)k * total + i];
@@ -604,13 +622,14 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   rc = BN == 256 ? GEMM_VARIANT(256) : GEMM_VARIANT(128);
 #undef GEMM_VARIANT
   if (rc == 0 && splits > 1) {
-    const int rgrid = grid_for(M * N, 256, 8);
+    const int vec4 = (N % 4 == 0) ? 1 : 0;   // ws slabs are 512-byte aligned and dense
+    const int rgrid = grid_for(M * N / (vec4 ? 4 : 1) + 1, 256, 8);
     if (out_dtype == ALPHA_F32)
       splitk_reduce_kernel<float><<<rgrid, 256, 0, g_stream>>>((const float *)ws, ptr<float>(C), M, N, ldc, splits,
-                                                               accumulate);
+                                                               accumulate, vec4);
     else
       splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, g_stream>>>((const float *)ws, ptr<__nv_bfloat16>(C), M, N,
-                                                                       ldc, splits, accumulate);
+                                                                       ldc, splits, accumulate, vec4);
     g_launches++;
   }
   if (ws) pool_free(ws);

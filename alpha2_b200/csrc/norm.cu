@@ -223,6 +223,214 @@ __global__ void __launch_bounds__(256) ln_reduce_partials(const float *__restric
   }
 }
 
+// ── one CTA per row (the fast path) ─────────────────────────────────────────────────────
+// 128 threads walk rows; thread t owns the 16-byte column vectors t and t+128 of every row, so
+// its slice of the weight / bias (and, backward, of the dw / db sums) stays in registers
+// for the whole kernel and only the row itself moves: ~40 registers per thread, twelve or
+// more CTAs per SM, every access a fully coalesced 16-byte load or store.  Row statistics
+// are block reductions (warp shuffle + 4 partials in shared memory, one __syncthreads each,
+// slots alternate between rows so no second barrier is needed).
+constexpr int LN_CTA = 128;
+
+// sum over the block; slot is a 4-float shared array private to this reduction instance
+__device__ __forceinline__ float cta_sum4(float v, float *slot) {
+  v = warp_sum(v);
+  if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+  __syncthreads();
+  return (slot[0] + slot[1]) + (slot[2] + slot[3]);
+}
+
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(LN_CTA) ln_fwd_cta(const T *__restrict__ x, const float *__restrict__ w,
+                                                     const float *__restrict__ b, T *__restrict__ y, int64_t rows,
+                                                     int dim, float eps) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[2][2][4];
+  const int nvec = dim / V;
+  float wv[NV][V], bv[NV][V];
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int iv = v * LN_CTA + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < V; j += 4) {
+      const float4 a = iv < nvec ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
+      const float4 c = (!RMS && iv < nvec) ? *reinterpret_cast<const float4 *>(b + iv * V + j) : make_float4(0, 0, 0, 0);
+      wv[v][j] = a.x; wv[v][j + 1] = a.y; wv[v][j + 2] = a.z; wv[v][j + 3] = a.w;
+      bv[v][j] = c.x; bv[v][j + 1] = c.y; bv[v][j + 2] = c.z; bv[v][j + 3] = c.w;
+    }
+  }
+  int par = 0;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
+    float xv[NV][V];
+    const T *xr = x + r * dim;
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * LN_CTA + threadIdx.x;
+      if (iv < nvec) {
+        Vec16<T> t;
+        t.load(xr + iv * V);
+        t.get(xv[v]);
+#pragma unroll
+        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+      }
+    }
+    s = cta_sum4(s, red[par][0]);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+        if (v * LN_CTA + threadIdx.x < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            const float d = xv[v][j] - mean;
+            q += d * d;
+          }
+        }
+      q = cta_sum4(q, red[par][1]);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    T *yr = y + r * dim;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * LN_CTA + threadIdx.x;
+      if (iv < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) o[j] = (xv[v][j] - mean) * rstd * wv[v][j] + bv[v][j];
+        Vec16<T> t;
+        t.set(o);
+        t.store(yr + iv * V);
+      }
+    }
+  }
+}
+
+// part: [gridDim.x][2][dim] f32 partial column sums (dw, db), written once per CTA.
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, const float *__restrict__ w,
+                                                     const T *__restrict__ g, const T *dx_add, T *dx,
+                                                     float *__restrict__ part, int64_t rows, int dim, float eps) {
+  constexpr int V = Vec16<T>::N;
+  __shared__ float red[2][4][4];
+  const int nvec = dim / V;
+  float wv[NV][V], dw_acc[NV][V], db_acc[NV][V];
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int iv = v * LN_CTA + threadIdx.x;
+#pragma unroll
+    for (int j = 0; j < V; j += 4) {
+      const float4 a = iv < nvec ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
+      wv[v][j] = a.x; wv[v][j + 1] = a.y; wv[v][j + 2] = a.z; wv[v][j + 3] = a.w;
+    }
+#pragma unroll
+    for (int j = 0; j < V; j++) dw_acc[v][j] = db_acc[v][j] = 0.f;
+  }
+  int par = 0;
+  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
+    float xv[NV][V], gv[NV][V];
+    const T *xr = x + r * dim, *gr = g + r * dim;
+    float s = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * LN_CTA + threadIdx.x;
+      if (iv < nvec) {
+        Vec16<T> t, u;
+        t.load(xr + iv * V);
+        u.load(gr + iv * V);
+        t.get(xv[v]);
+        u.get(gv[v]);
+#pragma unroll
+        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+      }
+    }
+    s = cta_sum4(s, red[par][0]);
+    float mean = 0.f, rstd;
+    if (RMS) {
+      rstd = rsqrtf(s / dim + eps);
+    } else {
+      mean = s / dim;
+      float q = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+        if (v * LN_CTA + threadIdx.x < nvec) {
+#pragma unroll
+          for (int j = 0; j < V; j++) {
+            const float d = xv[v][j] - mean;
+            q += d * d;
+          }
+        }
+      q = cta_sum4(q, red[par][1]);
+      rstd = 1.f / sqrtf(q / dim + eps);
+    }
+    float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < NV; v++)
+      if (v * LN_CTA + threadIdx.x < nvec) {
+#pragma unroll
+        for (int j = 0; j < V; j++) {
+          const float xhat = (xv[v][j] - mean) * rstd;
+          const float dy = gv[v][j] * wv[v][j];
+          dw_acc[v][j] += gv[v][j] * xhat;
+          db_acc[v][j] += gv[v][j];
+          s1 += dy;
+          s2 += dy * xhat;
+          xv[v][j] = xhat;
+          gv[v][j] = dy;
+        }
+      }
+    // the two sums share one barrier
+    s1 = warp_sum(s1);
+    s2 = warp_sum(s2);
+    if ((threadIdx.x & 31) == 0) {
+      red[par][2][threadIdx.x >> 5] = s1;
+      red[par][3][threadIdx.x >> 5] = s2;
+    }
+    __syncthreads();
+    s1 = RMS ? 0.f : (red[par][2][0] + red[par][2][1]) + (red[par][2][2] + red[par][2][3]);
+    s2 = (red[par][3][0] + red[par][3][1]) + (red[par][3][2] + red[par][3][3]);
+    T *dr = dx + r * dim;
+#pragma unroll
+    for (int v = 0; v < NV; v++) {
+      const int iv = v * LN_CTA + threadIdx.x;
+      if (iv < nvec) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) o[j] = rstd * (gv[v][j] - (s1 + xv[v][j] * s2) / dim);
+        if (dx_add) {
+          Vec16<T> u;
+          float e[V];
+          u.load(dx_add + r * dim + iv * V);
+          u.get(e);
+#pragma unroll
+          for (int j = 0; j < V; j++) o[j] += e[j];
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(dr + iv * V);
+      }
+    }
+  }
+  float *out = part + (size_t)blockIdx.x * 2 * dim;
+#pragma unroll
+  for (int v = 0; v < NV; v++) {
+    const int iv = v * LN_CTA + threadIdx.x;
+    if (iv < nvec) {
+#pragma unroll
+      for (int j = 0; j < V; j += 4) {
+        *reinterpret_cast<float4 *>(out + iv * V + j) =
+            make_float4(dw_acc[v][j], dw_acc[v][j + 1], dw_acc[v][j + 2], dw_acc[v][j + 3]);
+        *reinterpret_cast<float4 *>(out + dim + iv * V + j) =
+            make_float4(db_acc[v][j], db_acc[v][j + 1], db_acc[v][j + 2], db_acc[v][j + 3]);
+      }
+    }
+  }
+}
+
 // ── generic fallback (any dim / alignment): one block per row, scalar accesses ──────────
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) ln_fwd_block(const T *x, const float *w, const float *b, T *y, int64_t rows,
@@ -323,7 +531,15 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   ProfScope prof(PROF_NORM, 2.0 * rows * dim * sizeof(T));
   constexpr int V = Vec16<T>::N;
   const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
-  if (fast) {
+  if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
+    const int grid = grid_for(rows, 1, 12);
+    if (dim / V <= LN_CTA)
+      ln_fwd_cta<T, 1, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b), ptr<T>(y), rows,
+                                                            (int)dim, eps);
+    else
+      ln_fwd_cta<T, 2, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b), ptr<T>(y), rows,
+                                                            (int)dim, eps);
+  } else if (fast) {
     const int nv = (int)((dim / V + 31) / 32);
     const int grid = grid_for(rows, LN_WARPS, 16);
 #define LN_FWD_CASE(NV)                                                                                     \
@@ -361,7 +577,23 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
   const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && (dx_add & 15) == 0 &&
                     dim / V <= 32 * 8 &&
                     smem <= 48 * 1024;
-  if (fast) {
+  if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0) {
+    const int grid = grid_for(rows, 1, 6);
+    void *part = nullptr;
+    if (pool_alloc((size_t)grid * 2 * dim * sizeof(float), &part)) return 1;
+    if (dim / V <= LN_CTA)
+      ln_bwd_cta<T, 1, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),
+                                                            dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx),
+                                                            (float *)part, rows, (int)dim, eps);
+    else
+      ln_bwd_cta<T, 2, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),
+                                                            dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx),
+                                                            (float *)part, rows, (int)dim, eps);
+    g_launches++;
+    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, 8), 0, g_stream>>>(
+        (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
+    pool_free(part);
+  } else if (fast) {
     const int nv = (int)((dim / V + 31) / 32);
     int grid = grid_for(rows, LN_WARPS, 4);
     void *part = nullptr;

@@ -93,6 +93,20 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap *map, uint32_t sr
                ::"l"(map), "r"(src), "r"(x), "r"(y)
                : "memory");
 }
+// Same store with an L2 eviction-priority hint (policy from l2_policy_evict_first()): output
+// tiles are written once and not re-read by this kernel, so they should not displace the
+// operand tiles that other CTAs are about to fetch from L2.
+__device__ __forceinline__ uint64_t l2_policy_evict_first() {
+  uint64_t p;
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  return p;
+}
+__device__ __forceinline__ void tma_store_2d_hint(const CUtensorMap *map, uint32_t src, int32_t x, int32_t y,
+                                                  uint64_t policy) {
+  asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group.L2::cache_hint [%0, {%2, %3}], [%1], %4;"
+               ::"l"(map), "r"(src), "r"(x), "r"(y), "l"(policy)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
 // Waits until at most N of this thread's bulk groups still have to *read* their source.
 template <int N>
