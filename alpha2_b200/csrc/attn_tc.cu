@@ -17,7 +17,7 @@
 //              P -> bf16 -> 128B-swizzled shared memory; O is rescaled in TMEM only when the
 //              running max has moved by more than 2^8 (the stale max keeps P <= 2^8).
 // Two CTAs fit on an SM (96 KB shared memory, 256 TMEM columns each), so one CTA's softmax
-// overlaps the other's MMAs.  No cluster, no multicast.  Every wait is bounded.
+// overlaps the other's MMAs.  Single CTAs (no cluster).  Every wait is bounded.
 // Model work: forward 4*B*H*T^2*D flop (causal tiles are skipped, so about half is executed).
 #include <string.h>
 

@@ -10,14 +10,18 @@
 //
 // Shape of the kernel
 //   * persistent: one CTA per SM walks output tiles (grouped order for L2 reuse);
-//   * CTA tile 128 x BN (BN = 256 or 128), K step 64, 4-stage TMA ring;
+//   * pair form (the default for M > 128, N > 128): two CTAs of a cluster share a 256 x 256
+//     tile through tcgen05 cta_group::2 — each loads its 128 rows of A and 128 of the 256
+//     rows of B, so an SM fetches 32 KB per K step instead of 48 KB for the same tensor-core
+//     work (the single-CTA form is bound by what one SM can pull from L2), 6-stage ring;
+//   * single form: CTA tile 128 x BN (BN = 256 or 128), K step 64, 4-stage TMA ring;
 //   * warp 0 = TMA producer, warp 1 = MMA issuer (one elected lane), warps 2-5 = epilogue
 //     (one TMEM lane quadrant each);
 //   * two accumulators in tensor memory (2 x BN columns) so the epilogue of tile i overlaps
 //     the main loop of tile i+1;
 //   * operands may be K-major or MN-major (the transposed layouts are read in place through
 //     MN-major descriptors, nothing is transposed in memory);
-//   * no cluster, no multicast: every CTA issues its own TMA loads.
+//   * every CTA issues its own TMA loads (nothing is broadcast between CTAs);
 //   * split-K for the weight-gradient shapes (few output tiles, K = tokens): partial
 //     products go to an fp32 workspace and a second kernel adds them in split order.
 // Algorithmic work: 2*M*N*K flop; bytes (M*K + N*K)*2 + M*N*e_out.
@@ -32,7 +36,7 @@ namespace alpha {
 
 using namespace tc;
 
-constexpr int GBM = 128, GBK = 64, GSTAGES = 4;
+constexpr int GBM = 128, GBK = 64;
 constexpr int GEMM_THREADS = 192;
 
 struct GemmTcArgs {
@@ -60,12 +64,15 @@ __device__ __forceinline__ float gelu_grad_fast(float x) {
   return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * x * x);
 }
 
-template <int BN>
+// Per-CTA shared memory.  PAIR: the CTA holds 128 rows of A and BN/2 rows of B per stage.
+template <int BN, bool PAIR>
 struct GemmSmemLayout {
+  static constexpr int STAGES = PAIR ? 6 : 4;
   static constexpr int A_BYTES = GBM * GBK * 2;
-  static constexpr int B_BYTES = BN * GBK * 2;
+  static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
+  static constexpr int B_BYTES = B_ROWS * GBK * 2;
   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), 128B-swizzled TMA boxes
-  static constexpr int STAGE_OFF = GSTAGES * (A_BYTES + B_BYTES);
+  static constexpr int STAGE_OFF = STAGES * (A_BYTES + B_BYTES);
   static constexpr int STAGE_BYTES = 4 * 2 * 4096;
   static constexpr int BAR_OFF = STAGE_OFF + STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256;  // barriers + tmem base + abort flag
@@ -255,38 +262,46 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, GemmTcArgs g) {
-  using L = GemmSmemLayout<BN>;
+template <int BN, bool A_MN, bool B_MN, bool PAIR>
+__device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b,
+                                             const CUtensorMap &tmap_c, const CUtensorMap &tmap_aux,
+                                             const GemmTcArgs &g) {
+  using L = GemmSmemLayout<BN, PAIR>;
+  constexpr int STAGES = L::STAGES;
+  constexpr int TILE_M = PAIR ? 2 * GBM : GBM;  // rows of C per tile walker (CTA or CTA pair)
   extern __shared__ uint8_t smem_raw[];
+  // the pair's MMA addresses both CTAs' operands by one offset, so the aligned bases must
+  // sit at the same offset in both CTAs: the dynamic window starts at the same address in
+  // every CTA of a launch, hence so does its 1024-byte round-up
   uint8_t *smem = (uint8_t *)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t a_base = smem_base;
-  const uint32_t b_base = smem_base + GSTAGES * L::A_BYTES;
+  const uint32_t b_base = smem_base + STAGES * L::A_BYTES;
   const uint32_t bar_base = smem_base + L::BAR_OFF;
-  // barrier slots (8 bytes each): full[4], empty[4], tmem_full[2], tmem_empty[2]
+  // barrier slots (8 bytes each): full[S], empty[S], tmem_full[2], tmem_empty[2], aux[4]
   auto full_bar = [&](int s) { return bar_base + 8u * s; };
-  auto empty_bar = [&](int s) { return bar_base + 8u * (GSTAGES + s); };
-  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * GSTAGES + s); };
-  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * GSTAGES + 2 + s); };
-  auto aux_bar = [&](int q) { return bar_base + 8u * (2 * GSTAGES + 4 + q); };  // one per epilogue warp
-  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * GSTAGES + 8));
+  auto empty_bar = [&](int s) { return bar_base + 8u * (STAGES + s); };
+  auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
+  auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
+  auto aux_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 4 + q); };  // one per epilogue warp
+  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * STAGES + 8));
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr uint32_t TMEM_COLS = 2 * BN;
+  const uint32_t rank = PAIR ? cluster_ctarank() : 0u;  // 0 = the pair's leader
+  const int walker = PAIR ? (int)(blockIdx.x >> 1) : (int)blockIdx.x;
+  const int n_walkers = PAIR ? (int)(gridDim.x >> 1) : (int)gridDim.x;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < GSTAGES; s++) {
+    for (int s = 0; s < STAGES; s++) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
     for (int q = 0; q < 4; q++) mbar_init(aux_bar(q), 1);
     for (int s = 0; s < 2; s++) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), 4);
+      mbar_init(tempty_bar(s), PAIR ? 8 : 4);  // the leader's collects both CTAs' epilogue warps
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -298,56 +313,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // The pair's MMA writes both CTAs' tensor memory at one address, so both allocations must
+  // start at the same column; each CTA takes all 512 columns of its SM, which puts them at 0.
+  if (PAIR && (tmem_base & 0xFFFFu) != 0 && threadIdx.x == 0 && g.err) atomicExch(g.err, 0x6F000000u);
 
   const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
 
   if (warp == 0) {
-    // ── TMA producer ───────────────────────────────────────────────────────
+    // ── TMA producer (each CTA loads its own share) ────────────────────────
     if (lane == 0) {
       tma_prefetch_desc(&tmap_a);
       tma_prefetch_desc(&tmap_b);
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x) {
+      for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
         int split, mt, nt;
         tile_coords(g, tile, split, mt, nt);
-        const int m0 = mt * GBM, n0 = nt * BN;
+        const int m0 = mt * TILE_M + (int)rank * GBM;
+        const int n0 = nt * BN + (PAIR ? (int)rank * L::B_ROWS : 0);
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(g.kblocks, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          mbar_expect_tx(full_bar(stage), L::A_BYTES + L::B_BYTES);
+          // the leader's barrier counts the bytes of both CTAs
+          if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), (PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES));
+          const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
+          auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
+            if (PAIR) tma_load_2d_pair(dst, map, fb, x, y); else tma_load_2d(dst, map, fb, x, y);
+          };
           const uint32_t a_dst = a_base + stage * L::A_BYTES;
           const uint32_t b_dst = b_base + stage * L::B_BYTES;
           const int k0 = kb * GBK;
           if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < GBM / 64; i++) tma_load_2d(a_dst + i * 8192, &tmap_a, full_bar(stage), m0 + i * 64, k0);
+            for (int i = 0; i < GBM / 64; i++) load(a_dst + i * 8192, &tmap_a, m0 + i * 64, k0);
           } else {
-            tma_load_2d(a_dst, &tmap_a, full_bar(stage), k0, m0);
+            load(a_dst, &tmap_a, k0, m0);
           }
           if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < BN / 64; i++) tma_load_2d(b_dst + i * 8192, &tmap_b, full_bar(stage), n0 + i * 64, k0);
+            for (int i = 0; i < L::B_ROWS / 64; i++) load(b_dst + i * 8192, &tmap_b, n0 + i * 64, k0);
           } else {
-            tma_load_2d(b_dst, &tmap_b, full_bar(stage), k0, n0);
+            load(b_dst, &tmap_b, k0, n0);
           }
-          if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ── MMA issuer ─────────────────────────────────────────────────────────
-    if (lane == 0) {
-      constexpr uint32_t idesc = make_idesc_bf16(GBM, BN, A_MN, B_MN);
+    // ── MMA issuer (the leader's, for a pair) ──────────────────────────────
+    if (lane == 0 && rank == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(TILE_M, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
       int it = 0;
       bool ok = true;
-      for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
+      for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, it++) {
         int split, mt, nt;
         tile_coords(g, tile, split, mt, nt);
         const int kb0 = split * g.kb_per_split;
@@ -368,12 +393,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                         : make_smem_desc(a_s + k * 32, 16, 1024);
             const uint64_t bdesc = B_MN ? make_smem_desc(b_s + k * 2048, 8192, 1024)
                                         : make_smem_desc(b_s + k * 32, 16, 1024);
-            mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            if (PAIR) mma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            else mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
           }
-          mma_commit(empty_bar(stage));  // frees the stage once these MMAs have read it
-          if (++stage == GSTAGES) { stage = 0; phase ^= 1; }
+          // frees the stage (in both CTAs) once these MMAs have read it
+          if (PAIR) mma_commit_pair(empty_bar(stage)); else mma_commit(empty_bar(stage));
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
-        if (ok) mma_commit(tfull_bar(acc));  // accumulator complete
+        if (ok) {  // accumulator complete
+          if (PAIR) mma_commit_pair(tfull_bar(acc)); else mma_commit(tfull_bar(acc));
+        }
       }
     }
   } else {
@@ -388,10 +417,18 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
       tma_prefetch_desc(&tmap_c);
       if (g.epilogue != ALPHA_EPI_NONE) tma_prefetch_desc(&tmap_aux);
     }
-    for (int tile = blockIdx.x; tile < total_tiles && ok; tile += gridDim.x, it++) {
+    auto release_acc = [&](int acc) {  // this warp has read its accumulator rows
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) {
+        if (PAIR && rank != 0) mbar_arrive_cluster(map_to_cta(tempty_bar(acc), 0));
+        else mbar_arrive(tempty_bar(acc));
+      }
+    };
+    for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, it++) {
       int split, mt, nt;
       tile_coords(g, tile, split, mt, nt);
-      const int m0 = mt * GBM, n0 = nt * BN;
+      const int m0 = mt * TILE_M + (int)rank * GBM, n0 = nt * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
       if (!mbar_wait(tfull_bar(acc), acc_phase, abort_flag)) { ok = false; break; }
@@ -409,9 +446,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
                                                                 stage_u32, aux_bar(quad), aux_phase, chunk_count,
                                                                 abort_flag);
         }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(tempty_bar(acc));
+        release_acc(acc);
         continue;
       }
       GemmTcArgs gl = g;
@@ -428,9 +463,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
         else
           epilogue_store_chunk<__nv_bfloat16>(gl, r, row, col0, row_ok);
       }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(tempty_bar(acc));
+      release_acc(acc);
     }
     if (g.tma_epi && lane == 0) bulk_wait<0>();  // all stores have left shared memory and landed
   }
@@ -446,10 +479,29 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
   }
   tc_fence_before();
   __syncthreads();
+  // neither CTA of a pair may leave while the other can still signal its barriers or its
+  // tensor memory is still being written by the leader's MMAs
+  if (PAIR) cluster_sync_all();
   if (warp == 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, TMEM_COLS);
   }
+}
+
+template <int BN, bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, GemmTcArgs g) {
+  gemm_tc_body<BN, A_MN, B_MN, false>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
+}
+
+// Pair form: clusters of two CTAs, one 256 x 256 tile per pair and step.
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                    const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
+                    GemmTcArgs g) {
+  gemm_tc_body<256, A_MN, B_MN, true>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
 }
 
 // C (+)= sum_s ws[s]  — split order is fixed, so the result is reproducible.  ws holds
@@ -537,13 +589,45 @@ static int get_tmap_out(CUtensorMap *out, const void *base, int dtype, uint64_t 
 template <int BN, bool A_MN, bool B_MN>
 static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_, const CUtensorMap &tx,
                           const GemmTcArgs &g, int grid) {
-  using L = GemmSmemLayout<BN>;
+  using L = GemmSmemLayout<BN, false>;
   static bool attr = false;
   if (!attr) {
     ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     attr = true;
   }
   gemm_tc_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
+// Pair form.  `pairs` = tile walkers wanted; the grid is capped at the number of two-CTA
+// clusters the device can hold at once (asked from the occupancy API on first use).
+template <bool A_MN, bool B_MN>
+static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_,
+                               const CUtensorMap &tx, const GemmTcArgs &g, int pairs) {
+  using L = GemmSmemLayout<256, true>;
+  static int max_pairs = 0;
+  if (!max_pairs) {
+    ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * (g_sm_count / 2));
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = L::DYN;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<A_MN, B_MN>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = g_sm_count / 2;
+    }
+    max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
+  }
+  const int n = pairs < max_pairs ? pairs : max_pairs;
+  gemm_tc_pair_kernel<A_MN, B_MN><<<2 * n, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -565,26 +649,38 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   const bool a_mn = layout == ALPHA_GEMM_TN;
   const bool b_mn = layout != ALPHA_GEMM_NT;
   const int BN = N <= 128 ? 128 : 256;
+  const bool pair = BN == 256 && M > GBM;  // two CTAs per 256 x 256 tile
+  const int tile_m = pair ? 2 * GBM : GBM;
   CUtensorMap ta, tb;
   // A: K-major [M,K] (inner K) or M-major [K,M] (inner M)
   if (a_mn) { if (get_tmap(&ta, ptr<void>(A), M, K, lda, 64, 64)) return 1; }
   else      { if (get_tmap(&ta, ptr<void>(A), K, M, lda, 64, GBM)) return 1; }
   if (b_mn) { if (get_tmap(&tb, ptr<void>(B), N, K, ldb, 64, 64)) return 1; }
-  else      { if (get_tmap(&tb, ptr<void>(B), K, N, ldb, 64, BN)) return 1; }
+  else      { if (get_tmap(&tb, ptr<void>(B), K, N, ldb, 64, pair ? BN / 2 : BN)) return 1; }
 
   GemmTcArgs g;
   memset(&g, 0, sizeof(g));
   g.M = (int)M; g.N = (int)N; g.K = (int)K;
-  g.tiles_m = (int)((M + GBM - 1) / GBM);
+  g.tiles_m = (int)((M + tile_m - 1) / tile_m);
   g.tiles_n = (int)((N + BN - 1) / BN);
   g.kblocks = (int)((K + GBK - 1) / GBK);
   g.err = tc_error_word();
   const int tiles = g.tiles_m * g.tiles_n;
+  // Split-K when the output has too few tiles to fill the device: pick the split count that
+  // minimises (waves of tiles) x (K steps per tile + per-tile overhead) + the cost of adding
+  // the fp32 partial slabs, all in units of one K step of one tile walker (~0.5 us).
+  const int slots = pair ? g_sm_count / 2 : g_sm_count;
   int splits = 1;
-  if (epilogue == ALPHA_EPI_NONE && tiles * 2 <= g_sm_count && g.kblocks >= 16) {
-    splits = g_sm_count / tiles;
-    if (splits > g.kblocks / 8) splits = g.kblocks / 8;
-    if (splits < 1) splits = 1;
+  if (epilogue == ALPHA_EPI_NONE && tiles < slots && g.kblocks >= 16) {
+    const int max_s = g.kblocks / 8 < 32 ? g.kblocks / 8 : 32;
+    double best = 1e30;
+    for (int sp = 1; sp <= max_s; sp++) {
+      const int waves = (tiles * sp + slots - 1) / slots;
+      const int kb = (g.kblocks + sp - 1) / sp;
+      double t = (double)waves * (kb + 3);
+      if (sp > 1) t += (double)(sp + 1) * (double)M * (double)N * 4.0 / 5.0e12 / 0.5e-6;
+      if (t < best) { best = t; splits = sp; }
+    }
   }
   g.kb_per_split = (g.kblocks + splits - 1) / splits;
   splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;  // drop empty splits
@@ -615,12 +711,18 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   const int total = tiles * splits;
   const int grid = total < g_sm_count ? total : g_sm_count;
   int rc;
+  if (pair) {
+    rc = a_mn ? launch_pair_variant<true, true>(ta, tb, tcm, txm, g, total)
+              : (b_mn ? launch_pair_variant<false, true>(ta, tb, tcm, txm, g, total)
+                      : launch_pair_variant<false, false>(ta, tb, tcm, txm, g, total));
+  } else {
 #define GEMM_VARIANT(BNV)                                                                               \
   (a_mn ? launch_variant<BNV, true, true>(ta, tb, tcm, txm, g, grid)                                    \
         : (b_mn ? launch_variant<BNV, false, true>(ta, tb, tcm, txm, g, grid)                           \
                 : launch_variant<BNV, false, false>(ta, tb, tcm, txm, g, grid)))
   rc = BN == 256 ? GEMM_VARIANT(256) : GEMM_VARIANT(128);
 #undef GEMM_VARIANT
+  }
   if (rc == 0 && splits > 1) {
     const int vec4 = (N % 4 == 0) ? 1 : 0;   // ws slabs are 512-byte aligned and dense
     const int rgrid = grid_for(M * N / (vec4 ? 4 : 1) + 1, 256, 8);

@@ -223,203 +223,294 @@ __global__ void __launch_bounds__(256) ln_reduce_partials(const float *__restric
   }
 }
 
-// ── one CTA per row (the fast path) ─────────────────────────────────────────────────────
-// 128 threads walk rows; thread t owns the 16-byte column vectors t and t+128 of every row, so
-// its slice of the weight / bias (and, backward, of the dw / db sums) stays in registers
-// for the whole kernel and only the row itself moves: ~40 registers per thread, twelve or
-// more CTAs per SM, every access a fully coalesced 16-byte load or store.  Row statistics
-// are block reductions (warp shuffle + 4 partials in shared memory, one __syncthreads each,
-// slots alternate between rows so no second barrier is needed).
+// ── a CTA per group of R rows (the fast path) ────────────────────────────────────────────
+// Up to 128 threads walk groups of R rows; thread t owns the 16-byte column vectors t and
+// t + blockDim.x of every row, so its slice of the weight / bias (and, backward, of the
+// dw / db sums) stays in registers for the whole kernel and only the rows themselves move,
+// every access a fully coalesced 16-byte load or store.  The next group is fetched into
+// registers before the current one is reduced, so each CTA keeps 2·R rows of loads in flight
+// across the block reductions (warp shuffle + one partial per warp in shared memory, one
+// __syncthreads each; the slots alternate between groups so no second barrier is needed).
 constexpr int LN_CTA = 128;
 
-// sum over the block; slot is a 4-float shared array private to this reduction instance
-__device__ __forceinline__ float cta_sum4(float v, float *slot) {
-  v = warp_sum(v);
-  if ((threadIdx.x & 31) == 0) slot[threadIdx.x >> 5] = v;
+// sums of R values over the block; slot is [R][4] floats private to this reduction instance
+// (entries of warps that do not exist stay zero from the kernel prologue)
+template <int R>
+__device__ __forceinline__ void cta_sum_rows(float (&v)[R], float (*slot)[4]) {
+#pragma unroll
+  for (int k = 0; k < R; k++) v[k] = warp_sum(v[k]);
+  if ((threadIdx.x & 31) == 0) {
+#pragma unroll
+    for (int k = 0; k < R; k++) slot[k][threadIdx.x >> 5] = v[k];
+  }
   __syncthreads();
-  return (slot[0] + slot[1]) + (slot[2] + slot[3]);
+#pragma unroll
+  for (int k = 0; k < R; k++) v[k] = (slot[k][0] + slot[k][1]) + (slot[k][2] + slot[k][3]);
 }
 
-template <typename T, int NV, bool RMS>
+template <typename T, int NV, int R, bool RMS>
 __global__ void __launch_bounds__(LN_CTA) ln_fwd_cta(const T *__restrict__ x, const float *__restrict__ w,
                                                      const float *__restrict__ b, T *__restrict__ y, int64_t rows,
                                                      int dim, float eps) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[2][2][4];
-  const int nvec = dim / V;
+  __shared__ float red[2][2][R][4];
+  for (int i = threadIdx.x; i < 2 * 2 * R * 4; i += blockDim.x) (&red[0][0][0][0])[i] = 0.f;
+  __syncthreads();
+  const int nvec = dim / V, nt = blockDim.x;
+  bool act[NV];
   float wv[NV][V], bv[NV][V];
 #pragma unroll
   for (int v = 0; v < NV; v++) {
-    const int iv = v * LN_CTA + threadIdx.x;
+    const int iv = v * nt + threadIdx.x;
+    act[v] = iv < nvec;
 #pragma unroll
     for (int j = 0; j < V; j += 4) {
-      const float4 a = iv < nvec ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
-      const float4 c = (!RMS && iv < nvec) ? *reinterpret_cast<const float4 *>(b + iv * V + j) : make_float4(0, 0, 0, 0);
+      const float4 a = act[v] ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
+      const float4 c = (!RMS && act[v]) ? *reinterpret_cast<const float4 *>(b + iv * V + j) : make_float4(0, 0, 0, 0);
       wv[v][j] = a.x; wv[v][j + 1] = a.y; wv[v][j + 2] = a.z; wv[v][j + 3] = a.w;
       bv[v][j] = c.x; bv[v][j + 1] = c.y; bv[v][j + 2] = c.z; bv[v][j + 3] = c.w;
     }
   }
-  int par = 0;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
-    float xv[NV][V];
-    const T *xr = x + r * dim;
-    float s = 0.f;
+  const int64_t ngroups = (rows + R - 1) / R;
+  Vec16<T> nxt[R][NV];
+  auto fetch = [&](int64_t grp) {
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int iv = v * LN_CTA + threadIdx.x;
-      if (iv < nvec) {
-        Vec16<T> t;
-        t.load(xr + iv * V);
-        t.get(xv[v]);
+    for (int k = 0; k < R; k++) {
+      const int64_t r = grp * R + k;
+      if (r < rows) {
 #pragma unroll
-        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+        for (int v = 0; v < NV; v++)
+          if (act[v]) nxt[k][v].load(x + r * dim + (v * nt + threadIdx.x) * V);
       }
     }
-    s = cta_sum4(s, red[par][0]);
-    float mean = 0.f, rstd;
-    if (RMS) {
-      rstd = rsqrtf(s / dim + eps);
-    } else {
-      mean = s / dim;
-      float q = 0.f;
+  };
+  if (blockIdx.x < ngroups) fetch(blockIdx.x);
+  int par = 0;
+  for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x, par ^= 1) {
+    float xv[R][NV][V];
+    float s[R];
 #pragma unroll
-      for (int v = 0; v < NV; v++)
-        if (v * LN_CTA + threadIdx.x < nvec) {
+    for (int k = 0; k < R; k++) {
+      s[k] = 0.f;
+      const bool rv = grp * R + k < rows;
 #pragma unroll
-          for (int j = 0; j < V; j++) {
-            const float d = xv[v][j] - mean;
-            q += d * d;
-          }
+      for (int v = 0; v < NV; v++) {
+        if (rv && act[v]) {
+          nxt[k][v].get(xv[k][v]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; j++) xv[k][v][j] = 0.f;
         }
-      q = cta_sum4(q, red[par][1]);
-      rstd = 1.f / sqrtf(q / dim + eps);
+#pragma unroll
+        for (int j = 0; j < V; j++) s[k] += RMS ? xv[k][v][j] * xv[k][v][j] : xv[k][v][j];
+      }
     }
-    T *yr = y + r * dim;
+    if (grp + gridDim.x < ngroups) fetch(grp + gridDim.x);
+    cta_sum_rows<R>(s, red[par][0]);
+    float mean[R], rstd[R];
+    if (RMS) {
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int iv = v * LN_CTA + threadIdx.x;
-      if (iv < nvec) {
-        float o[V];
+      for (int k = 0; k < R; k++) {
+        mean[k] = 0.f;
+        rstd[k] = rsqrtf(s[k] / dim + eps);
+      }
+    } else {
+      float q[R];
 #pragma unroll
-        for (int j = 0; j < V; j++) o[j] = (xv[v][j] - mean) * rstd * wv[v][j] + bv[v][j];
-        Vec16<T> t;
-        t.set(o);
-        t.store(yr + iv * V);
+      for (int k = 0; k < R; k++) {
+        mean[k] = s[k] / dim;
+        q[k] = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+          if (act[v]) {
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+              const float d = xv[k][v][j] - mean[k];
+              q[k] += d * d;
+            }
+          }
+      }
+      cta_sum_rows<R>(q, red[par][1]);
+#pragma unroll
+      for (int k = 0; k < R; k++) rstd[k] = 1.f / sqrtf(q[k] / dim + eps);
+    }
+#pragma unroll
+    for (int k = 0; k < R; k++) {
+      const int64_t r = grp * R + k;
+      if (r < rows) {
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+          if (act[v]) {
+            float o[V];
+#pragma unroll
+            for (int j = 0; j < V; j++) o[j] = (xv[k][v][j] - mean[k]) * rstd[k] * wv[v][j] + bv[v][j];
+            Vec16<T> t;
+            t.set(o);
+            t.store(y + r * dim + (v * nt + threadIdx.x) * V);
+          }
       }
     }
   }
 }
 
 // part: [gridDim.x][2][dim] f32 partial column sums (dw, db), written once per CTA.
-template <typename T, int NV, bool RMS>
+template <typename T, int NV, int R, bool RMS>
 __global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, const float *__restrict__ w,
                                                      const T *__restrict__ g, const T *dx_add, T *dx,
                                                      float *__restrict__ part, int64_t rows, int dim, float eps) {
   constexpr int V = Vec16<T>::N;
-  __shared__ float red[2][4][4];
-  const int nvec = dim / V;
+  __shared__ float red[2][4][R][4];
+  for (int i = threadIdx.x; i < 2 * 4 * R * 4; i += blockDim.x) (&red[0][0][0][0])[i] = 0.f;
+  __syncthreads();
+  const int nvec = dim / V, nt = blockDim.x;
+  bool act[NV];
   float wv[NV][V], dw_acc[NV][V], db_acc[NV][V];
 #pragma unroll
   for (int v = 0; v < NV; v++) {
-    const int iv = v * LN_CTA + threadIdx.x;
+    const int iv = v * nt + threadIdx.x;
+    act[v] = iv < nvec;
 #pragma unroll
     for (int j = 0; j < V; j += 4) {
-      const float4 a = iv < nvec ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
+      const float4 a = act[v] ? *reinterpret_cast<const float4 *>(w + iv * V + j) : make_float4(0, 0, 0, 0);
       wv[v][j] = a.x; wv[v][j + 1] = a.y; wv[v][j + 2] = a.z; wv[v][j + 3] = a.w;
     }
 #pragma unroll
     for (int j = 0; j < V; j++) dw_acc[v][j] = db_acc[v][j] = 0.f;
   }
-  int par = 0;
-  for (int64_t r = blockIdx.x; r < rows; r += gridDim.x, par ^= 1) {
-    float xv[NV][V], gv[NV][V];
-    const T *xr = x + r * dim, *gr = g + r * dim;
-    float s = 0.f;
+  const int64_t ngroups = (rows + R - 1) / R;
+  Vec16<T> nx[R][NV], ng[R][NV], na[R][NV];
+  auto fetch = [&](int64_t grp) {
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int iv = v * LN_CTA + threadIdx.x;
-      if (iv < nvec) {
-        Vec16<T> t, u;
-        t.load(xr + iv * V);
-        u.load(gr + iv * V);
-        t.get(xv[v]);
-        u.get(gv[v]);
+    for (int k = 0; k < R; k++) {
+      const int64_t r = grp * R + k;
+      if (r < rows) {
 #pragma unroll
-        for (int j = 0; j < V; j++) s += RMS ? xv[v][j] * xv[v][j] : xv[v][j];
+        for (int v = 0; v < NV; v++)
+          if (act[v]) {
+            const int64_t off = r * dim + (v * nt + threadIdx.x) * V;
+            nx[k][v].load(x + off);
+            ng[k][v].load(g + off);
+            if (dx_add) na[k][v].load(dx_add + off);
+          }
       }
     }
-    s = cta_sum4(s, red[par][0]);
-    float mean = 0.f, rstd;
+  };
+  if (blockIdx.x < ngroups) fetch(blockIdx.x);
+  int par = 0;
+  for (int64_t grp = blockIdx.x; grp < ngroups; grp += gridDim.x, par ^= 1) {
+    float xv[R][NV][V], gv[R][NV][V];
+    Vec16<T> av[R][NV];
+    float s[R];
+#pragma unroll
+    for (int k = 0; k < R; k++) {
+      s[k] = 0.f;
+      const bool rv = grp * R + k < rows;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        if (rv && act[v]) {
+          nx[k][v].get(xv[k][v]);
+          ng[k][v].get(gv[k][v]);
+          av[k][v] = na[k][v];
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; j++) xv[k][v][j] = gv[k][v][j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < V; j++) s[k] += RMS ? xv[k][v][j] * xv[k][v][j] : xv[k][v][j];
+      }
+    }
+    if (grp + gridDim.x < ngroups) fetch(grp + gridDim.x);
+    cta_sum_rows<R>(s, red[par][0]);
+    float mean[R], rstd[R];
     if (RMS) {
-      rstd = rsqrtf(s / dim + eps);
+#pragma unroll
+      for (int k = 0; k < R; k++) {
+        mean[k] = 0.f;
+        rstd[k] = rsqrtf(s[k] / dim + eps);
+      }
     } else {
-      mean = s / dim;
-      float q = 0.f;
+      float q[R];
+#pragma unroll
+      for (int k = 0; k < R; k++) {
+        mean[k] = s[k] / dim;
+        q[k] = 0.f;
+#pragma unroll
+        for (int v = 0; v < NV; v++)
+          if (act[v]) {
+#pragma unroll
+            for (int j = 0; j < V; j++) {
+              const float d = xv[k][v][j] - mean[k];
+              q[k] += d * d;
+            }
+          }
+      }
+      cta_sum_rows<R>(q, red[par][1]);
+#pragma unroll
+      for (int k = 0; k < R; k++) rstd[k] = 1.f / sqrtf(q[k] / dim + eps);
+    }
+    float s1[R], s2[R];
+#pragma unroll
+    for (int k = 0; k < R; k++) {
+      s1[k] = s2[k] = 0.f;
 #pragma unroll
       for (int v = 0; v < NV; v++)
-        if (v * LN_CTA + threadIdx.x < nvec) {
+        if (act[v]) {
 #pragma unroll
           for (int j = 0; j < V; j++) {
-            const float d = xv[v][j] - mean;
-            q += d * d;
+            const float xhat = (xv[k][v][j] - mean[k]) * rstd[k];
+            const float dy = gv[k][v][j] * wv[v][j];
+            dw_acc[v][j] += gv[k][v][j] * xhat;  // rows past the end carry g == 0
+            db_acc[v][j] += gv[k][v][j];
+            s1[k] += dy;
+            s2[k] += dy * xhat;
+            xv[k][v][j] = xhat;
+            gv[k][v][j] = dy;
           }
         }
-      q = cta_sum4(q, red[par][1]);
-      rstd = 1.f / sqrtf(q / dim + eps);
     }
-    float s1 = 0.f, s2 = 0.f;
-#pragma unroll
-    for (int v = 0; v < NV; v++)
-      if (v * LN_CTA + threadIdx.x < nvec) {
-#pragma unroll
-        for (int j = 0; j < V; j++) {
-          const float xhat = (xv[v][j] - mean) * rstd;
-          const float dy = gv[v][j] * wv[v][j];
-          dw_acc[v][j] += gv[v][j] * xhat;
-          db_acc[v][j] += gv[v][j];
-          s1 += dy;
-          s2 += dy * xhat;
-          xv[v][j] = xhat;
-          gv[v][j] = dy;
-        }
-      }
     // the two sums share one barrier
-    s1 = warp_sum(s1);
-    s2 = warp_sum(s2);
-    if ((threadIdx.x & 31) == 0) {
-      red[par][2][threadIdx.x >> 5] = s1;
-      red[par][3][threadIdx.x >> 5] = s2;
+    {
+      float both[2 * R];
+#pragma unroll
+      for (int k = 0; k < R; k++) {
+        both[k] = s1[k];
+        both[R + k] = s2[k];
+      }
+      cta_sum_rows<2 * R>(both, reinterpret_cast<float(*)[4]>(&red[par][2][0][0]));
+#pragma unroll
+      for (int k = 0; k < R; k++) {
+        s1[k] = RMS ? 0.f : both[k];
+        s2[k] = both[R + k];
+      }
     }
-    __syncthreads();
-    s1 = RMS ? 0.f : (red[par][2][0] + red[par][2][1]) + (red[par][2][2] + red[par][2][3]);
-    s2 = (red[par][3][0] + red[par][3][1]) + (red[par][3][2] + red[par][3][3]);
-    T *dr = dx + r * dim;
 #pragma unroll
-    for (int v = 0; v < NV; v++) {
-      const int iv = v * LN_CTA + threadIdx.x;
-      if (iv < nvec) {
-        float o[V];
+    for (int k = 0; k < R; k++) {
+      const int64_t r = grp * R + k;
+      if (r < rows) {
 #pragma unroll
-        for (int j = 0; j < V; j++) o[j] = rstd * (gv[v][j] - (s1 + xv[v][j] * s2) / dim);
-        if (dx_add) {
-          Vec16<T> u;
-          float e[V];
-          u.load(dx_add + r * dim + iv * V);
-          u.get(e);
+        for (int v = 0; v < NV; v++)
+          if (act[v]) {
+            float o[V];
 #pragma unroll
-          for (int j = 0; j < V; j++) o[j] += e[j];
-        }
-        Vec16<T> t;
-        t.set(o);
-        t.store(dr + iv * V);
+            for (int j = 0; j < V; j++) o[j] = rstd[k] * (gv[k][v][j] - (s1[k] + xv[k][v][j] * s2[k]) / dim);
+            if (dx_add) {
+              float e[V];
+              av[k][v].get(e);
+#pragma unroll
+              for (int j = 0; j < V; j++) o[j] += e[j];
+            }
+            Vec16<T> t;
+            t.set(o);
+            t.store(dx + r * dim + (v * nt + threadIdx.x) * V);
+          }
       }
     }
   }
   float *out = part + (size_t)blockIdx.x * 2 * dim;
 #pragma unroll
   for (int v = 0; v < NV; v++) {
-    const int iv = v * LN_CTA + threadIdx.x;
-    if (iv < nvec) {
+    if (act[v]) {
+      const int iv = v * nt + threadIdx.x;
 #pragma unroll
       for (int j = 0; j < V; j += 4) {
         *reinterpret_cast<float4 *>(out + iv * V + j) =
@@ -532,13 +623,16 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   constexpr int V = Vec16<T>::N;
   const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
   if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
-    const int grid = grid_for(rows, 1, 12);
-    if (dim / V <= LN_CTA)
-      ln_fwd_cta<T, 1, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b), ptr<T>(y), rows,
-                                                            (int)dim, eps);
-    else
-      ln_fwd_cta<T, 2, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b), ptr<T>(y), rows,
-                                                            (int)dim, eps);
+    const int nvec = (int)(dim / V);
+    if (nvec <= LN_CTA) {
+      const int nt = (nvec + 31) / 32 * 32;
+      ln_fwd_cta<T, 1, 2, RMS><<<grid_for(rows, 2, 10), nt, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b),
+                                                                            ptr<T>(y), rows, (int)dim, eps);
+    } else {
+      const int nt = ((nvec + 1) / 2 + 31) / 32 * 32;
+      ln_fwd_cta<T, 2, 1, RMS><<<grid_for(rows, 1, 12), nt, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<float>(b),
+                                                                            ptr<T>(y), rows, (int)dim, eps);
+    }
   } else if (fast) {
     const int nv = (int)((dim / V + 31) / 32);
     const int grid = grid_for(rows, LN_WARPS, 16);
@@ -578,17 +672,18 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
                     dim / V <= 32 * 8 &&
                     smem <= 48 * 1024;
   if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0) {
-    const int grid = grid_for(rows, 1, 6);
+    const int nvec = (int)(dim / V);
+    const int grid = nvec <= LN_CTA ? grid_for(rows, 2, 5) : grid_for(rows, 1, 4);
     void *part = nullptr;
     if (pool_alloc((size_t)grid * 2 * dim * sizeof(float), &part)) return 1;
-    if (dim / V <= LN_CTA)
-      ln_bwd_cta<T, 1, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),
-                                                            dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx),
-                                                            (float *)part, rows, (int)dim, eps);
+    if (nvec <= LN_CTA)
+      ln_bwd_cta<T, 1, 2, RMS><<<grid, (nvec + 31) / 32 * 32, 0, g_stream>>>(
+          ptr<T>(x), ptr<float>(w), ptr<T>(g), dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx), (float *)part, rows,
+          (int)dim, eps);
     else
-      ln_bwd_cta<T, 2, RMS><<<grid, LN_CTA, 0, g_stream>>>(ptr<T>(x), ptr<float>(w), ptr<T>(g),
-                                                            dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx),
-                                                            (float *)part, rows, (int)dim, eps);
+      ln_bwd_cta<T, 2, 1, RMS><<<grid, ((nvec + 1) / 2 + 31) / 32 * 32, 0, g_stream>>>(
+          ptr<T>(x), ptr<float>(w), ptr<T>(g), dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx), (float *)part, rows,
+          (int)dim, eps);
     g_launches++;
     ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, 8), 0, g_stream>>>(
         (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);

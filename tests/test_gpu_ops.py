@@ -365,6 +365,7 @@ TC_SHAPES = [
     (200, 300, 72), (1, 8, 8), (130, 264, 200),             # ragged M / N / K
     (384, 2304, 768), (512, 768, 3072),                     # train-step K sizes
     (768, 768, 4096), (96, 3072, 2048),                     # few tiles, long K: split-K
+    (4096, 2304, 192), (4104, 1032, 136),                   # more tiles than tile walkers (both accumulators cycle)
 ]
 
 
