@@ -282,13 +282,13 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 //   dK/dV kernel: CTA = (batch, head, 128 keys), loops over the query blocks at or after it;
 //   dQ    kernel: CTA = (batch, head, 128 queries), loops over the key blocks at or before it.
 // Per (query block, key block) pair both recompute S = Q K^T and dP = dO V^T on the tensor
-// cores into TMEM; the 128 "softmax" threads (one query row each) turn them into
+// cores into TMEM; eight math warps (32 query rows x 64 key columns each) turn them into
 // P = exp2(x2 - lse2) and dS = P*(dP - D)*(1 - tanh^2)*scale, round to bf16 and store them as
 // [query rows][key columns] 128B-swizzled tiles.  That one layout serves both remaining
 // products: read K-major it is the A operand of dQ += dS K, read M-major it is the A operand
 // of dV += P^T dO and dK += dS^T Q (the tensor core transposes through the descriptor).
 // Q, dO, K, V tiles are likewise used both K-major (score products) and N-major (gradient
-// products) from the same bytes.
+// products) from the same bytes.  The streamed operand pair comes through a 4-stage TMA ring.
 struct AttnBwdArgs {
   void *dq, *dk, *dv;
   const float *lse, *delta;
@@ -331,63 +331,148 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
   }
 }
 
-// One thread = one query row (TMEM lane).  Reads its S and dP rows, writes the bf16 P (optional)
-// and dS rows into the swizzled tiles.
+// ── backward math warps ─────────────────────────────────────────────────────────────────
+// Eight math warps work on one 128 x 128 (query x key) tile: warp w owns the TMEM lane
+// quadrant w % 4 (32 query rows, one per thread) and the key-column half (w - 2) / 4, so a
+// thread handles 64 scores.  The work is split in two phases so that the tensor core can run
+// ahead: phase A needs only S (scores -> P and the factor P * (1 - tanh^2)), phase B needs dP
+// (-> dS) and stores the bf16 P / dS rows into the 128B-swizzled tiles.
+//
+// Soft cap: tanh(x) for |x| <= 1/2 comes from an odd polynomial on the FMA pipes
+// (x + x^3 (p1 + p2 x^2 + p3 x^4 + p4 x^6), truncation error < 5e-6), which halves the load
+// on the special-function unit that exp2 also needs; a warp whose tile holds a larger
+// argument redoes the tile with the hardware tanh.
+constexpr int AB_THREADS = 320;            // TMA warp, MMA warp, 8 math warps
+constexpr float TANH_POLY_LIMIT2 = 0.25f;  // x^2 bound of the polynomial branch
+
+struct BwdRowConsts {
+  float c1, c2, lse2, scale, delta;
+};
+
+// Phase A for 64 scores of one row.  pk: P as 32 packed bf16 pairs; f0: P * dcap (fp32).
+// Returns the largest squared tanh argument seen (0 when not capped).
+template <bool DIAG, bool CAPPED, bool POLY>
+__device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, bool row_valid, const BwdRowConsts &k,
+                                             uint32_t (&pk)[32], float (&f0)[64]) {
+  uint32_t r0[32], r1[32];
+  tmem_ld_32x32(t_s, r0);
+  tmem_ld_32x32(t_s + 32, r1);
+  tmem_ld_wait();
+  float big = 0.f;
+  const uint64_t c1 = f2_pack(k.c1, k.c1), c2 = f2_pack(k.c2, k.c2), nl = f2_pack(-k.lse2, -k.lse2);
+  const uint64_t one = f2_pack(1.f, 1.f);
+#pragma unroll
+  for (int i = 0; i < 64; i += 2) {
+    const uint32_t a = i < 32 ? r0[i] : r1[i - 32], b = i < 32 ? r0[i + 1] : r1[i - 31];
+    const uint64_t s = f2_pack(__uint_as_float(a), __uint_as_float(b));
+    uint64_t e, dcap = one;
+    if (CAPPED) {
+      const uint64_t x = f2_mul(s, c1);
+      uint64_t th;
+      if (POLY) {
+        const uint64_t x2 = f2_mul(x, x);
+        float xa, xb;
+        f2_unpack(x2, xa, xb);
+        big = fmaxf(big, fmaxf(xa, xb));
+        uint64_t t = f2_fma(x2, f2_pack(0.0218694885f, 0.0218694885f), f2_pack(-0.0539682540f, -0.0539682540f));
+        t = f2_fma(t, x2, f2_pack(0.1333333333f, 0.1333333333f));
+        t = f2_fma(t, x2, f2_pack(-0.3333333333f, -0.3333333333f));
+        th = f2_fma(f2_mul(x, x2), t, x);
+      } else {
+        float xa, xb;
+        f2_unpack(x, xa, xb);
+        th = f2_pack(tanh_approx(xa), tanh_approx(xb));
+      }
+      e = f2_fma(th, c2, nl);
+      dcap = f2_fma(f2_mul(th, f2_pack(-1.f, -1.f)), th, one);
+    } else {
+      e = f2_fma(s, c1, nl);
+    }
+    float ea, eb;
+    f2_unpack(e, ea, eb);
+    float pa = ex2_approx(ea), pb = ex2_approx(eb);
+    if (DIAG) {
+      if (col0 + i > row) pa = 0.f;
+      if (col0 + i + 1 > row) pb = 0.f;
+    }
+    if (!row_valid) pa = pb = 0.f;
+    pk[i >> 1] = bf16x2_pack(pa, pb);
+    if (CAPPED) {
+      f2_unpack(f2_mul(f2_pack(pa, pb), dcap), f0[i], f0[i + 1]);
+    } else {
+      f0[i] = pa;
+      f0[i + 1] = pb;
+    }
+  }
+  return big;
+}
+
+// Phase B: dS = f0 * (dP - delta) * scale for the same 64 columns, then the row's P (optional)
+// and dS chunks go to shared memory.  p_half / ds_half point at this thread's 128-byte row in
+// the 64-column tile of its column half.
 template <bool WRITE_P>
-__device__ __forceinline__ void bwd_row_math(uint32_t tS, uint32_t tdP, uint32_t lane_off, uint8_t *p_row,
-                                             uint8_t *ds_row, int row, bool diag, bool row_valid, float lse2,
-                                             float delta, float c1, float c2, bool capped, float scale) {
-#pragma unroll 1
-  for (int c = 0; c < 4; c++) {
-    uint32_t r[32], d[32];
-    tmem_ld_32x32(tS + lane_off + c * 32, r);
-    tmem_ld_32x32(tdP + lane_off + c * 32, d);
+__device__ __forceinline__ void bwd_phase_b(uint32_t t_dp, int row, const BwdRowConsts &k, const uint32_t (&pk)[32],
+                                            const float (&f0)[64], uint8_t *p_half, uint8_t *ds_half) {
+  const uint64_t sc = f2_pack(k.scale, k.scale), nd = f2_pack(-k.delta * k.scale, -k.delta * k.scale);
+#pragma unroll
+  for (int c = 0; c < 2; c++) {
+    uint32_t d[32];
+    tmem_ld_32x32(t_dp + c * 32, d);
     tmem_ld_wait();
-    uint32_t pp[16], dd[16];
+    uint32_t dd[16];
 #pragma unroll
     for (int i = 0; i < 32; i += 2) {
-      float p[2], ds[2];
-#pragma unroll
-      for (int u = 0; u < 2; u++) {
-        const float s = __uint_as_float(r[i + u]);
-        float x2, dcap = 1.f;
-        if (capped) {
-          const float th = tanh_approx(c1 * s);
-          x2 = c2 * th;
-          dcap = 1.f - th * th;
-        } else {
-          x2 = c1 * s;
-        }
-        const bool dead = !row_valid || (diag && c * 32 + i + u > row);
-        p[u] = dead ? 0.f : ex2_approx(x2 - lse2);
-        ds[u] = p[u] * (__uint_as_float(d[i + u]) - delta) * dcap * scale;
-      }
-      const __nv_bfloat162 pk = __floats2bfloat162_rn(p[0], p[1]);
-      const __nv_bfloat162 dk = __floats2bfloat162_rn(ds[0], ds[1]);
-      pp[i >> 1] = *reinterpret_cast<const uint32_t *>(&pk);
-      dd[i >> 1] = *reinterpret_cast<const uint32_t *>(&dk);
+      const uint64_t g = f2_fma(f2_pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), sc, nd);
+      float da, db;
+      f2_unpack(f2_mul(f2_pack(f0[c * 32 + i], f0[c * 32 + i + 1]), g), da, db);
+      dd[i >> 1] = bf16x2_pack(da, db);
     }
 #pragma unroll
     for (int q = 0; q < 4; q++) {
-      const int chunk = ((c & 1) * 4 + q) ^ (row & 7);
-      const int off = (c >> 1) * AT_TILE + chunk * 16;
-      if (WRITE_P) *reinterpret_cast<uint4 *>(p_row + off) = make_uint4(pp[4 * q], pp[4 * q + 1], pp[4 * q + 2], pp[4 * q + 3]);
-      *reinterpret_cast<uint4 *>(ds_row + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+      const int off = ((c * 4 + q) ^ (row & 7)) * 16;
+      if (WRITE_P)
+        *reinterpret_cast<uint4 *>(p_half + off) =
+            make_uint4(pk[c * 16 + 4 * q], pk[c * 16 + 4 * q + 1], pk[c * 16 + 4 * q + 2], pk[c * 16 + 4 * q + 3]);
+      *reinterpret_cast<uint4 *>(ds_half + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
     }
   }
 }
 
+// Phase A with the branch selection: diagonal tile or not, capped or not, and for capped
+// scores the polynomial tanh unless some argument in the warp's part of the tile is too large.
+__device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0, bool diag, bool capped, bool row_valid,
+                                                const BwdRowConsts &k, uint32_t (&pk)[32], float (&f0)[64]) {
+  if (!capped) {
+    if (diag) bwd_phase_a<true, false, false>(t_s, row, col0, row_valid, k, pk, f0);
+    else bwd_phase_a<false, false, false>(t_s, row, col0, row_valid, k, pk, f0);
+    return;
+  }
+  const float big = diag ? bwd_phase_a<true, true, true>(t_s, row, col0, row_valid, k, pk, f0)
+                         : bwd_phase_a<false, true, true>(t_s, row, col0, row_valid, k, pk, f0);
+  if (__any_sync(0xffffffffu, !(big <= TANH_POLY_LIMIT2))) {  // also catches NaN
+    if (diag) bwd_phase_a<true, true, false>(t_s, row, col0, row_valid, k, pk, f0);
+    else bwd_phase_a<false, true, false>(t_s, row, col0, row_valid, k, pk, f0);
+  }
+}
+
 // shared-memory map of the dK/dV kernel
+constexpr int AK_STAGES = 4;                               // ring of (Q, dO) tiles
 constexpr int AK_K = 0;
 constexpr int AK_V = AT_TILE;
-constexpr int AK_Q = 2 * AT_TILE;              // 2 stages of (Q, dO)
-constexpr int AK_DO = AK_Q + 2 * AT_TILE;
-constexpr int AK_P = AK_DO + 2 * AT_TILE;      // 2 tiles
-constexpr int AK_DS = AK_P + 2 * AT_TILE;      // 2 tiles
+constexpr int AK_Q = 2 * AT_TILE;
+constexpr int AK_DO = AK_Q + AK_STAGES * AT_TILE;
+constexpr int AK_P = AK_DO + AK_STAGES * AT_TILE;          // 2 tiles (key halves)
+constexpr int AK_DS = AK_P + 2 * AT_TILE;                  // 2 tiles
 constexpr int AK_BAR = AK_DS + 2 * AT_TILE;
-constexpr int AK_DYN = AK_BAR + 128 + 1024;
+constexpr int AK_DYN = AK_BAR + 256 + 1024;
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// Pipeline of the dK/dV kernel (tile index `it` walks the query blocks of this key block):
+//   tensor core, on "tile it-1 stored" : dP(it)  ->  dV,dK += (P,dS)(it-1)  ->  S(it+1)
+//   math warps                          : phase A(it) from S(it) | wait dP(it) and the end of
+//                                         dV,dK(it-1) | phase B(it) stores P,dS | signal
+// S has two TMEM buffers, so the scores of the next tile are ready before the math warps ask
+// for them and the tensor core works while they compute.
+__global__ void __launch_bounds__(AB_THREADS, 1)
 attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                        AttnBwdArgs a) {
@@ -395,9 +480,9 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AK_BAR;
-  const uint32_t kv_full = bar, q_full0 = bar + 8, q_empty0 = bar + 24, sdp_full = bar + 40, pds_ready = bar + 48,
-                 acc_done = bar + 56;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 64);
+  const uint32_t kv_full = bar, s_full0 = bar + 8, dp_full = bar + 24, pds_ready = bar + 32, acc_done = bar + 40,
+                 q_full0 = bar + 48, q_empty0 = q_full0 + 8 * AK_STAGES;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 48 + 16 * AK_STAGES);
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (a.T + 127) / 128;
@@ -410,11 +495,14 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
-    mbar_init(q_full0, 1); mbar_init(q_full0 + 8, 1);
-    mbar_init(q_empty0, 1); mbar_init(q_empty0 + 8, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(pds_ready, 4);
+    mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(pds_ready, 8);
     mbar_init(acc_done, 1);
+    for (int s = 0; s < AK_STAGES; s++) {
+      mbar_init(q_full0 + 8 * s, 1);
+      mbar_init(q_empty0 + 8 * s, 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -427,7 +515,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdV = tmem_base + 256, tdK = tmem_base + 320;
+  const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdV = tmem_base + 384, tdK = tmem_base + 448;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -435,8 +523,8 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, k0, h, b);
       tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, k0, h, b);
       for (int it = 0; it < n_it; it++) {
-        const int st = it & 1;
-        if (!mbar_wait(q_empty0 + 8 * st, ((it >> 1) & 1) ^ 1, abort_flag)) break;
+        const int st = it % AK_STAGES;
+        if (!mbar_wait(q_empty0 + 8 * st, ((it / AK_STAGES) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(q_full0 + 8 * st, 2 * AT_TILE);
         const int q0 = (kb + it) * 128;
         tma_load_4d(sb + AK_Q + st * AT_TILE, &tmap_q, q_full0 + 8 * st, 0, q0, h, b);
@@ -447,57 +535,77 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [q x k] = A[q,d] B[k,d]^T
       constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, true, true);      // [k x d] = A[q,k]^T B[q,d]
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
-      for (int it = 0; it < n_it && ok; it++) {
-        const int st = it & 1;
-        if (!mbar_wait(q_full0 + 8 * st, (it >> 1) & 1, abort_flag)) { ok = false; break; }
+      auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer it & 1 (waits for the tile's loads)
+        const int st = it % AK_STAGES;
+        if (!mbar_wait(q_full0 + 8 * st, (it / AK_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t qs = sb + AK_Q + st * AT_TILE, dos = sb + AK_DO + st * AT_TILE;
+        const uint32_t qs = sb + AK_Q + st * AT_TILE;
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tS, make_smem_desc(qs + kk * 32, 16, 1024), make_smem_desc(sb + AK_K + kk * 32, 16, 1024), idesc_s,
-                      kk > 0 ? 1u : 0u);
+          mma_bf16_ss(tS0 + (it & 1) * 128, make_smem_desc(qs + kk * 32, 16, 1024),
+                      make_smem_desc(sb + AK_K + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(s_full0 + 8 * (it & 1));
+        return true;
+      };
+      auto issue_dp = [&](int it) {          // dP(it) = dO(it) V^T (loads already awaited by issue_s(it))
+        const uint32_t dos = sb + AK_DO + (it % AK_STAGES) * AT_TILE;
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
           mma_bf16_ss(tdP, make_smem_desc(dos + kk * 32, 16, 1024), make_smem_desc(sb + AK_V + kk * 32, 16, 1024),
                       idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(sdp_full);
+        mma_commit(dp_full);
+      };
+      bool ok = mbar_wait(kv_full, 0, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
+      if (ok && n_it > 1) ok = issue_s(1);
+      for (int it = 0; it < n_it && ok; it++) {
         if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (it + 1 < n_it) issue_dp(it + 1);
+        const int st = it % AK_STAGES;
+        const uint32_t qs = sb + AK_Q + st * AT_TILE, dos = sb + AK_DO + st * AT_TILE;
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++) {  // 16 query rows per step
+        for (int kk = 0; kk < 8; kk++)  // 16 query rows per step
           mma_bf16_ss(tdV, make_smem_desc(sb + AK_P + kk * 2048, AT_TILE, 1024), make_smem_desc(dos + kk * 2048, AT_TILE, 1024),
                       idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
-        }
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
+        for (int kk = 0; kk < 8; kk++)
           mma_bf16_ss(tdK, make_smem_desc(sb + AK_DS + kk * 2048, AT_TILE, 1024), make_smem_desc(qs + kk * 2048, AT_TILE, 1024),
                       idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
-        }
         mma_commit(q_empty0 + 8 * st);
         mma_commit(acc_done);
+        if (it + 2 < n_it) ok = issue_s(it + 2);
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     const bool capped = a.cap > 0.f;
-    const float c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
-    const float c2 = a.cap * LOG2E;
+    BwdRowConsts k;
+    k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
+    k.c2 = a.cap * LOG2E;
+    k.scale = a.scale;
+    uint8_t *p_half = smem + AK_P + half * AT_TILE + row * 128;
+    uint8_t *ds_half = smem + AK_DS + half * AT_TILE + row * 128;
     bool ok = true;
     for (int it = 0; it < n_it && ok; it++) {
       const int qi = (kb + it) * 128 + row;
       const bool valid = qi < a.T;
-      const float lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
-      const float dl = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-      // sdp_full also means the gradient products of the previous iteration have finished
-      // reading the P / dS tiles (commits complete in issue order)
-      if (!mbar_wait(sdp_full, it & 1, abort_flag)) { ok = false; break; }
+      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+      k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+      uint32_t pk[32];
+      float f0[64];
+      if (!mbar_wait(s_full0 + 8 * (it & 1), (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_row_math<true>(tS, tdP, lane_off, smem + AK_P + row * 128, smem + AK_DS + row * 128, row, it == 0, valid,
-                         lse2, dl, c1, c2, capped, a.scale);
+      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + half * 64, row, half * 64, it == 0, capped, valid, k, pk, f0);
+      if (!mbar_wait(dp_full, it & 1, abort_flag)) { ok = false; break; }
+      // the gradient products of the previous tile must have finished reading the P / dS tiles
+      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      bwd_phase_b<true>(tdP + lane_off + half * 64, row, k, pk, f0, p_half, ds_half);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
@@ -505,27 +613,24 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     if (ok && mbar_wait(acc_done, (n_it - 1) & 1, abort_flag)) {
       tc_fence_after();
-      const int kj = k0 + row;  // accumulator lanes are keys
+      const int kj = k0 + row;  // accumulator lanes are keys; column half 0 stores dV, half 1 dK
       const int64_t off = (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)kj * a.q_st;
+      __nv_bfloat16 *dst = (__nv_bfloat16 *)(half ? a.dk : a.dv) + off;
+      const uint32_t tacc = half ? tdK : tdV;
 #pragma unroll 1
-      for (int which = 0; which < 2; which++) {
-        __nv_bfloat16 *dst = (__nv_bfloat16 *)(which ? a.dk : a.dv) + off;
-        const uint32_t tacc = which ? tdK : tdV;
-#pragma unroll 1
-        for (int c = 0; c < 2; c++) {
-          uint32_t r[32];
-          tmem_ld_32x32(tacc + lane_off + c * 32, r);
-          tmem_ld_wait();
-          if (kj < a.T) {
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tacc + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (kj < a.T) {
 #pragma unroll
-            for (int q = 0; q < 4; q++) {
-              float f[8];
+          for (int q = 0; q < 4; q++) {
+            float f[8];
 #pragma unroll
-              for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-              Vec16<__nv_bfloat16> v;
-              v.set(f);
-              v.store(dst + c * 32 + q * 8);
-            }
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(dst + c * 32 + q * 8);
           }
         }
       }
@@ -547,15 +652,19 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 }
 
 // shared-memory map of the dQ kernel
+constexpr int AQ_STAGES = 4;                               // ring of (K, V) tiles
 constexpr int AQ_Q = 0;
 constexpr int AQ_DO = AT_TILE;
-constexpr int AQ_K = 2 * AT_TILE;              // 2 stages of (K, V)
-constexpr int AQ_V = AQ_K + 2 * AT_TILE;
-constexpr int AQ_DS = AQ_V + 2 * AT_TILE;      // 2 tiles
+constexpr int AQ_K = 2 * AT_TILE;
+constexpr int AQ_V = AQ_K + AQ_STAGES * AT_TILE;
+constexpr int AQ_DS = AQ_V + AQ_STAGES * AT_TILE;          // 2 tiles (key halves)
 constexpr int AQ_BAR = AQ_DS + 2 * AT_TILE;
-constexpr int AQ_DYN = AQ_BAR + 128 + 1024;
+constexpr int AQ_DYN = AQ_BAR + 256 + 1024;
 
-__global__ void __launch_bounds__(AT_THREADS, 1)
+// Same pipeline as the dK/dV kernel with the roles of the operands exchanged: the tile index j
+// walks the key blocks of this query block, (K, V) tiles come through the ring, and the only
+// gradient product is dQ += dS K.
+__global__ void __launch_bounds__(AB_THREADS, 1)
 attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
                       AttnBwdArgs a) {
@@ -563,9 +672,9 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AQ_BAR;
-  const uint32_t q_full = bar, kv_full0 = bar + 8, kv_empty0 = bar + 24, sdp_full = bar + 40, ds_ready = bar + 48,
-                 dq_done = bar + 56;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 64);
+  const uint32_t q_full = bar, s_full0 = bar + 8, dp_full = bar + 24, ds_ready = bar + 32, acc_done = bar + 40,
+                 kv_full0 = bar + 48, kv_empty0 = kv_full0 + 8 * AQ_STAGES;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 48 + 16 * AQ_STAGES);
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (a.T + 127) / 128;
@@ -578,11 +687,14 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
-    mbar_init(kv_full0, 1); mbar_init(kv_full0 + 8, 1);
-    mbar_init(kv_empty0, 1); mbar_init(kv_empty0 + 8, 1);
-    mbar_init(sdp_full, 1);
-    mbar_init(ds_ready, 4);
-    mbar_init(dq_done, 1);
+    mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
+    mbar_init(dp_full, 1);
+    mbar_init(ds_ready, 8);
+    mbar_init(acc_done, 1);
+    for (int s = 0; s < AQ_STAGES; s++) {
+      mbar_init(kv_full0 + 8 * s, 1);
+      mbar_init(kv_empty0 + 8 * s, 1);
+    }
     *abort_flag = 0;
     fence_barrier_init();
     fence_proxy_async();
@@ -595,7 +707,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS = tmem_base, tdP = tmem_base + 128, tdQ = tmem_base + 256;
+  const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdQ = tmem_base + 384;
 
   if (warp == 0) {
     if (lane == 0) {
@@ -603,8 +715,8 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, q0, h, b);
       tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, q0, h, b);
       for (int j = 0; j < nb; j++) {
-        const int st = j & 1;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((j >> 1) & 1) ^ 1, abort_flag)) break;
+        const int st = j % AQ_STAGES;
+        if (!mbar_wait(kv_empty0 + 8 * st, ((j / AQ_STAGES) & 1) ^ 1, abort_flag)) break;
         mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
         tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
         tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
@@ -614,73 +726,94 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     if (lane == 0) {
       constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
       constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);     // [q x d] = A[q,k] B[k,d]
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      for (int j = 0; j < nb && ok; j++) {
-        const int st = j & 1;
-        if (!mbar_wait(kv_full0 + 8 * st, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer j & 1 (waits for the tile's loads)
+        const int st = j % AQ_STAGES;
+        if (!mbar_wait(kv_full0 + 8 * st, (j / AQ_STAGES) & 1, abort_flag)) return false;
         tc_fence_after();
-        const uint32_t ks = sb + AQ_K + st * AT_TILE, vs = sb + AQ_V + st * AT_TILE;
+        const uint32_t ks = sb + AQ_K + st * AT_TILE;
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tS, make_smem_desc(sb + AQ_Q + kk * 32, 16, 1024), make_smem_desc(ks + kk * 32, 16, 1024), idesc_s,
-                      kk > 0 ? 1u : 0u);
+          mma_bf16_ss(tS0 + (j & 1) * 128, make_smem_desc(sb + AQ_Q + kk * 32, 16, 1024),
+                      make_smem_desc(ks + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(s_full0 + 8 * (j & 1));
+        return true;
+      };
+      auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
+        const uint32_t vs = sb + AQ_V + (j % AQ_STAGES) * AT_TILE;
 #pragma unroll
         for (int kk = 0; kk < 4; kk++)
           mma_bf16_ss(tdP, make_smem_desc(sb + AQ_DO + kk * 32, 16, 1024), make_smem_desc(vs + kk * 32, 16, 1024), idesc_s,
                       kk > 0 ? 1u : 0u);
-        mma_commit(sdp_full);
+        mma_commit(dp_full);
+      };
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
+      if (ok && nb > 1) ok = issue_s(1);
+      for (int j = 0; j < nb && ok; j++) {
         if (!mbar_wait(ds_ready, j & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        if (j + 1 < nb) issue_dp(j + 1);
+        const int st = j % AQ_STAGES;
+        const uint32_t ks = sb + AQ_K + st * AT_TILE;
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++) {  // 16 keys per step
+        for (int kk = 0; kk < 8; kk++)  // 16 keys per step
           mma_bf16_ss(tdQ, make_smem_desc(sb + AQ_DS + (kk >> 2) * AT_TILE + (kk & 3) * 32, 16, 1024),
                       make_smem_desc(ks + kk * 2048, AT_TILE, 1024), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
-        }
         mma_commit(kv_empty0 + 8 * st);
-        if (j == nb - 1) mma_commit(dq_done);
+        mma_commit(acc_done);
+        if (j + 2 < nb) ok = issue_s(j + 2);
       }
     }
   } else {
-    const int quad = warp & 3;
+    const int quad = warp & 3, half = (warp - 2) >> 2;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     const bool capped = a.cap > 0.f;
-    const float c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
-    const float c2 = a.cap * LOG2E;
     const int qi = q0 + row;
     const bool valid = qi < a.T;
-    const float lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
-    const float dl = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+    BwdRowConsts k;
+    k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
+    k.c2 = a.cap * LOG2E;
+    k.scale = a.scale;
+    k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+    k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+    uint8_t *ds_half = smem + AQ_DS + half * AT_TILE + row * 128;
     bool ok = true;
     for (int j = 0; j < nb && ok; j++) {
-      if (!mbar_wait(sdp_full, j & 1, abort_flag)) { ok = false; break; }
+      uint32_t pk[32];
+      float f0[64];
+      if (!mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_row_math<false>(tS, tdP, lane_off, nullptr, smem + AQ_DS + row * 128, row, j == qb, valid, lse2, dl, c1, c2,
-                          capped, a.scale);
+      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + half * 64, row, half * 64, j == qb, capped, valid, k, pk, f0);
+      if (!mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
+      // dQ += dS(j-1) K(j-1) must have finished reading the dS tiles
+      if (j > 0 && !mbar_wait(acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      bwd_phase_b<false>(tdP + lane_off + half * 64, row, k, pk, f0, nullptr, ds_half);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(ds_ready);
     }
-    if (ok && mbar_wait(dq_done, 0, abort_flag)) {
+    if (ok && mbar_wait(acc_done, (nb - 1) & 1, abort_flag)) {
       tc_fence_after();
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st;
-#pragma unroll 1
-      for (int c = 0; c < 2; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(tdQ + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (valid) {
+      // dQ is 64 columns: each column half of the math warps stores 32 of them
+      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st +
+                           half * 32;
+      uint32_t r[32];
+      tmem_ld_32x32(tdQ + lane_off + half * 32, r);
+      tmem_ld_wait();
+      if (valid) {
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            float f[8];
+        for (int q = 0; q < 4; q++) {
+          float f[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-            Vec16<__nv_bfloat16> v;
-            v.set(f);
-            v.store(dst + c * 32 + q * 8);
-          }
+          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+          Vec16<__nv_bfloat16> v;
+          v.set(f);
+          v.store(dst + q * 8);
         }
       }
     }
@@ -801,9 +934,9 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
     attr = true;
   }
   dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
-  attn_tc_bwd_dkv_kernel<<<grid, AT_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  attn_tc_bwd_dkv_kernel<<<grid, AB_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a);
   g_launches++;
-  attn_tc_bwd_dq_kernel<<<grid, AT_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  attn_tc_bwd_dq_kernel<<<grid, AB_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a);
   pool_free(delta);
   ALPHA_LAUNCHED();
   return 0;

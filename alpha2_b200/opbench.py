@@ -96,17 +96,17 @@ def gemm_case(b: Bench, layout: str, M: int, N: int, K: int, out_dtype: str = "b
     return {"ms": ms, "work": 2.0 * M * N * K, "kind": "flop"}
 
 
-def attn_case(b: Bench, Bn=8, H=12, T=1024, D=64, backward=False, dtype="bf16"):
+def attn_case(b: Bench, Bn=16, H=12, T=1024, D=64, backward=False, dtype="bf16", cap=30.0):
     B = b.B
     E = H * D
     qkv = b.normal((Bn * T, 3 * E), 1.0, dtype)
     dout = b.normal((Bn * T, E), 1.0, dtype)
     scale = 1 / math.sqrt(D)
-    out, lse = B.attentionQkv(qkv, Bn, T, H, scale, 0.0)
+    out, lse = B.attentionQkv(qkv, Bn, T, H, scale, cap)
     if not backward:
-        ms = b.time(lambda: B.attentionQkv(qkv, Bn, T, H, scale, 0.0))
+        ms = b.time(lambda: B.attentionQkv(qkv, Bn, T, H, scale, cap))
         return {"ms": ms, "work": 4.0 * Bn * H * T * T * D, "kind": "flop"}
-    ms = b.time(lambda: B.attentionQkvBackward(qkv, out, dout, lse, Bn, T, H, scale, 0.0))
+    ms = b.time(lambda: B.attentionQkvBackward(qkv, out, dout, lse, Bn, T, H, scale, cap))
     return {"ms": ms, "work": 8.0 * Bn * H * T * T * D, "kind": "flop"}
 
 

@@ -430,7 +430,10 @@ def test_gemm_bf16_epilogues_and_accumulate(B):
 
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("cfg", [(3, 64, 16, 30.0), (2, 100, 64, 30.0), (2, 256, 64, 0.0), (1, 130, 32, 2.0),
-                                 (1, 192, 128, 30.0)])
+                                 (1, 192, 128, 30.0),
+                                 (2, 640, 64, 30.0),    # 5 key/query blocks: the 4-stage rings wrap
+                                 (1, 300, 64, 2.0),     # tight cap: tanh arguments beyond the polynomial range
+                                 (1, 1024, 64, 0.0)])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_flash_attention_contract(B, cfg, dtype):
     """Backend.flashAttention / flashAttentionBackward on [B*H, T, D] (interfaces.ts:127-135)."""
