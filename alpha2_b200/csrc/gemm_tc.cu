@@ -323,10 +323,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
   const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
 
   if (warp == 0) {
-    // ── TMA producer (each CTA loads its own share) ────────────────────────
-    if (lane == 0) {
-      tma_prefetch_desc(&tmap_a);
-      tma_prefetch_desc(&tmap_b);
+    // ── TMA producer (each CTA loads its own share); the warp runs the loop, one lane issues ──
+    {
+      if (elect_one()) {
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+      }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
@@ -339,34 +341,37 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
         const int kb1 = min(g.kblocks, kb0 + g.kb_per_split);
         for (int kb = kb0; kb < kb1; kb++) {
           if (!mbar_wait(empty_bar(stage), phase ^ 1, abort_flag)) { ok = false; break; }
-          // the leader's barrier counts the bytes of both CTAs
-          if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), (PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES));
           const uint32_t fb = PAIR ? map_to_cta(full_bar(stage), 0) : full_bar(stage);
-          auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
-            if (PAIR) tma_load_2d_pair(dst, map, fb, x, y); else tma_load_2d(dst, map, fb, x, y);
-          };
           const uint32_t a_dst = a_base + stage * L::A_BYTES;
           const uint32_t b_dst = b_base + stage * L::B_BYTES;
           const int k0 = kb * GBK;
-          if (A_MN) {
+          if (elect_one()) {
+            // the leader's barrier counts the bytes of both CTAs
+            if (!PAIR || rank == 0) mbar_expect_tx(full_bar(stage), (PAIR ? 2 : 1) * (L::A_BYTES + L::B_BYTES));
+            auto load = [&](uint32_t dst, const CUtensorMap *map, int x, int y) {
+              if (PAIR) tma_load_2d_pair(dst, map, fb, x, y); else tma_load_2d(dst, map, fb, x, y);
+            };
+            if (A_MN) {
 #pragma unroll
-            for (int i = 0; i < GBM / 64; i++) load(a_dst + i * 8192, &tmap_a, m0 + i * 64, k0);
-          } else {
-            load(a_dst, &tmap_a, k0, m0);
-          }
-          if (B_MN) {
+              for (int i = 0; i < GBM / 64; i++) load(a_dst + i * 8192, &tmap_a, m0 + i * 64, k0);
+            } else {
+              load(a_dst, &tmap_a, k0, m0);
+            }
+            if (B_MN) {
 #pragma unroll
-            for (int i = 0; i < L::B_ROWS / 64; i++) load(b_dst + i * 8192, &tmap_b, n0 + i * 64, k0);
-          } else {
-            load(b_dst, &tmap_b, k0, n0);
+              for (int i = 0; i < L::B_ROWS / 64; i++) load(b_dst + i * 8192, &tmap_b, n0 + i * 64, k0);
+            } else {
+              load(b_dst, &tmap_b, k0, n0);
+            }
           }
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
-    // ── MMA issuer (the leader's, for a pair) ──────────────────────────────
-    if (lane == 0 && rank == 0) {
+    // ── MMA issuer (the leader's, for a pair): warp-uniform loop, one lane issues ─────────
+    if (rank == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(TILE_M, BN, A_MN, B_MN);
       int stage = 0;
       uint32_t phase = 0;
@@ -387,21 +392,27 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
           tc_fence_after();
           const uint32_t a_s = a_base + stage * L::A_BYTES;
           const uint32_t b_s = b_base + stage * L::B_BYTES;
+          uint64_t adesc[GBK / 16], bdesc[GBK / 16];
 #pragma unroll
           for (int k = 0; k < GBK / 16; k++) {
-            const uint64_t adesc = A_MN ? make_smem_desc(a_s + k * 2048, 8192, 1024)
-                                        : make_smem_desc(a_s + k * 32, 16, 1024);
-            const uint64_t bdesc = B_MN ? make_smem_desc(b_s + k * 2048, 8192, 1024)
-                                        : make_smem_desc(b_s + k * 32, 16, 1024);
-            if (PAIR) mma_bf16_ss_pair(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            else mma_bf16_ss(d_tmem, adesc, bdesc, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+            adesc[k] = A_MN ? make_smem_desc(a_s + k * 2048, 8192, 1024) : make_smem_desc(a_s + k * 32, 16, 1024);
+            bdesc[k] = B_MN ? make_smem_desc(b_s + k * 2048, 8192, 1024) : make_smem_desc(b_s + k * 32, 16, 1024);
           }
-          // frees the stage (in both CTAs) once these MMAs have read it
-          if (PAIR) mma_commit_pair(empty_bar(stage)); else mma_commit(empty_bar(stage));
+          const uint32_t first = kb > kb0 ? 1u : 0u;
+          if (elect_one()) {
+#pragma unroll
+            for (int k = 0; k < GBK / 16; k++) {
+              if (PAIR) mma_bf16_ss_pair(d_tmem, adesc[k], bdesc[k], idesc, k > 0 ? 1u : first);
+              else mma_bf16_ss(d_tmem, adesc[k], bdesc[k], idesc, k > 0 ? 1u : first);
+            }
+            // frees the stage (in both CTAs) once these MMAs have read it
+            if (PAIR) mma_commit_pair(empty_bar(stage)); else mma_commit(empty_bar(stage));
+            if (kb == kb1 - 1) {  // accumulator complete
+              if (PAIR) mma_commit_pair(tfull_bar(acc)); else mma_commit(tfull_bar(acc));
+            }
+          }
+          __syncwarp();
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        }
-        if (ok) {  // accumulator complete
-          if (PAIR) mma_commit_pair(tfull_bar(acc)); else mma_commit(tfull_bar(acc));
         }
       }
     }

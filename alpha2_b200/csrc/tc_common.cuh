@@ -71,6 +71,19 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(x), "r"(y)
       : "memory");
 }
+// One lane of the (converged) warp is chosen; the rest skip the guarded statement.  The
+// single-thread instructions (TMA, tcgen05.mma, tcgen05.commit) are issued this way from code
+// that the whole warp executes, so that addresses and descriptors stay warp-uniform values.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ── CTA pairs (cluster of two, tcgen05 cta_group::2) ────────────────────────────────────────
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;
