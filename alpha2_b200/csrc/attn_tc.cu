@@ -95,56 +95,68 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   const uint32_t tS = tmem_base, tO = tmem_base + 128;
 
   if (warp == 0) {
-    if (lane == 0) {
+    // TMA producer: the warp runs the loop, one elected lane issues
+    if (elect_one()) {
       tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
       mbar_expect_tx(q_full, AT_TILE);
       tma_load_4d(sb + AF_Q, &tmap_q, q_full, 0, q0, h, b);
-      for (int j = 0; j < nb; j++) {
-        const int st = j & 1;
-        const uint32_t ph = (j >> 1) & 1;
-        if (!mbar_wait(k_empty0 + 8 * st, ph ^ 1, abort_flag)) break;
+    }
+    __syncwarp();
+    for (int j = 0; j < nb; j++) {
+      const int st = j & 1;
+      const uint32_t ph = (j >> 1) & 1;
+      if (!mbar_wait(k_empty0 + 8 * st, ph ^ 1, abort_flag)) break;
+      if (elect_one()) {
         mbar_expect_tx(k_full0 + 8 * st, AT_TILE);
         tma_load_4d(sb + AF_K + st * AT_TILE, &tmap_k, k_full0 + 8 * st, 0, j * 128, h, b);
-        if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag)) break;
+      }
+      __syncwarp();
+      if (!mbar_wait(v_empty, (j & 1) ^ 1, abort_flag)) break;
+      if (elect_one()) {
         mbar_expect_tx(v_full, AT_TILE);
         tma_load_4d(sb + AF_V, &tmap_v, v_full, 0, j * 128, h, b);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      auto issue_pv = [&](int j) -> bool {  // O (+)= P(j) V(j)
-        if (!mbar_wait(p_ready, j & 1, abort_flag)) return false;
-        if (!mbar_wait(v_full, j & 1, abort_flag)) return false;
-        tc_fence_after();
+    // MMA issuer: warp-uniform control flow and descriptors, one elected lane issues
+    constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
+    const uint64_t d_q = make_smem_desc(sb + AF_Q, 16, 1024), d_k = make_smem_desc(sb + AF_K, 16, 1024);
+    const uint64_t d_p = make_smem_desc(sb + AF_P, 16, 1024), d_v = make_smem_desc(sb + AF_V, AT_TILE, 1024);
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    auto issue_pv = [&](int j) -> bool {  // O (+)= P(j) V(j)
+      if (!mbar_wait(p_ready, j & 1, abort_flag)) return false;
+      if (!mbar_wait(v_full, j & 1, abort_flag)) return false;
+      tc_fence_after();
+      const uint32_t first = j > 0 ? 1u : 0u;
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++) {
-          const uint64_t adesc = make_smem_desc(sb + AF_P + (kk >> 2) * AT_TILE + (kk & 3) * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sb + AF_V + kk * 2048, AT_TILE, 1024);
-          mma_bf16_ss(tO, adesc, bdesc, idesc_pv, (j > 0 || kk > 0) ? 1u : 0u);
-        }
+        for (int kk = 0; kk < 8; kk++)
+          mma_bf16_ss(tO, d_p + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), d_v + kk * 128, idesc_pv,
+                      kk > 0 ? 1u : first);
         mma_commit(v_empty);
         mma_commit(pv_done);
-        return true;
-      };
-      for (int j = 0; j < nb && ok; j++) {
-        if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
-        const int st = j & 1;
-        if (!mbar_wait(k_full0 + 8 * st, (j >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
+      }
+      __syncwarp();
+      return true;
+    };
+    for (int j = 0; j < nb && ok; j++) {
+      if (j > 0 && !issue_pv(j - 1)) { ok = false; break; }
+      const int st = j & 1;
+      if (!mbar_wait(k_full0 + 8 * st, (j >> 1) & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const uint64_t kd = d_k + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t freed = k_empty0 + 8 * st;
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++) {
-          const uint64_t adesc = make_smem_desc(sb + AF_Q + kk * 32, 16, 1024);
-          const uint64_t bdesc = make_smem_desc(sb + AF_K + st * AT_TILE + kk * 32, 16, 1024);
-          mma_bf16_ss(tS, adesc, bdesc, idesc_qk, kk > 0 ? 1u : 0u);
-        }
-        mma_commit(k_empty0 + 8 * st);
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tS, d_q + kk * 2, kd + kk * 2, idesc_qk, kk > 0 ? 1u : 0u);
+        mma_commit(freed);
         mma_commit(s_full);
       }
-      if (ok) issue_pv(nb - 1);
+      __syncwarp();
     }
+    if (ok) issue_pv(nb - 1);
   } else {
     // ── softmax warps: thread <-> query row <-> TMEM lane ────────────────────
     const int quad = warp & 3;
@@ -518,65 +530,77 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdV = tmem_base + 384, tdK = tmem_base + 448;
 
   if (warp == 0) {
-    if (lane == 0) {
+    // TMA producer: the warp runs the loop, one elected lane issues
+    if (elect_one()) {
       mbar_expect_tx(kv_full, 2 * AT_TILE);
       tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, k0, h, b);
       tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, k0, h, b);
-      for (int it = 0; it < n_it; it++) {
-        const int st = it % AK_STAGES;
-        if (!mbar_wait(q_empty0 + 8 * st, ((it / AK_STAGES) & 1) ^ 1, abort_flag)) break;
+    }
+    __syncwarp();
+    for (int it = 0; it < n_it; it++) {
+      const int st = it % AK_STAGES;
+      if (!mbar_wait(q_empty0 + 8 * st, ((it / AK_STAGES) & 1) ^ 1, abort_flag)) break;
+      const int q0 = (kb + it) * 128;
+      if (elect_one()) {
         mbar_expect_tx(q_full0 + 8 * st, 2 * AT_TILE);
-        const int q0 = (kb + it) * 128;
         tma_load_4d(sb + AK_Q + st * AT_TILE, &tmap_q, q_full0 + 8 * st, 0, q0, h, b);
         tma_load_4d(sb + AK_DO + st * AT_TILE, &tmap_do, q_full0 + 8 * st, 0, q0, h, b);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [q x k] = A[q,d] B[k,d]^T
-      constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, true, true);      // [k x d] = A[q,k]^T B[q,d]
-      auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer it & 1 (waits for the tile's loads)
-        const int st = it % AK_STAGES;
-        if (!mbar_wait(q_full0 + 8 * st, (it / AK_STAGES) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t qs = sb + AK_Q + st * AT_TILE;
+    // MMA issuer: warp-uniform control flow and descriptors, one elected lane issues
+    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [q x k] = A[q,d] B[k,d]^T
+    constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, true, true);      // [k x d] = A[q,k]^T B[q,d]
+    const uint64_t d_k = make_smem_desc(sb + AK_K, 16, 1024), d_v = make_smem_desc(sb + AK_V, 16, 1024);
+    const uint64_t d_q_k = make_smem_desc(sb + AK_Q, 16, 1024), d_do_k = make_smem_desc(sb + AK_DO, 16, 1024);
+    const uint64_t d_q_n = make_smem_desc(sb + AK_Q, AT_TILE, 1024), d_do_n = make_smem_desc(sb + AK_DO, AT_TILE, 1024);
+    const uint64_t d_p = make_smem_desc(sb + AK_P, AT_TILE, 1024), d_ds = make_smem_desc(sb + AK_DS, AT_TILE, 1024);
+    auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer it & 1 (waits for the tile's loads)
+      const int st = it % AK_STAGES;
+      if (!mbar_wait(q_full0 + 8 * st, (it / AK_STAGES) & 1, abort_flag)) return false;
+      tc_fence_after();
+      const uint64_t qd = d_q_k + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t t = tS0 + (it & 1) * 128, done = s_full0 + 8 * (it & 1);
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tS0 + (it & 1) * 128, make_smem_desc(qs + kk * 32, 16, 1024),
-                      make_smem_desc(sb + AK_K + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(s_full0 + 8 * (it & 1));
-        return true;
-      };
-      auto issue_dp = [&](int it) {          // dP(it) = dO(it) V^T (loads already awaited by issue_s(it))
-        const uint32_t dos = sb + AK_DO + (it % AK_STAGES) * AT_TILE;
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(t, qd + kk * 2, d_k + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(done);
+      }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](int it) {          // dP(it) = dO(it) V^T (loads already awaited by issue_s(it))
+      const uint64_t dd = d_do_k + (uint64_t)(((it % AK_STAGES) * AT_TILE) >> 4);
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tdP, make_smem_desc(dos + kk * 32, 16, 1024), make_smem_desc(sb + AK_V + kk * 32, 16, 1024),
-                      idesc_s, kk > 0 ? 1u : 0u);
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, dd + kk * 2, d_v + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
         mma_commit(dp_full);
-      };
-      bool ok = mbar_wait(kv_full, 0, abort_flag);
-      if (ok) ok = issue_s(0);
-      if (ok) issue_dp(0);
-      if (ok && n_it > 1) ok = issue_s(1);
-      for (int it = 0; it < n_it && ok; it++) {
-        if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        if (it + 1 < n_it) issue_dp(it + 1);
-        const int st = it % AK_STAGES;
-        const uint32_t qs = sb + AK_Q + st * AT_TILE, dos = sb + AK_DO + st * AT_TILE;
+      }
+      __syncwarp();
+    };
+    bool ok = mbar_wait(kv_full, 0, abort_flag);
+    if (ok) ok = issue_s(0);
+    if (ok) issue_dp(0);
+    if (ok && n_it > 1) ok = issue_s(1);
+    for (int it = 0; it < n_it && ok; it++) {
+      if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (it + 1 < n_it) issue_dp(it + 1);
+      const int st = it % AK_STAGES;
+      const uint64_t qn = d_q_n + (uint64_t)((st * AT_TILE) >> 4), don = d_do_n + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t first = it > 0 ? 1u : 0u, freed = q_empty0 + 8 * st;
+      if (elect_one()) {
 #pragma unroll
         for (int kk = 0; kk < 8; kk++)  // 16 query rows per step
-          mma_bf16_ss(tdV, make_smem_desc(sb + AK_P + kk * 2048, AT_TILE, 1024), make_smem_desc(dos + kk * 2048, AT_TILE, 1024),
-                      idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
+          mma_bf16_ss(tdV, d_p + kk * 128, don + kk * 128, idesc_g, kk > 0 ? 1u : first);
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++)
-          mma_bf16_ss(tdK, make_smem_desc(sb + AK_DS + kk * 2048, AT_TILE, 1024), make_smem_desc(qs + kk * 2048, AT_TILE, 1024),
-                      idesc_g, (it > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(q_empty0 + 8 * st);
+        for (int kk = 0; kk < 8; kk++) mma_bf16_ss(tdK, d_ds + kk * 128, qn + kk * 128, idesc_g, kk > 0 ? 1u : first);
+        mma_commit(freed);
         mma_commit(acc_done);
-        if (it + 2 < n_it) ok = issue_s(it + 2);
       }
+      __syncwarp();
+      if (it + 2 < n_it) ok = issue_s(it + 2);
     }
   } else {
     const int quad = warp & 3, half = (warp - 2) >> 2;
@@ -710,60 +734,73 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdQ = tmem_base + 384;
 
   if (warp == 0) {
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_expect_tx(q_full, 2 * AT_TILE);
       tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, q0, h, b);
       tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, q0, h, b);
-      for (int j = 0; j < nb; j++) {
-        const int st = j % AQ_STAGES;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((j / AQ_STAGES) & 1) ^ 1, abort_flag)) break;
+    }
+    __syncwarp();
+    for (int j = 0; j < nb; j++) {
+      const int st = j % AQ_STAGES;
+      if (!mbar_wait(kv_empty0 + 8 * st, ((j / AQ_STAGES) & 1) ^ 1, abort_flag)) break;
+      if (elect_one()) {
         mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
         tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
         tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
       }
+      __syncwarp();
     }
   } else if (warp == 1) {
-    if (lane == 0) {
-      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-      constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);     // [q x d] = A[q,k] B[k,d]
-      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer j & 1 (waits for the tile's loads)
-        const int st = j % AQ_STAGES;
-        if (!mbar_wait(kv_full0 + 8 * st, (j / AQ_STAGES) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint32_t ks = sb + AQ_K + st * AT_TILE;
+    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);     // [q x d] = A[q,k] B[k,d]
+    const uint64_t d_q = make_smem_desc(sb + AQ_Q, 16, 1024), d_do = make_smem_desc(sb + AQ_DO, 16, 1024);
+    const uint64_t d_k_k = make_smem_desc(sb + AQ_K, 16, 1024), d_v_k = make_smem_desc(sb + AQ_V, 16, 1024);
+    const uint64_t d_k_n = make_smem_desc(sb + AQ_K, AT_TILE, 1024);
+    const uint64_t d_ds = make_smem_desc(sb + AQ_DS, 16, 1024);
+    auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer j & 1 (waits for the tile's loads)
+      const int st = j % AQ_STAGES;
+      if (!mbar_wait(kv_full0 + 8 * st, (j / AQ_STAGES) & 1, abort_flag)) return false;
+      tc_fence_after();
+      const uint64_t kd = d_k_k + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t t = tS0 + (j & 1) * 128, done = s_full0 + 8 * (j & 1);
+      if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tS0 + (j & 1) * 128, make_smem_desc(sb + AQ_Q + kk * 32, 16, 1024),
-                      make_smem_desc(ks + kk * 32, 16, 1024), idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(s_full0 + 8 * (j & 1));
-        return true;
-      };
-      auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
-        const uint32_t vs = sb + AQ_V + (j % AQ_STAGES) * AT_TILE;
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++)
-          mma_bf16_ss(tdP, make_smem_desc(sb + AQ_DO + kk * 32, 16, 1024), make_smem_desc(vs + kk * 32, 16, 1024), idesc_s,
-                      kk > 0 ? 1u : 0u);
-        mma_commit(dp_full);
-      };
-      bool ok = mbar_wait(q_full, 0, abort_flag);
-      if (ok) ok = issue_s(0);
-      if (ok) issue_dp(0);
-      if (ok && nb > 1) ok = issue_s(1);
-      for (int j = 0; j < nb && ok; j++) {
-        if (!mbar_wait(ds_ready, j & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        if (j + 1 < nb) issue_dp(j + 1);
-        const int st = j % AQ_STAGES;
-        const uint32_t ks = sb + AQ_K + st * AT_TILE;
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++)  // 16 keys per step
-          mma_bf16_ss(tdQ, make_smem_desc(sb + AQ_DS + (kk >> 2) * AT_TILE + (kk & 3) * 32, 16, 1024),
-                      make_smem_desc(ks + kk * 2048, AT_TILE, 1024), idesc_q, (j > 0 || kk > 0) ? 1u : 0u);
-        mma_commit(kv_empty0 + 8 * st);
-        mma_commit(acc_done);
-        if (j + 2 < nb) ok = issue_s(j + 2);
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(t, d_q + kk * 2, kd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(done);
       }
+      __syncwarp();
+      return true;
+    };
+    auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
+      const uint64_t vd = d_v_k + (uint64_t)(((j % AQ_STAGES) * AT_TILE) >> 4);
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, d_do + kk * 2, vd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+        mma_commit(dp_full);
+      }
+      __syncwarp();
+    };
+    bool ok = mbar_wait(q_full, 0, abort_flag);
+    if (ok) ok = issue_s(0);
+    if (ok) issue_dp(0);
+    if (ok && nb > 1) ok = issue_s(1);
+    for (int j = 0; j < nb && ok; j++) {
+      if (!mbar_wait(ds_ready, j & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      if (j + 1 < nb) issue_dp(j + 1);
+      const int st = j % AQ_STAGES;
+      const uint64_t kn = d_k_n + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t first = j > 0 ? 1u : 0u, freed = kv_empty0 + 8 * st;
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 8; kk++)  // 16 keys per step; dS tile (kk >> 2), 32 bytes per step inside it
+          mma_bf16_ss(tdQ, d_ds + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), kn + kk * 128, idesc_q,
+                      kk > 0 ? 1u : first);
+        mma_commit(freed);
+        mma_commit(acc_done);
+      }
+      __syncwarp();
+      if (j + 2 < nb) ok = issue_s(j + 2);
     }
   } else {
     const int quad = warp & 3, half = (warp - 2) >> 2;
