@@ -294,7 +294,7 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 //   dK/dV kernel: CTA = (batch, head, 128 keys), loops over the query blocks at or after it;
 //   dQ    kernel: CTA = (batch, head, 128 queries), loops over the key blocks at or before it.
 // Per (query block, key block) pair both recompute S = Q K^T and dP = dO V^T on the tensor
-// cores into TMEM; eight math warps (32 query rows x 64 key columns each) turn them into
+// cores into TMEM; sixteen math warps (32 query rows x 32 key columns each) turn them into
 // P = exp2(x2 - lse2) and dS = P*(dP - D)*(1 - tanh^2)*scale, round to bf16 and store them as
 // [query rows][key columns] 128B-swizzled tiles.  That one layout serves both remaining
 // products: read K-major it is the A operand of dQ += dS K, read M-major it is the A operand
@@ -344,9 +344,9 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
 }
 
 // ── backward math warps ─────────────────────────────────────────────────────────────────
-// Eight math warps work on one 128 x 128 (query x key) tile: warp w owns the TMEM lane
-// quadrant w % 4 (32 query rows, one per thread) and the key-column half (w - 2) / 4, so a
-// thread handles 64 scores.  The work is split in two phases so that the tensor core can run
+// Sixteen math warps work on one 128 x 128 (query x key) tile: warp w owns the TMEM lane
+// quadrant w % 4 (32 query rows, one per thread) and the key-column quarter (w - 2) / 4, so a
+// thread handles 32 scores and an SM sub-partition has four math warps to switch between.  The work is split in two phases so that the tensor core can run
 // ahead: phase A needs only S (scores -> P and the factor P * (1 - tanh^2)), phase B needs dP
 // (-> dS) and stores the bf16 P / dS rows into the 128B-swizzled tiles.
 //
@@ -354,29 +354,30 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
 // (x + x^3 (p1 + p2 x^2 + p3 x^4 + p4 x^6), truncation error < 5e-6), which halves the load
 // on the special-function unit that exp2 also needs; a warp whose tile holds a larger
 // argument redoes the tile with the hardware tanh.
-constexpr int AB_THREADS = 320;            // TMA warp, MMA warp, 8 math warps
+constexpr int AB_MATH_WARPS = 16;
+constexpr int AB_THREADS = 64 + 32 * AB_MATH_WARPS;  // TMA warp, MMA warp, math warps
+constexpr int AB_NC = 128 / (AB_MATH_WARPS / 4);     // score columns per math thread (32)
 constexpr float TANH_POLY_LIMIT2 = 0.25f;  // x^2 bound of the polynomial branch
 
 struct BwdRowConsts {
   float c1, c2, lse2, scale, delta;
 };
 
-// Phase A for 64 scores of one row.  pk: P as 32 packed bf16 pairs; f0: P * dcap (fp32).
+// Phase A for AB_NC scores of one row.  pk: P as packed bf16 pairs; f0: P * dcap (fp32).
 // Returns the largest squared tanh argument seen (0 when not capped).
 template <bool DIAG, bool CAPPED, bool POLY>
 __device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, bool row_valid, const BwdRowConsts &k,
-                                             uint32_t (&pk)[32], float (&f0)[64]) {
-  uint32_t r0[32], r1[32];
+                                             uint32_t (&pk)[AB_NC / 2], float (&f0)[AB_NC]) {
+  static_assert(AB_NC == 32, "one 32-column tensor-memory load per phase");
+  uint32_t r0[32];
   tmem_ld_32x32(t_s, r0);
-  tmem_ld_32x32(t_s + 32, r1);
   tmem_ld_wait();
   float big = 0.f;
   const uint64_t c1 = f2_pack(k.c1, k.c1), c2 = f2_pack(k.c2, k.c2), nl = f2_pack(-k.lse2, -k.lse2);
   const uint64_t one = f2_pack(1.f, 1.f);
 #pragma unroll
-  for (int i = 0; i < 64; i += 2) {
-    const uint32_t a = i < 32 ? r0[i] : r1[i - 32], b = i < 32 ? r0[i + 1] : r1[i - 31];
-    const uint64_t s = f2_pack(__uint_as_float(a), __uint_as_float(b));
+  for (int i = 0; i < AB_NC; i += 2) {
+    const uint64_t s = f2_pack(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
     uint64_t e, dcap = one;
     if (CAPPED) {
       const uint64_t x = f2_mul(s, c1);
@@ -419,41 +420,38 @@ __device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, bo
   return big;
 }
 
-// Phase B: dS = f0 * (dP - delta) * scale for the same 64 columns, then the row's P (optional)
-// and dS chunks go to shared memory.  p_half / ds_half point at this thread's 128-byte row in
-// the 64-column tile of its column half.
+// Phase B: dS = f0 * (dP - delta) * scale for the same columns, then the row's P (optional)
+// and dS chunks go to shared memory.  p_row / ds_row point at this thread's 128-byte row in
+// the 64-column tile that holds its columns; chunk0 is its first 16-byte chunk there (0 or 4).
 template <bool WRITE_P>
-__device__ __forceinline__ void bwd_phase_b(uint32_t t_dp, int row, const BwdRowConsts &k, const uint32_t (&pk)[32],
-                                            const float (&f0)[64], uint8_t *p_half, uint8_t *ds_half) {
+__device__ __forceinline__ void bwd_phase_b(uint32_t t_dp, int row, int chunk0, const BwdRowConsts &k,
+                                            const uint32_t (&pk)[AB_NC / 2], const float (&f0)[AB_NC], uint8_t *p_row,
+                                            uint8_t *ds_row) {
   const uint64_t sc = f2_pack(k.scale, k.scale), nd = f2_pack(-k.delta * k.scale, -k.delta * k.scale);
+  uint32_t d[32];
+  tmem_ld_32x32(t_dp, d);
+  tmem_ld_wait();
+  uint32_t dd[16];
 #pragma unroll
-  for (int c = 0; c < 2; c++) {
-    uint32_t d[32];
-    tmem_ld_32x32(t_dp + c * 32, d);
-    tmem_ld_wait();
-    uint32_t dd[16];
+  for (int i = 0; i < 32; i += 2) {
+    const uint64_t g = f2_fma(f2_pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), sc, nd);
+    float da, db;
+    f2_unpack(f2_mul(f2_pack(f0[i], f0[i + 1]), g), da, db);
+    dd[i >> 1] = bf16x2_pack(da, db);
+  }
 #pragma unroll
-    for (int i = 0; i < 32; i += 2) {
-      const uint64_t g = f2_fma(f2_pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), sc, nd);
-      float da, db;
-      f2_unpack(f2_mul(f2_pack(f0[c * 32 + i], f0[c * 32 + i + 1]), g), da, db);
-      dd[i >> 1] = bf16x2_pack(da, db);
-    }
-#pragma unroll
-    for (int q = 0; q < 4; q++) {
-      const int off = ((c * 4 + q) ^ (row & 7)) * 16;
-      if (WRITE_P)
-        *reinterpret_cast<uint4 *>(p_half + off) =
-            make_uint4(pk[c * 16 + 4 * q], pk[c * 16 + 4 * q + 1], pk[c * 16 + 4 * q + 2], pk[c * 16 + 4 * q + 3]);
-      *reinterpret_cast<uint4 *>(ds_half + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
-    }
+  for (int q = 0; q < 4; q++) {
+    const int off = ((chunk0 + q) ^ (row & 7)) * 16;
+    if (WRITE_P)
+      *reinterpret_cast<uint4 *>(p_row + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+    *reinterpret_cast<uint4 *>(ds_row + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
   }
 }
 
 // Phase A with the branch selection: diagonal tile or not, capped or not, and for capped
 // scores the polynomial tanh unless some argument in the warp's part of the tile is too large.
 __device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0, bool diag, bool capped, bool row_valid,
-                                                const BwdRowConsts &k, uint32_t (&pk)[32], float (&f0)[64]) {
+                                                const BwdRowConsts &k, uint32_t (&pk)[AB_NC / 2], float (&f0)[AB_NC]) {
   if (!capped) {
     if (diag) bwd_phase_a<true, false, false>(t_s, row, col0, row_valid, k, pk, f0);
     else bwd_phase_a<false, false, false>(t_s, row, col0, row_valid, k, pk, f0);
@@ -509,7 +507,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     mbar_init(kv_full, 1);
     mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
     mbar_init(dp_full, 1);
-    mbar_init(pds_ready, 8);
+    mbar_init(pds_ready, AB_MATH_WARPS);
     mbar_init(acc_done, 1);
     for (int s = 0; s < AK_STAGES; s++) {
       mbar_init(q_full0 + 8 * s, 1);
@@ -603,7 +601,8 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       if (it + 2 < n_it) ok = issue_s(it + 2);
     }
   } else {
-    const int quad = warp & 3, half = (warp - 2) >> 2;
+    const int quad = warp & 3, colq = (warp - 2) >> 2;  // lane quadrant, 32-column quarter
+    const int col0 = colq * AB_NC;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
@@ -612,24 +611,24 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
     k.c2 = a.cap * LOG2E;
     k.scale = a.scale;
-    uint8_t *p_half = smem + AK_P + half * AT_TILE + row * 128;
-    uint8_t *ds_half = smem + AK_DS + half * AT_TILE + row * 128;
+    uint8_t *p_row = smem + AK_P + (colq >> 1) * AT_TILE + row * 128;
+    uint8_t *ds_row = smem + AK_DS + (colq >> 1) * AT_TILE + row * 128;
     bool ok = true;
     for (int it = 0; it < n_it && ok; it++) {
       const int qi = (kb + it) * 128 + row;
       const bool valid = qi < a.T;
       k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
       k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-      uint32_t pk[32];
-      float f0[64];
+      uint32_t pk[AB_NC / 2];
+      float f0[AB_NC];
       if (!mbar_wait(s_full0 + 8 * (it & 1), (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + half * 64, row, half * 64, it == 0, capped, valid, k, pk, f0);
+      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + col0, row, col0, it == 0, capped, valid, k, pk, f0);
       if (!mbar_wait(dp_full, it & 1, abort_flag)) { ok = false; break; }
       // the gradient products of the previous tile must have finished reading the P / dS tiles
       if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_b<true>(tdP + lane_off + half * 64, row, k, pk, f0, p_half, ds_half);
+      bwd_phase_b<true>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, f0, p_row, ds_row);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
@@ -637,25 +636,23 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     }
     if (ok && mbar_wait(acc_done, (n_it - 1) & 1, abort_flag)) {
       tc_fence_after();
-      const int kj = k0 + row;  // accumulator lanes are keys; column half 0 stores dV, half 1 dK
+      // accumulator lanes are keys; the four column quarters store dV[0:32], dV[32:64], dK[0:32], dK[32:64]
+      const int kj = k0 + row, c = colq & 1;
       const int64_t off = (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)kj * a.q_st;
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)(half ? a.dk : a.dv) + off;
-      const uint32_t tacc = half ? tdK : tdV;
-#pragma unroll 1
-      for (int c = 0; c < 2; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(tacc + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (kj < a.T) {
+      __nv_bfloat16 *dst = (__nv_bfloat16 *)((colq >> 1) ? a.dk : a.dv) + off;
+      const uint32_t tacc = (colq >> 1) ? tdK : tdV;
+      uint32_t r[32];
+      tmem_ld_32x32(tacc + lane_off + c * 32, r);
+      tmem_ld_wait();
+      if (kj < a.T) {
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            float f[8];
+        for (int q = 0; q < 4; q++) {
+          float f[8];
 #pragma unroll
-            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-            Vec16<__nv_bfloat16> v;
-            v.set(f);
-            v.store(dst + c * 32 + q * 8);
-          }
+          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+          Vec16<__nv_bfloat16> v;
+          v.set(f);
+          v.store(dst + c * 32 + q * 8);
         }
       }
     }
@@ -713,7 +710,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     mbar_init(q_full, 1);
     mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
     mbar_init(dp_full, 1);
-    mbar_init(ds_ready, 8);
+    mbar_init(ds_ready, AB_MATH_WARPS);
     mbar_init(acc_done, 1);
     for (int s = 0; s < AQ_STAGES; s++) {
       mbar_init(kv_full0 + 8 * s, 1);
@@ -803,7 +800,8 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
       if (j + 2 < nb) ok = issue_s(j + 2);
     }
   } else {
-    const int quad = warp & 3, half = (warp - 2) >> 2;
+    const int quad = warp & 3, colq = (warp - 2) >> 2;  // lane quadrant, 32-column quarter
+    const int col0 = colq * AB_NC;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
@@ -816,19 +814,19 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     k.scale = a.scale;
     k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
     k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-    uint8_t *ds_half = smem + AQ_DS + half * AT_TILE + row * 128;
+    uint8_t *ds_row = smem + AQ_DS + (colq >> 1) * AT_TILE + row * 128;
     bool ok = true;
     for (int j = 0; j < nb && ok; j++) {
-      uint32_t pk[32];
-      float f0[64];
+      uint32_t pk[AB_NC / 2];
+      float f0[AB_NC];
       if (!mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + half * 64, row, half * 64, j == qb, capped, valid, k, pk, f0);
+      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, valid, k, pk, f0);
       if (!mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
       // dQ += dS(j-1) K(j-1) must have finished reading the dS tiles
       if (j > 0 && !mbar_wait(acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_b<false>(tdP + lane_off + half * 64, row, k, pk, f0, nullptr, ds_half);
+      bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, f0, nullptr, ds_row);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
@@ -836,13 +834,15 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     }
     if (ok && mbar_wait(acc_done, (nb - 1) & 1, abort_flag)) {
       tc_fence_after();
-      // dQ is 64 columns: each column half of the math warps stores 32 of them
+      // dQ is 64 columns: the first two column quarters of the math warps store 32 each
       __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st +
-                           half * 32;
+                           (colq & 1) * 32;
       uint32_t r[32];
-      tmem_ld_32x32(tdQ + lane_off + half * 32, r);
-      tmem_ld_wait();
-      if (valid) {
+      if (colq < 2) {  // warp-uniform
+        tmem_ld_32x32(tdQ + lane_off + colq * 32, r);
+        tmem_ld_wait();
+      }
+      if (valid && colq < 2) {
 #pragma unroll
         for (int q = 0; q < 4; q++) {
           float f[8];
