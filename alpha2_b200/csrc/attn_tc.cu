@@ -350,118 +350,130 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
 // ahead: phase A needs only S (scores -> P and the factor P * (1 - tanh^2)), phase B needs dP
 // (-> dS) and stores the bf16 P / dS rows into the 128B-swizzled tiles.
 //
-// Soft cap: tanh(x) for |x| <= 1/2 comes from an odd polynomial on the FMA pipes
-// (x + x^3 (p1 + p2 x^2 + p3 x^4 + p4 x^6), truncation error < 5e-6), which halves the load
+// Soft cap: tanh(x) for |x| <= 0.35 comes from an odd polynomial on the FMA pipes
+// (x + x^3 (p1 + p2 x^2 + p3 x^4), truncation error < 2e-6), which halves the load
 // on the special-function unit that exp2 also needs; a warp whose tile holds a larger
 // argument redoes the tile with the hardware tanh.
 constexpr int AB_MATH_WARPS = 16;
 constexpr int AB_THREADS = 64 + 32 * AB_MATH_WARPS;  // TMA warp, MMA warp, math warps
 constexpr int AB_NC = 128 / (AB_MATH_WARPS / 4);     // score columns per math thread (32)
-constexpr float TANH_POLY_LIMIT2 = 0.25f;  // x^2 bound of the polynomial branch
+constexpr float TANH_POLY_LIMIT2 = 0.1225f;  // x^2 bound of the polynomial branch (|x| <= 0.35)
 
 struct BwdRowConsts {
-  float c1, c2, lse2, scale, delta;
+  float c1, c2, lse2, scale, delta;  // lse2 = +inf for a query row past the end (its P becomes 0)
 };
 
-// Phase A for AB_NC scores of one row.  pk: P as packed bf16 pairs; f0: P * dcap (fp32).
+// Phase A for AB_NC scores of one row.  pk: P as packed bf16 pairs; fk: -P * dcap as packed
+// bf16 pairs (dcap = 1 - tanh^2, or 1 without a cap).  The scores are read 16 columns at a
+// time to keep registers free for interleaving the per-pair dependency chains.
 // Returns the largest squared tanh argument seen (0 when not capped).
 template <bool DIAG, bool CAPPED, bool POLY>
-__device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, bool row_valid, const BwdRowConsts &k,
-                                             uint32_t (&pk)[AB_NC / 2], float (&f0)[AB_NC]) {
-  static_assert(AB_NC == 32, "one 32-column tensor-memory load per phase");
-  uint32_t r0[32];
-  tmem_ld_32x32(t_s, r0);
-  tmem_ld_wait();
+__device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, const BwdRowConsts &k,
+                                             uint32_t (&pk)[AB_NC / 2], uint32_t (&fk)[AB_NC / 2]) {
   float big = 0.f;
   const uint64_t c1 = f2_pack(k.c1, k.c1), c2 = f2_pack(k.c2, k.c2), nl = f2_pack(-k.lse2, -k.lse2);
-  const uint64_t one = f2_pack(1.f, 1.f);
+  const uint64_t m1 = f2_pack(-1.f, -1.f);
+  const uint64_t p1 = f2_pack(-0.3333333333f, -0.3333333333f), p2 = f2_pack(0.1333333333f, 0.1333333333f),
+                 p3 = f2_pack(-0.0539682540f, -0.0539682540f);
 #pragma unroll
-  for (int i = 0; i < AB_NC; i += 2) {
-    const uint64_t s = f2_pack(__uint_as_float(r0[i]), __uint_as_float(r0[i + 1]));
-    uint64_t e, dcap = one;
-    if (CAPPED) {
-      const uint64_t x = f2_mul(s, c1);
-      uint64_t th;
-      if (POLY) {
-        const uint64_t x2 = f2_mul(x, x);
-        float xa, xb;
-        f2_unpack(x2, xa, xb);
-        big = fmaxf(big, fmaxf(xa, xb));
-        uint64_t t = f2_fma(x2, f2_pack(0.0218694885f, 0.0218694885f), f2_pack(-0.0539682540f, -0.0539682540f));
-        t = f2_fma(t, x2, f2_pack(0.1333333333f, 0.1333333333f));
-        t = f2_fma(t, x2, f2_pack(-0.3333333333f, -0.3333333333f));
-        th = f2_fma(f2_mul(x, x2), t, x);
+  for (int part = 0; part < AB_NC / 16; part++) {
+    uint32_t r[16];
+    tmem_ld_32x16(t_s + part * 16, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const uint64_t s = f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      uint64_t e, ndcap = m1;  // ndcap = tanh^2 - 1
+      if (CAPPED) {
+        const uint64_t x = f2_mul(s, c1);
+        uint64_t th;
+        if (POLY) {
+          const uint64_t x2 = f2_mul(x, x);
+          float xa, xb;
+          f2_unpack(x2, xa, xb);
+          big = fmax3(big, xa, xb);
+          uint64_t t = f2_fma(x2, p3, p2);
+          t = f2_fma(t, x2, p1);
+          th = f2_fma(f2_mul(x, x2), t, x);
+        } else {
+          float xa, xb;
+          f2_unpack(x, xa, xb);
+          th = f2_pack(tanh_approx(xa), tanh_approx(xb));
+        }
+        e = f2_fma(th, c2, nl);
+        ndcap = f2_fma(th, th, m1);
       } else {
-        float xa, xb;
-        f2_unpack(x, xa, xb);
-        th = f2_pack(tanh_approx(xa), tanh_approx(xb));
+        e = f2_fma(s, c1, nl);
       }
-      e = f2_fma(th, c2, nl);
-      dcap = f2_fma(f2_mul(th, f2_pack(-1.f, -1.f)), th, one);
-    } else {
-      e = f2_fma(s, c1, nl);
-    }
-    float ea, eb;
-    f2_unpack(e, ea, eb);
-    float pa = ex2_approx(ea), pb = ex2_approx(eb);
-    if (DIAG) {
-      if (col0 + i > row) pa = 0.f;
-      if (col0 + i + 1 > row) pb = 0.f;
-    }
-    if (!row_valid) pa = pb = 0.f;
-    pk[i >> 1] = bf16x2_pack(pa, pb);
-    if (CAPPED) {
-      f2_unpack(f2_mul(f2_pack(pa, pb), dcap), f0[i], f0[i + 1]);
-    } else {
-      f0[i] = pa;
-      f0[i + 1] = pb;
+      float ea, eb;
+      f2_unpack(e, ea, eb);
+      float pa = ex2_approx(ea), pb = ex2_approx(eb);
+      if (DIAG) {
+        const int c = col0 + part * 16 + i;
+        if (c > row) pa = 0.f;
+        if (c + 1 > row) pb = 0.f;
+      }
+      const uint32_t pp = bf16x2_pack(pa, pb);
+      pk[part * 8 + (i >> 1)] = pp;
+      if (CAPPED) {
+        float fa, fb;
+        f2_unpack(f2_mul(f2_pack(pa, pb), ndcap), fa, fb);
+        fk[part * 8 + (i >> 1)] = bf16x2_pack(fa, fb);
+      } else {
+        fk[part * 8 + (i >> 1)] = pp ^ 0x80008000u;
+      }
     }
   }
   return big;
 }
 
-// Phase B: dS = f0 * (dP - delta) * scale for the same columns, then the row's P (optional)
-// and dS chunks go to shared memory.  p_row / ds_row point at this thread's 128-byte row in
-// the 64-column tile that holds its columns; chunk0 is its first 16-byte chunk there (0 or 4).
+// Phase B: dS = (-P dcap) * (-(dP - delta) * scale) for the same columns (the second factor is
+// rounded to bf16 and the product taken in packed bf16), then the row's P (optional) and dS
+// chunks go to shared memory.  p_row / ds_row point at this thread's 128-byte row in the
+// 64-column tile that holds its columns; chunk0 is its first 16-byte chunk there (0 or 4).
 template <bool WRITE_P>
 __device__ __forceinline__ void bwd_phase_b(uint32_t t_dp, int row, int chunk0, const BwdRowConsts &k,
-                                            const uint32_t (&pk)[AB_NC / 2], const float (&f0)[AB_NC], uint8_t *p_row,
-                                            uint8_t *ds_row) {
-  const uint64_t sc = f2_pack(k.scale, k.scale), nd = f2_pack(-k.delta * k.scale, -k.delta * k.scale);
-  uint32_t d[32];
-  tmem_ld_32x32(t_dp, d);
-  tmem_ld_wait();
-  uint32_t dd[16];
+                                            const uint32_t (&pk)[AB_NC / 2], const uint32_t (&fk)[AB_NC / 2],
+                                            uint8_t *p_row, uint8_t *ds_row) {
+  const uint64_t nsc = f2_pack(-k.scale, -k.scale), ds0 = f2_pack(k.delta * k.scale, k.delta * k.scale);
 #pragma unroll
-  for (int i = 0; i < 32; i += 2) {
-    const uint64_t g = f2_fma(f2_pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), sc, nd);
-    float da, db;
-    f2_unpack(f2_mul(f2_pack(f0[i], f0[i + 1]), g), da, db);
-    dd[i >> 1] = bf16x2_pack(da, db);
-  }
+  for (int part = 0; part < AB_NC / 16; part++) {
+    uint32_t d[16];
+    tmem_ld_32x16(t_dp + part * 16, d);
+    tmem_ld_wait();
+    uint32_t dd[8];
 #pragma unroll
-  for (int q = 0; q < 4; q++) {
-    const int off = ((chunk0 + q) ^ (row & 7)) * 16;
-    if (WRITE_P)
-      *reinterpret_cast<uint4 *>(p_row + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
-    *reinterpret_cast<uint4 *>(ds_row + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+    for (int i = 0; i < 16; i += 2) {
+      float ga, gb;
+      f2_unpack(f2_fma(f2_pack(__uint_as_float(d[i]), __uint_as_float(d[i + 1])), nsc, ds0), ga, gb);
+      dd[i >> 1] = bf16x2_mul(fk[part * 8 + (i >> 1)], bf16x2_pack(ga, gb));
+    }
+#pragma unroll
+    for (int q = 0; q < 2; q++) {
+      const int off = ((chunk0 + part * 2 + q) ^ (row & 7)) * 16;
+      if (WRITE_P)
+        *reinterpret_cast<uint4 *>(p_row + off) =
+            make_uint4(pk[part * 8 + 4 * q], pk[part * 8 + 4 * q + 1], pk[part * 8 + 4 * q + 2], pk[part * 8 + 4 * q + 3]);
+      *reinterpret_cast<uint4 *>(ds_row + off) = make_uint4(dd[4 * q], dd[4 * q + 1], dd[4 * q + 2], dd[4 * q + 3]);
+    }
   }
 }
 
 // Phase A with the branch selection: diagonal tile or not, capped or not, and for capped
 // scores the polynomial tanh unless some argument in the warp's part of the tile is too large.
-__device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0, bool diag, bool capped, bool row_valid,
-                                                const BwdRowConsts &k, uint32_t (&pk)[AB_NC / 2], float (&f0)[AB_NC]) {
+__device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0, bool diag, bool capped,
+                                                const BwdRowConsts &k, uint32_t (&pk)[AB_NC / 2],
+                                                uint32_t (&fk)[AB_NC / 2]) {
   if (!capped) {
-    if (diag) bwd_phase_a<true, false, false>(t_s, row, col0, row_valid, k, pk, f0);
-    else bwd_phase_a<false, false, false>(t_s, row, col0, row_valid, k, pk, f0);
+    if (diag) bwd_phase_a<true, false, false>(t_s, row, col0, k, pk, fk);
+    else bwd_phase_a<false, false, false>(t_s, row, col0, k, pk, fk);
     return;
   }
-  const float big = diag ? bwd_phase_a<true, true, true>(t_s, row, col0, row_valid, k, pk, f0)
-                         : bwd_phase_a<false, true, true>(t_s, row, col0, row_valid, k, pk, f0);
+  const float big = diag ? bwd_phase_a<true, true, true>(t_s, row, col0, k, pk, fk)
+                         : bwd_phase_a<false, true, true>(t_s, row, col0, k, pk, fk);
   if (__any_sync(0xffffffffu, !(big <= TANH_POLY_LIMIT2))) {  // also catches NaN
-    if (diag) bwd_phase_a<true, true, false>(t_s, row, col0, row_valid, k, pk, f0);
-    else bwd_phase_a<false, true, false>(t_s, row, col0, row_valid, k, pk, f0);
+    if (diag) bwd_phase_a<true, true, false>(t_s, row, col0, k, pk, fk);
+    else bwd_phase_a<false, true, false>(t_s, row, col0, k, pk, fk);
   }
 }
 
@@ -617,18 +629,17 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     for (int it = 0; it < n_it && ok; it++) {
       const int qi = (kb + it) * 128 + row;
       const bool valid = qi < a.T;
-      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
       k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-      uint32_t pk[AB_NC / 2];
-      float f0[AB_NC];
+      uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
       if (!mbar_wait(s_full0 + 8 * (it & 1), (it >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + col0, row, col0, it == 0, capped, valid, k, pk, f0);
+      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + col0, row, col0, it == 0, capped, k, pk, fk);
       if (!mbar_wait(dp_full, it & 1, abort_flag)) { ok = false; break; }
       // the gradient products of the previous tile must have finished reading the P / dS tiles
       if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_b<true>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, f0, p_row, ds_row);
+      bwd_phase_b<true>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, p_row, ds_row);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
@@ -812,21 +823,20 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
     k.c2 = a.cap * LOG2E;
     k.scale = a.scale;
-    k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : 0.f;
+    k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
     k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
     uint8_t *ds_row = smem + AQ_DS + (colq >> 1) * AT_TILE + row * 128;
     bool ok = true;
     for (int j = 0; j < nb && ok; j++) {
-      uint32_t pk[AB_NC / 2];
-      float f0[AB_NC];
+      uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
       if (!mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, valid, k, pk, f0);
+      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, k, pk, fk);
       if (!mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
       // dQ += dS(j-1) K(j-1) must have finished reading the dS tiles
       if (j > 0 && !mbar_wait(acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, f0, nullptr, ds_row);
+      bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, nullptr, ds_row);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
