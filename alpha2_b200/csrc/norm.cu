@@ -202,22 +202,34 @@ __global__ void __launch_bounds__(LN_WARPS * 32) ln_bwd_warp(const T *__restrict
   }
 }
 
-// dw[c] (+)= sum_p part[p][0][c]; db[c] (+)= sum_p part[p][1][c].  Block = 32 columns x 8 row
-// groups: each thread adds every 8th partial row of its column (independent loads), then the
-// 8 group sums are added in fixed order, so the result does not depend on scheduling.
-__global__ void __launch_bounds__(256) ln_reduce_partials(const float *__restrict__ part, float *dw, float *db,
-                                                          int n_part, int dim, int accumulate) {
-  __shared__ float sm[8][33];
+// dw[c] (+)= sum_p part[p][0][c]; db[c] (+)= sum_p part[p][1][c].  Block = 32 columns x 32 row
+// groups: each thread adds every 32nd partial row of its column, four independent loads at a
+// time, then the 32 group sums are added in fixed order, so the result does not depend on
+// scheduling.
+constexpr int LN_RED_GROUPS = 32;
+__global__ void __launch_bounds__(32 * LN_RED_GROUPS) ln_reduce_partials(const float *__restrict__ part, float *dw,
+                                                                         float *db, int n_part, int dim,
+                                                                         int accumulate) {
+  __shared__ float sm[LN_RED_GROUPS][33];
   const int c = blockIdx.x * 32 + threadIdx.x;
-  float a = 0.f;
-  if (c < 2 * dim)
-    for (int p = threadIdx.y; p < n_part; p += 8) a += part[(size_t)p * 2 * dim + c];
-  sm[threadIdx.y][threadIdx.x] = a;
+  float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
+  if (c < 2 * dim) {
+    const size_t ld = (size_t)2 * dim;
+    int p = threadIdx.y;
+    for (; p + 3 * LN_RED_GROUPS < n_part; p += 4 * LN_RED_GROUPS) {
+      a0 += part[(size_t)p * ld + c];
+      a1 += part[(size_t)(p + LN_RED_GROUPS) * ld + c];
+      a2 += part[(size_t)(p + 2 * LN_RED_GROUPS) * ld + c];
+      a3 += part[(size_t)(p + 3 * LN_RED_GROUPS) * ld + c];
+    }
+    for (; p < n_part; p += LN_RED_GROUPS) a0 += part[(size_t)p * ld + c];
+  }
+  sm[threadIdx.y][threadIdx.x] = (a0 + a1) + (a2 + a3);
   __syncthreads();
   if (threadIdx.y == 0 && c < 2 * dim) {
     float t = 0.f;
 #pragma unroll
-    for (int k = 0; k < 8; k++) t += sm[k][threadIdx.x];
+    for (int k = 0; k < LN_RED_GROUPS; k++) t += sm[k][threadIdx.x];
     float *dst = c < dim ? dw + c : (db ? db + (c - dim) : nullptr);
     if (dst) *dst = accumulate ? *dst + t : t;
   }
@@ -685,7 +697,7 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
           ptr<T>(x), ptr<float>(w), ptr<T>(g), dx_add ? ptr<T>(dx_add) : nullptr, ptr<T>(dx), (float *)part, rows,
           (int)dim, eps);
     g_launches++;
-    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, 8), 0, g_stream>>>(
+    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, LN_RED_GROUPS), 0, g_stream>>>(
         (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
     pool_free(part);
   } else if (fast) {
@@ -706,7 +718,7 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
     }
 #undef LN_BWD_CASE
     g_launches++;
-    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, 8), 0, g_stream>>>(
+    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, LN_RED_GROUPS), 0, g_stream>>>(
         (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
     pool_free(part);
   } else {
