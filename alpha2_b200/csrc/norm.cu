@@ -11,7 +11,7 @@
 // sums over the rows it walks, writes one partial row to scratch, and a second kernel adds
 // the partial rows in block order.  Algorithmic bytes per row: forward 2*dim*e, backward
 // 3*dim*e (e = element size) — the scratch adds 2*grid*dim*4 bytes per call.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace alpha {
 
@@ -534,6 +534,181 @@ __global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, co
   }
 }
 
+// ── backward, a warp per row fed by a bulk-copy ring (the fastest path) ──────────────────
+// Four worker warps each own one row of a 4-row group; a fifth warp streams the groups
+// (x, g and the optional residual gradient are contiguous 4-row slabs) into a 3-stage
+// shared-memory ring with one bulk copy per slab, so the loads of the next groups are in
+// flight while the workers compute and nothing depends on how the compiler schedules
+// loads.  A lane owns the 16-byte vectors lane, lane + 32, ... of its row: row statistics
+// are warp shuffles only (no block barrier in the loop), dw / db sums stay in registers
+// and are combined across the four warps once at the end, in fixed order.
+constexpr int LR_WARPS = 4, LR_STAGES = 3, LR_THREADS = (LR_WARPS + 1) * 32;
+
+template <typename T, int NV, bool RMS, bool HAS_ADD>
+__global__ void __launch_bounds__(LR_THREADS, 3)
+ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__restrict__ g,
+            const T *__restrict__ dx_add, T *__restrict__ dx, float *__restrict__ part, int64_t rows, int dim, float eps,
+            uint32_t *err) {
+  using namespace tc;
+  constexpr int V = Vec16<T>::N;
+  constexpr int NE = NV * V;  // elements per lane per row
+  constexpr int NS = HAS_ADD ? 3 : 2;
+  extern __shared__ __align__(128) uint8_t lr_smem[];
+  const uint32_t row_bytes = (uint32_t)dim * sizeof(T);
+  const uint32_t slab = LR_WARPS * row_bytes, stage_bytes = NS * slab;
+  const uint32_t ring = smem_u32(lr_smem);
+  const uint32_t bar = ring + LR_STAGES * stage_bytes;
+  auto full_bar = [&](int s) { return bar + 8u * s; };
+  auto empty_bar = [&](int s) { return bar + 8u * (LR_STAGES + s); };
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(lr_smem + LR_STAGES * stage_bytes + 16 * LR_STAGES);
+  float *w_sm = reinterpret_cast<float *>(lr_smem + LR_STAGES * stage_bytes + 64);  // the weight row
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < dim; c += LR_THREADS) w_sm[c] = w[c];
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < LR_STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), LR_WARPS);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
+
+  float dw_acc[NE], db_acc[NE];
+#pragma unroll
+  for (int j = 0; j < NE; j++) dw_acc[j] = db_acc[j] = 0.f;
+
+  if (warp == LR_WARPS) {
+    // producer
+    int i = 0;
+    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
+      const int s = i % LR_STAGES;
+      if (!mbar_wait(empty_bar(s), ((i / LR_STAGES) & 1) ^ 1, abort_flag)) break;
+      const int64_t r0 = grp * LR_WARPS;
+      const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
+      const uint32_t dst = ring + s * stage_bytes;
+      if (elect_one()) {
+        mbar_expect_tx(full_bar(s), NS * bytes);
+        bulk_load_1d(dst, x + r0 * dim, bytes, full_bar(s));
+        bulk_load_1d(dst + slab, g + r0 * dim, bytes, full_bar(s));
+        if (HAS_ADD) bulk_load_1d(dst + 2 * slab, dx_add + r0 * dim, bytes, full_bar(s));
+      }
+      __syncwarp();
+    }
+  } else {
+    const float inv_dim = 1.f / (float)dim;
+    int i = 0;
+    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
+      const int s = i % LR_STAGES;
+      if (!mbar_wait(full_bar(s), (i / LR_STAGES) & 1, abort_flag)) break;
+      const int64_t r = grp * LR_WARPS + warp;
+      const uint8_t *src = lr_smem + s * stage_bytes + warp * row_bytes;
+      float xv[NE], gv[NE];
+      Vec16<T> av[NV];
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        Vec16<T> t, u;
+        t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
+        u.load(reinterpret_cast<const T *>(src + slab + (v * 32 + lane) * 16));
+        if (HAS_ADD) av[v].load(reinterpret_cast<const T *>(src + 2 * slab + (v * 32 + lane) * 16));
+        t.get(&xv[v * V]);
+        u.get(&gv[v * V]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the stage may be refilled
+      if (r >= rows) continue;                   // warp-uniform (a short last group)
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
+      sum = warp_sum(sum);
+      float mean = 0.f, rstd;
+      if (RMS) {
+        rstd = rsqrtf(sum * inv_dim + eps);
+      } else {
+        mean = sum * inv_dim;
+        float q = 0.f;
+#pragma unroll
+        for (int j = 0; j < NE; j++) {
+          const float d = xv[j] - mean;
+          q += d * d;
+        }
+        q = warp_sum(q);
+        rstd = 1.f / sqrtf(q * inv_dim + eps);
+      }
+      float s1 = 0.f, s2 = 0.f;
+#pragma unroll
+      for (int v = 0; v < NV; v++)
+#pragma unroll
+        for (int j4 = 0; j4 < V; j4 += 4) {
+          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + (v * 32 + lane) * V + j4);
+          const float wq[4] = {w4.x, w4.y, w4.z, w4.w};
+#pragma unroll
+          for (int q = 0; q < 4; q++) {
+            const int j = v * V + j4 + q;
+            const float xhat = (xv[j] - mean) * rstd;
+            const float dy = gv[j] * wq[q];
+            dw_acc[j] += gv[j] * xhat;
+            db_acc[j] += gv[j];
+            s1 += dy;
+            s2 += dy * xhat;
+            xv[j] = xhat;
+            gv[j] = dy;
+          }
+        }
+      s1 = RMS ? 0.f : warp_sum(s1);
+      s2 = warp_sum(s2);
+      T *dr = dx + r * dim;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        float o[V];
+#pragma unroll
+        for (int j = 0; j < V; j++) o[j] = rstd * (gv[v * V + j] - (s1 + xv[v * V + j] * s2) * inv_dim);
+        if (HAS_ADD) {
+          float e[V];
+          av[v].get(e);
+#pragma unroll
+          for (int j = 0; j < V; j++) o[j] += e[j];
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(dr + (v * 32 + lane) * V);
+      }
+    }
+  }
+  // combine the four warps' column sums in warp order through the (now idle) ring
+  __syncthreads();
+  float *red = reinterpret_cast<float *>(lr_smem);  // [LR_WARPS][2 * dim]
+  if (warp < LR_WARPS) {
+    float *mine = red + (size_t)warp * 2 * dim;
+#pragma unroll
+    for (int v = 0; v < NV; v++)
+#pragma unroll
+      for (int j = 0; j < V; j += 4) {
+        const int c = (v * 32 + lane) * V + j;
+        *reinterpret_cast<float4 *>(mine + c) =
+            make_float4(dw_acc[v * V + j], dw_acc[v * V + j + 1], dw_acc[v * V + j + 2], dw_acc[v * V + j + 3]);
+        *reinterpret_cast<float4 *>(mine + dim + c) =
+            make_float4(db_acc[v * V + j], db_acc[v * V + j + 1], db_acc[v * V + j + 2], db_acc[v * V + j + 3]);
+      }
+  }
+  __syncthreads();
+  float *out = part + (size_t)blockIdx.x * 2 * dim;
+  for (int c = threadIdx.x; c < 2 * dim; c += LR_THREADS) {
+    float t = 0.f;
+#pragma unroll
+    for (int k = 0; k < LR_WARPS; k++) t += red[(size_t)k * 2 * dim + c];
+    out[c] = t;
+  }
+  if (*abort_flag) {  // a bounded wait ran out: let copies in flight land before the block's memory goes away
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && err) atomicExch(err, 0xB1000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+}
+
 // ── generic fallback (any dim / alignment): one block per row, scalar accesses ──────────
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) ln_fwd_block(const T *x, const float *w, const float *b, T *y, int64_t rows,
@@ -666,6 +841,33 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   return 0;
 }
 
+template <typename T, int NV, bool RMS, bool HAS_ADD>
+static int launch_bwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, float *part,
+                              int64_t rows, int64_t dim, float eps, int grid) {
+  const size_t smem = (size_t)LR_STAGES * (HAS_ADD ? 3 : 2) * LR_WARPS * dim * sizeof(T) + 64 + dim * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    ALPHA_CUDA(cudaFuncSetAttribute(ln_bwd_ring<T, NV, RMS, HAS_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    200 * 1024));
+    attr = true;
+  }
+  ln_bwd_ring<T, NV, RMS, HAS_ADD><<<grid, LR_THREADS, smem, g_stream>>>(
+      ptr<T>(x), ptr<float>(w), ptr<T>(g), HAS_ADD ? ptr<T>(dx_add) : nullptr, ptr<T>(dx), part, rows, (int)dim, eps,
+      tc::tc_error_word());
+  return 0;
+}
+template <typename T, bool RMS, bool HAS_ADD>
+static int launch_bwd_ring(int nv, alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, float *part,
+                           int64_t rows, int64_t dim, float eps, int grid) {
+  constexpr int K = sizeof(T) == 2 ? 1 : 2;  // lanes hold up to 24 elements: 3 bf16 vectors or 6 f32 vectors
+  switch (nv) {
+    case 1 * K: return launch_bwd_ring_nv<T, 1 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
+    case 2 * K: return launch_bwd_ring_nv<T, 2 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
+    case 3 * K: return launch_bwd_ring_nv<T, 3 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
+  }
+  return set_error("layernorm backward: unsupported vector count %d", nv);
+}
+
 template <typename T, bool RMS>
 static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, alpha_buf dw, alpha_buf db,
                     int64_t rows, int64_t dim, float eps, int accumulate) {
@@ -683,7 +885,21 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
   const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && (dx_add & 15) == 0 &&
                     dim / V <= 32 * 8 &&
                     smem <= 48 * 1024;
-  if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0) {
+  constexpr int RK = sizeof(T) == 2 ? 1 : 2;  // 16-byte vectors per 8 elements
+  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
+    // ring-fed warp-per-row kernel: 8, 16 or 24 elements per lane
+    const int nv = (int)(dim / (32 * V));
+    const int grid = grid_for(rows, LR_WARPS, 3);
+    void *part = nullptr;
+    if (pool_alloc((size_t)grid * 2 * dim * sizeof(float), &part)) return 1;
+    int rc = dx_add ? launch_bwd_ring<T, RMS, true>(nv, x, w, g, dx_add, dx, (float *)part, rows, dim, eps, grid)
+                    : launch_bwd_ring<T, RMS, false>(nv, x, w, g, dx_add, dx, (float *)part, rows, dim, eps, grid);
+    if (rc) { pool_free(part); return 1; }
+    g_launches++;
+    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, LN_RED_GROUPS), 0, g_stream>>>(
+        (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
+    pool_free(part);
+  } else if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0) {
     const int nvec = (int)(dim / V);
     const int grid = nvec <= LN_CTA ? grid_for(rows, 2, 5) : grid_for(rows, 1, 4);
     void *part = nullptr;

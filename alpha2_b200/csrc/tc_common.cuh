@@ -127,6 +127,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
       ::"r"(dst), "l"(map), "r"(bar), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// 1-D bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16),
+// completion counted on an mbarrier.
+__device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
+               : "memory");
+}
 // 2-D tiled TMA store shared -> global (bulk-group completion).  Elements outside the
 // tensor's extents are not written.  x follows the same 16-byte rule as loads and must not
 // be negative.
