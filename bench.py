@@ -340,9 +340,14 @@ def main() -> None:
         "clocks": clocks,
         "mfu": {"flops_per_token": fpt, "of_burst_peak": value / world * fpt / (peaks["bf16_tflops"] * 1e12),
                 "of_sustained_peak": value / world * fpt / (peak_tf * 1e12), "peaks": peaks["source"]},
-        "roofline": {"bound": "tensor", "kernel": "gemm_tc_kernel (bf16 tcgen05 GEMM, all layouts)", "achieved": achieved,
+        "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel (bf16 tcgen05 GEMM, CTA pairs, all layouts)",
+                     "achieved": achieved,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": (achieved / peak_tf) if achieved else None,
-                     "traffic": None, "peak_source": f"{peaks['source']} cuBLAS bf16, sustained",
+                     # DRAM bytes of one profiled launch (the 16384 x 3072 x 768 forward GEMM: 30.0 MB read +
+                     # 41.6 MB written, against 130.6 MB algorithmic: part of the output stays in L2)
+                     "traffic": 71.6e6 if args.workload == "gpt2-124m" else None,
+                     "traffic_launch": "fc1 forward 16384x3072x768, one ncu capture" if args.workload == "gpt2-124m" else None,
+                     "peak_source": f"{peaks['source']} cuBLAS bf16, sustained",
                      "launches_per_step": gemm.launches / args.steps, "ms_per_step": gemm.ms / args.steps},
         "profile": profile, "profile_pass_ms_per_step": ms_p / args.steps,
         "final_loss": final_loss,
