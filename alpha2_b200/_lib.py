@@ -111,6 +111,7 @@ SIGNATURES = {
     "alpha_adamw_multi": [C.POINTER(AdamWTensor), _I, _F, _F, _F, _F, _F, _F, _F, _B, _F],
     "alpha_comm_unique_id": [_P], "alpha_comm_init_rank": [_I, _I, _P],
     "alpha_comm_allreduce_sum": [_B, _L, _I], "alpha_comm_wait": [], "alpha_comm_destroy": [],
+    "alpha_comm_allreduce_sum_bucket": [C.POINTER(C.c_uint64), _PL, _I, _I],
     "alpha_rng_seed": [C.POINTER(HostRng), C.c_uint32],
     "alpha_rng_fill_gauss": [C.POINTER(HostRng), _P, _L, C.c_double],
 }

@@ -26,6 +26,8 @@ struct Nccl {
   ncclResult_t (*GetUniqueId)(ncclUniqueId *) = nullptr;
   ncclResult_t (*CommInitRank)(ncclComm_t *, int, ncclUniqueId, int) = nullptr;
   ncclResult_t (*AllReduce)(const void *, void *, size_t, int, int, ncclComm_t, cudaStream_t) = nullptr;
+  ncclResult_t (*GroupStart)() = nullptr;
+  ncclResult_t (*GroupEnd)() = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
@@ -49,6 +51,8 @@ static int load_nccl() {
   SYM(GetUniqueId, "ncclGetUniqueId")
   SYM(CommInitRank, "ncclCommInitRank")
   SYM(AllReduce, "ncclAllReduce")
+  SYM(GroupStart, "ncclGroupStart")
+  SYM(GroupEnd, "ncclGroupEnd")
   SYM(CommDestroy, "ncclCommDestroy")
   SYM(GetErrorString, "ncclGetErrorString")
 #undef SYM
@@ -101,6 +105,31 @@ int alpha_comm_allreduce_sum(alpha_buf buf, int64_t n, int dtype) {
   ALPHA_CUDA(cudaStreamWaitEvent(g_comm_stream, g_ev_ready, 0));
   ALPHA_NCCL(g_nccl.AllReduce(ptr<void>(buf), ptr<void>(buf), (size_t)n, dtype == ALPHA_F32 ? ncclFloat32 : ncclBfloat16,
                               ncclSum, g_comm, g_comm_stream));
+  return 0;
+}
+
+// One bucket = several gradient tensors reduced as one NCCL group: a single collective launch
+// on the side stream moves all of them (sizes of tens of MB keep the launch count per step
+// small and the NVLink transfers long).
+int alpha_comm_allreduce_sum_bucket(const alpha_buf *bufs, const int64_t *counts, int n_bufs, int dtype) {
+  ALPHA_REQUIRE_INIT();
+  if (g_nranks == 1 || n_bufs == 0) return 0;
+  ALPHA_CHECK(g_comm != nullptr, "alpha_comm_allreduce_sum_bucket: alpha_comm_init_rank was not called");
+  ALPHA_CHECK(bufs != nullptr && counts != nullptr && n_bufs > 0, "alpha_comm_allreduce_sum_bucket: bad arguments");
+  ALPHA_CHECK(dtype == ALPHA_F32 || dtype == ALPHA_BF16, "alpha_comm_allreduce_sum_bucket: unsupported dtype %d", dtype);
+  ALPHA_CUDA(cudaEventRecord(g_ev_ready, g_stream));
+  ALPHA_CUDA(cudaStreamWaitEvent(g_comm_stream, g_ev_ready, 0));
+  ALPHA_NCCL(g_nccl.GroupStart());
+  for (int i = 0; i < n_bufs; i++) {
+    if (counts[i] == 0) continue;
+    ncclResult_t r = g_nccl.AllReduce(ptr<void>(bufs[i]), ptr<void>(bufs[i]), (size_t)counts[i],
+                                      dtype == ALPHA_F32 ? ncclFloat32 : ncclBfloat16, ncclSum, g_comm, g_comm_stream);
+    if (r != 0) {
+      g_nccl.GroupEnd();
+      return set_error("alpha_comm_allreduce_sum_bucket: ncclAllReduce -> %s", g_nccl.GetErrorString(r));
+    }
+  }
+  ALPHA_NCCL(g_nccl.GroupEnd());
   return 0;
 }
 

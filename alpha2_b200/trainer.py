@@ -94,9 +94,23 @@ class DataParallel:
         check(L.load().alpha_comm_unique_id(buf))
         return buf.raw
 
+    #: gradients are handed to NCCL in groups of about this many bytes (one collective launch each)
+    bucket_bytes = 32 << 20
+
     def allreduce(self, grad: TensorData) -> None:
         from ._lib import check
         check(self.backend.lib.alpha_comm_allreduce_sum(grad.ptr, grad.size, self.backend._code(grad.dtype)))
+
+    def allreduce_bucket(self, grads: list) -> None:
+        """Sum-allreduce several gradient tensors of one dtype as a single NCCL group."""
+        import ctypes as C
+        from ._lib import check
+        if not grads:
+            return
+        n = len(grads)
+        ptrs = (C.c_uint64 * n)(*[g.ptr for g in grads])
+        counts = (C.c_int64 * n)(*[g.size for g in grads])
+        check(self.backend.lib.alpha_comm_allreduce_sum_bucket(ptrs, counts, n, self.backend._code(grads[0].dtype)))
 
     def wait(self) -> None:
         from ._lib import check
@@ -197,15 +211,39 @@ class Trainer:
                     pending[v.id] = pending.get(v.id, 0) + 1
                     by_id[v.id] = v
         dp = self.dp
+        # Finished gradients collect in a bucket (in the order backward finalises them: head and
+        # last layers first); a full bucket goes to the collective as one group while backward
+        # continues.  A communicator without bucket support gets them one by one.
+        bucketed = hasattr(dp, "allreduce_bucket")
+        limit = getattr(dp, "bucket_bytes", 32 << 20)
+        bucket: list = []
+        fill = [0]
+
+        def flush():
+            if bucket:
+                by_dtype: dict = {}
+                for g in bucket:
+                    by_dtype.setdefault(g.dtype, []).append(g)
+                for gs in by_dtype.values():
+                    dp.allreduce_bucket(gs)
+                bucket.clear()
+                fill[0] = 0
 
         def on_entry_done(entry):
             for v in entry.inputs:
                 if isinstance(v, Param) and v.id in pending:
                     pending[v.id] -= 1
                     if pending[v.id] == 0 and v.grad is not None:
-                        dp.allreduce(v.grad)
+                        if bucketed:
+                            bucket.append(v.grad)
+                            fill[0] += v.grad.size * (2 if v.grad.dtype == "bf16" else 4)
+                            if fill[0] >= limit:
+                                flush()
+                        else:
+                            dp.allreduce(v.grad)
                         del pending[v.id]
         self.tape.backward(loss, self.B, self.releaseFn, onEntryDone=on_entry_done)
+        flush()
 
     # ── state exchange with the host (checkpointing needs exactly this) ───────
     def host_params(self) -> dict:

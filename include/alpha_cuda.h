@@ -338,6 +338,8 @@ int alpha_rng_fill_gauss(alpha_host_rng_t *r, float *host_out, int64_t n, double
 int alpha_comm_unique_id(void *out_128_bytes);
 int alpha_comm_init_rank(int n_ranks, int rank, const void *unique_id_128_bytes);
 int alpha_comm_allreduce_sum(alpha_buf buf, int64_t n, int dtype);
+/* A bucket of gradient tensors (same dtype) reduced as one NCCL group = one collective launch. */
+int alpha_comm_allreduce_sum_bucket(const alpha_buf *bufs, const int64_t *counts, int n_bufs, int dtype);
 int alpha_comm_wait(void);
 int alpha_comm_destroy(void);
 

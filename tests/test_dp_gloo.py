@@ -33,7 +33,22 @@ class GlooDP:
         pass
 
 
-def _worker(rank, world, port, out_dir):
+class GlooBucketDP(GlooDP):
+    """Same exchange through the bucket interface: small buckets so that several are flushed
+    during backward and one at its end."""
+    bucket_bytes = 8 << 10
+
+    def __init__(self, world, rank):
+        super().__init__(world, rank)
+        self.buckets = []
+
+    def allreduce_bucket(self, grads):
+        self.buckets.append(len(grads))
+        for g in grads:
+            self.allreduce(g)
+
+
+def _worker(rank, world, port, out_dir, bucketed=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -43,20 +58,26 @@ def _worker(rank, world, port, out_dir):
     from tests.fake_backend import NumpyBackend, T
     mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=2, nEmbd=32, nHead=4, tied=True, init="plain")
     tc = TrainConfig(iters=10, batchSize=2, gradClip=0.5, seed=3)
-    dp = GlooDP(world, rank)
+    dp = GlooBucketDP(world, rank) if bucketed else GlooDP(world, rank)
     tr = Trainer(NumpyBackend(), mc, tc, dp=dp)
     batches = uniform_batches(100 + rank, 3, 2, 16, 64)          # a different stream per rank
     res = [tr.train_step([(T(t, "i32"), T(g, "i32"))]) for t, g in batches]
     n_params = len(tr.entries)
     assert len(dp.handed) == 3 * n_params                        # every gradient handed over once per step
+    if bucketed:
+        assert sum(dp.buckets) == 3 * n_params and len(dp.buckets) > 3 and max(dp.buckets) > 1
     np.savez(os.path.join(out_dir, f"rank{rank}.npz"), gn=np.array([r["gradNorm"] for r in res]),
              **{n: v.data.data for n, v in tr.entries})
     dist.destroy_process_group()
 
 
-def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path):
-    port = 29500 + os.getpid() % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path)), nprocs=2, join=True)
+import pytest
+
+
+@pytest.mark.parametrize("bucketed", [False, True])
+def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path, bucketed):
+    port = 29500 + (os.getpid() + (997 if bucketed else 0)) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), bucketed), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     for k in r0.files:
         assert np.array_equal(r0[k], r1[k]), k                   # replicas stay identical
