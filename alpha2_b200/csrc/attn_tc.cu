@@ -880,6 +880,318 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   }
 }
 
+// ── forward, bounded scores (soft cap), persistent ─────────────────────────────────────
+// With a soft cap the transformed score cap*tanh(s/cap) lies in [-cap, cap], so the softmax
+// can use the constant cap as its reference maximum: exp2(c2*(tanh - 1)) never overflows and,
+// for cap*log2(e) <= 50, never underflows either.  That removes the running maximum, the
+// rescaling of O and every dependency between key blocks, and lets the tile be split over
+// sixteen math warps (32 query rows x 32 key columns each, row sums combined once per query
+// block).  tanh comes from the polynomial of the backward kernels, exp2 from the
+// special-function unit.
+//
+// One CTA per SM walks (batch*head, query block) items, longest first, round-robin:
+//   warp 0      TMA producer: Q (2 buffers), K tiles through a 3-stage ring (a K tile is free as
+//               soon as its score product is done) and V tiles through a 4-stage ring; it
+//               runs ahead into the next item while the current one is being computed
+//   warp 1      MMA issuer: S(j+2) is issued as soon as the math warps have consumed S(j)
+//               (two S buffers in TMEM), O += P(j) V(j) when P(j) is in shared memory (two P
+//               buffers), so the tensor core works while the math warps compute
+//   warps 2-17  math warps
+// All barrier phases are running counters over items and tiles; every wait is bounded.
+constexpr int AF2_THREADS = 64 + 32 * 16;
+constexpr int AF2_KST = 3, AF2_VST = 4;
+constexpr int AF2_Q = 0;                                   // 2 buffers
+constexpr int AF2_K = 2 * AT_TILE;
+constexpr int AF2_V = AF2_K + AF2_KST * AT_TILE;
+constexpr int AF2_P = AF2_V + AF2_VST * AT_TILE;           // 2 buffers x 2 tiles (key halves)
+constexpr int AF2_BAR = AF2_P + 4 * AT_TILE;
+constexpr int AF2_LSUM = AF2_BAR + 256;                    // [4 column quarters][128 rows] floats
+constexpr int AF2_DYN = AF2_LSUM + 2048 + 1024;
+constexpr float AF2_MAX_C2 = 50.f;                         // largest cap*log2(e) this kernel accepts
+
+// P for 32 scores of one row (bounded-score softmax).  Returns the largest squared tanh
+// argument seen; adds the row's probabilities to lsum.
+template <bool DIAG, bool POLY>
+__device__ __forceinline__ float fwd2_scores(uint32_t t_s, int row, int col0, float c1f, float c2f, uint64_t &lsum,
+                                             uint32_t (&pk)[16]) {
+  float big = 0.f;
+  const uint64_t c1 = f2_pack(c1f, c1f), c2 = f2_pack(c2f, c2f), nm = f2_pack(-c2f, -c2f);
+  const uint64_t p1 = f2_pack(-0.3333333333f, -0.3333333333f), p2 = f2_pack(0.1333333333f, 0.1333333333f),
+                 p3 = f2_pack(-0.0539682540f, -0.0539682540f);
+#pragma unroll
+  for (int part = 0; part < 2; part++) {
+    uint32_t r[16];
+    tmem_ld_32x16(t_s + part * 16, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int i = 0; i < 16; i += 2) {
+      const uint64_t x = f2_mul(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c1);
+      uint64_t th;
+      if (POLY) {
+        const uint64_t x2 = f2_mul(x, x);
+        float xa, xb;
+        f2_unpack(x2, xa, xb);
+        big = fmax3(big, xa, xb);
+        uint64_t t = f2_fma(x2, p3, p2);
+        t = f2_fma(t, x2, p1);
+        th = f2_fma(f2_mul(x, x2), t, x);
+      } else {
+        float xa, xb;
+        f2_unpack(x, xa, xb);
+        th = f2_pack(tanh_approx(xa), tanh_approx(xb));
+      }
+      float ea, eb;
+      f2_unpack(f2_fma(th, c2, nm), ea, eb);
+      float pa = ex2_approx(ea), pb = ex2_approx(eb);
+      if (DIAG) {
+        const int c = col0 + part * 16 + i;
+        if (c > row) pa = 0.f;
+        if (c + 1 > row) pb = 0.f;
+      }
+      lsum = f2_add(lsum, f2_pack(pa, pb));
+      pk[part * 8 + (i >> 1)] = bf16x2_pack(pa, pb);
+    }
+  }
+  return big;
+}
+
+__global__ void __launch_bounds__(AF2_THREADS, 1)
+attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+                    const __grid_constant__ CUtensorMap tmap_v, AttnTcArgs a, int n_items, int BH) {
+  extern __shared__ uint8_t at_smem_raw[];
+  uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t sb = smem_u32(smem);
+  const uint32_t bar = sb + AF2_BAR;
+  const uint32_t q_full0 = bar, q_empty0 = bar + 16, s_full0 = bar + 32, p_ready0 = bar + 48, p_free0 = bar + 64,
+                 o_done = bar + 80, l_ready = bar + 88, k_full0 = bar + 96, k_empty0 = k_full0 + 8 * AF2_KST,
+                 v_full0 = k_empty0 + 8 * AF2_KST, v_empty0 = v_full0 + 8 * AF2_VST;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AF2_BAR + 96 + 16 * (AF2_KST + AF2_VST));
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
+  float *lsm = reinterpret_cast<float *>(smem + AF2_LSUM);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n_qb = (a.T + 127) / 128;
+  constexpr uint32_t TMEM_COLS = 512;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 2; i++) {
+      mbar_init(q_full0 + 8 * i, 1);
+      mbar_init(q_empty0 + 8 * i, 1);
+      mbar_init(s_full0 + 8 * i, 1);
+      mbar_init(p_ready0 + 8 * i, 16);
+      mbar_init(p_free0 + 8 * i, 1);
+    }
+    mbar_init(o_done, 1);
+    mbar_init(l_ready, 16);
+    for (int s = 0; s < AF2_KST; s++) {
+      mbar_init(k_full0 + 8 * s, 1);
+      mbar_init(k_empty0 + 8 * s, 1);
+    }
+    for (int s = 0; s < AF2_VST; s++) {
+      mbar_init(v_full0 + 8 * s, 1);
+      mbar_init(v_empty0 + 8 * s, 1);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tS0 = tmem_base, tO = tmem_base + 256;
+
+  // item -> (batch*head, query block): the longest query blocks come first
+  auto decode = [&](int item, int &bh, int &qb) {
+    qb = n_qb - 1 - item / BH;
+    bh = item - (item / BH) * BH;
+  };
+
+  if (warp == 0) {
+    if (elect_one()) {
+      tma_prefetch_desc(&tmap_q); tma_prefetch_desc(&tmap_k); tma_prefetch_desc(&tmap_v);
+    }
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
+      if (!mbar_wait(q_empty0 + 8 * (n & 1), ((n >> 1) & 1) ^ 1, abort_flag)) break;
+      if (elect_one()) {
+        mbar_expect_tx(q_full0 + 8 * (n & 1), AT_TILE);
+        tma_load_4d(sb + AF2_Q + (n & 1) * AT_TILE, &tmap_q, q_full0 + 8 * (n & 1), 0, qb * 128, h, b);
+      }
+      __syncwarp();
+      for (int j = 0; j < nb; j++, t++) {
+        const int ks = t % AF2_KST, vs = t % AF2_VST;
+        if (!mbar_wait(k_empty0 + 8 * ks, ((t / AF2_KST) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (elect_one()) {
+          mbar_expect_tx(k_full0 + 8 * ks, AT_TILE);
+          tma_load_4d(sb + AF2_K + ks * AT_TILE, &tmap_k, k_full0 + 8 * ks, 0, j * 128, h, b);
+        }
+        __syncwarp();
+        if (!mbar_wait(v_empty0 + 8 * vs, ((t / AF2_VST) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (elect_one()) {
+          mbar_expect_tx(v_full0 + 8 * vs, AT_TILE);
+          tma_load_4d(sb + AF2_V + vs * AT_TILE, &tmap_v, v_full0 + 8 * vs, 0, j * 128, h, b);
+        }
+        __syncwarp();
+      }
+    }
+  } else if (warp == 1) {
+    constexpr uint32_t idesc_qk = make_idesc_bf16(128, 128, false, false);
+    constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
+    const uint64_t d_q = make_smem_desc(sb + AF2_Q, 16, 1024), d_k = make_smem_desc(sb + AF2_K, 16, 1024);
+    const uint64_t d_p = make_smem_desc(sb + AF2_P, 16, 1024), d_v = make_smem_desc(sb + AF2_V, AT_TILE, 1024);
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int nb = qb + 1;
+      if (!mbar_wait(q_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag)) break;
+      const uint64_t qd = d_q + (uint64_t)(((n & 1) * AT_TILE) >> 4);
+      const uint32_t q_freed = q_empty0 + 8 * (n & 1);
+      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer (t + j) & 1
+        const int tt = t + j, st = tt % AF2_KST;
+        if (!mbar_wait(k_full0 + 8 * st, (tt / AF2_KST) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t kd = d_k + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1), k_freed = k_empty0 + 8 * st;
+        const bool last = j == nb - 1;
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, qd + kk * 2, kd + kk * 2, idesc_qk, kk > 0 ? 1u : 0u);
+          mma_commit(k_freed);
+          mma_commit(done);
+          if (last) mma_commit(q_freed);  // Q is not needed after the item's last score product
+        }
+        __syncwarp();
+        return true;
+      };
+      ok = issue_s(0);
+      if (ok && nb > 1) ok = issue_s(1);
+      for (int j = 0; j < nb && ok; j++) {
+        const int tt = t + j, st = tt % AF2_VST;
+        if (!mbar_wait(p_ready0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
+        if (!mbar_wait(v_full0 + 8 * st, (tt / AF2_VST) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint64_t pd = d_p + (uint64_t)(((tt & 1) * 2 * AT_TILE) >> 4);
+        const uint64_t vd = d_v + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t first = j > 0 ? 1u : 0u, kv_freed = v_empty0 + 8 * st, p_freed = p_free0 + 8 * (tt & 1);
+        const bool last = j == nb - 1;
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++)
+            mma_bf16_ss(tO, pd + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), vd + kk * 128, idesc_pv,
+                        kk > 0 ? 1u : first);
+          mma_commit(kv_freed);
+          mma_commit(p_freed);
+          if (last) mma_commit(o_done);
+        }
+        __syncwarp();
+        if (j + 2 < nb) ok = issue_s(j + 2);
+      }
+      t += nb;
+    }
+  } else {
+    const int quad = warp & 3, colq = (warp - 2) >> 2;
+    const int col0 = colq * 32;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float LOG2E = 1.4426950408889634f;
+    const float c1 = a.scale / a.cap, c2 = a.cap * LOG2E;
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
+      uint64_t lsum = 0;  // two fp32 zeros
+      for (int j = 0; j < nb; j++) {
+        const int tt = t + j, buf = tt & 1;
+        if (!mbar_wait(s_full0 + 8 * buf, (tt >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t t_s = tS0 + buf * 128 + lane_off + col0;
+        uint32_t pk[16];
+        const bool diag = j == qb;
+        const uint64_t l_before = lsum;
+        const float big = diag ? fwd2_scores<true, true>(t_s, row, col0, c1, c2, lsum, pk)
+                               : fwd2_scores<false, true>(t_s, row, col0, c1, c2, lsum, pk);
+        if (__any_sync(0xffffffffu, !(big <= TANH_POLY_LIMIT2))) {  // out of the polynomial's range (or NaN)
+          lsum = l_before;
+          if (diag) fwd2_scores<true, false>(t_s, row, col0, c1, c2, lsum, pk);
+          else fwd2_scores<false, false>(t_s, row, col0, c1, c2, lsum, pk);
+        }
+        // the P buffer is free once O += P V of two tiles ago has read it
+        if (tt >= 2 && !mbar_wait(p_free0 + 8 * buf, ((tt >> 1) - 1) & 1, abort_flag)) { ok = false; break; }
+        uint8_t *p_row = smem + AF2_P + buf * 2 * AT_TILE + (colq >> 1) * AT_TILE + row * 128;
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          const int off = (((colq & 1) * 4 + q) ^ (row & 7)) * 16;
+          *reinterpret_cast<uint4 *>(p_row + off) = make_uint4(pk[4 * q], pk[4 * q + 1], pk[4 * q + 2], pk[4 * q + 3]);
+        }
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(p_ready0 + 8 * buf);
+      }
+      if (!ok) break;
+      t += nb;
+      // row sums of the four column quarters meet in shared memory
+      float la, lb;
+      f2_unpack(lsum, la, lb);
+      lsm[colq * 128 + row] = la + lb;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(l_ready);
+      if (!mbar_wait(l_ready, n & 1, abort_flag)) { ok = false; break; }
+      const float l = (lsm[row] + lsm[128 + row]) + (lsm[256 + row] + lsm[384 + row]);
+      if (!mbar_wait(o_done, n & 1, abort_flag)) { ok = false; break; }
+      tc_fence_after();
+      const int qi = qb * 128 + row;
+      uint32_t r[16];
+      tmem_ld_32x16(tO + lane_off + colq * 16, r);
+      tmem_ld_wait();
+      tc_fence_before();
+      if (qi < a.T) {
+        const float inv = 1.f / l;
+        __nv_bfloat16 *orow = (__nv_bfloat16 *)a.o + (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + (int64_t)qi * a.o_st +
+                              colq * 16;
+#pragma unroll
+        for (int q = 0; q < 2; q++) {
+          float f[8];
+#pragma unroll
+          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]) * inv;
+          Vec16<__nv_bfloat16> v;
+          v.set(f);
+          v.store(orow + q * 8);
+        }
+        if (colq == 0) a.lse[(int64_t)bh * a.T + qi] = (c2 + log2f(l)) * 0.6931471805599453f;
+      }
+      // No barrier is needed before the next item: its first tile's P is announced by all
+      // sixteen warps only after each has finished this read of the row sums and of O, and
+      // both are rewritten only after that announcement.
+    }
+  }
+
+  if (*abort_flag) {
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 0xAA000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, TMEM_COLS);
+  }
+}
+
 // ── host ────────────────────────────────────────────────────────────────────
 struct Tmap4Key {
   uint64_t base, T, H, B, st, sh, sb;
@@ -942,7 +1254,17 @@ int attn_tc_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf ls
   static bool attr = false;
   if (!attr) {
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF_DYN));
+    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF2_DYN));
     attr = true;
+  }
+  if (p->soft_cap > 0.f && p->soft_cap * 1.4426950408889634f <= AF2_MAX_C2) {
+    // bounded scores: the persistent kernel without a running maximum
+    const int BH = (int)(p->batch * p->heads);
+    const int n_items = (int)((p->T + 127) / 128) * BH;
+    const int grid2 = n_items < g_sm_count ? n_items : g_sm_count;
+    attn_tc_fwd2_kernel<<<grid2, AF2_THREADS, AF2_DYN, g_stream>>>(tq, tk, tv, a, n_items, BH);
+    ALPHA_LAUNCHED();
+    return 0;
   }
   dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
   attn_tc_fwd_kernel<<<grid, AT_THREADS, AF_DYN, g_stream>>>(tq, tk, tv, a);
