@@ -247,6 +247,20 @@ class CudaBackend:
             t._host = None
         return t
 
+    def pinned_array(self, shape, np_dtype):
+        """A numpy array over page-locked host memory (uploads from it are asynchronous) and
+        the handle that keeps the allocation alive; free it with ``free_pinned``."""
+        nbytes = int(np.prod(shape)) * np.dtype(np_dtype).itemsize
+        p = C.c_void_p()
+        check(self.lib.alpha_host_alloc(max(nbytes, 1), C.byref(p)))
+        buf = (C.c_char * max(nbytes, 1)).from_address(p.value)
+        arr = np.frombuffer(buf, dtype=np_dtype, count=int(np.prod(shape))).reshape(shape)
+        arr[...] = 0
+        return arr, p
+
+    def free_pinned(self, handle) -> None:
+        check(self.lib.alpha_host_free(handle))
+
     # ── elementwise (interfaces.ts:49-71) ────────────────────────────────────
     def _binary(self, op: int, a: TensorData, b: TensorData) -> TensorData:
         if a.dtype != b.dtype:

@@ -7,6 +7,8 @@ instead: uniform over the vocabulary, or Zipf(s) with p(k) ~ 1/(k+1)^s.
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 
 
@@ -28,3 +30,96 @@ def zipf_batches(seed: int, n_steps: int, batch: int, T: int, vocab: int, s: flo
         u = g.random(size=(batch, T + 1))
         out.append(_windows(np.minimum(np.searchsorted(cdf, u), vocab - 1).astype(np.int32)))
     return out
+
+
+class DataLoader:
+    """Batches of (inputs, targets) int32 [B, T] windows from a token array — the reference's
+    DataLoader (packages/train/src/data.ts:18-177) with per-rank sharding added for data
+    parallel runs.
+
+    random mode (data.ts:91-119): every batch item starts at ``floor(rng.next() * (N - T))``;
+    one draw per item, in item order.  With ``world > 1`` all ranks consume the same stream
+    of draws and rank r keeps items r*B .. r*B+B-1 of every global batch of B*world, so the
+    union over ranks equals the single-process loader with batch B*world.
+    packed mode (data.ts:130-167): cursors ``b * floor(N / (B*world))`` advance by T per batch
+    and wrap at N; the target of the last token of the corpus is token 0.  Rank r owns
+    cursors r*B .. r*B+B-1.
+
+    Two reusable host buffers alternate between calls (data.ts:48-58); ``pin`` puts them in
+    page-locked memory so that ``to_device`` is a plain asynchronous copy.
+    """
+
+    def __init__(self, tokens, rng, batchSize: int, blockSize: int, packed: bool = False, rank: int = 0,
+                 world: int = 1, backend=None, pin: bool = False):
+        self.tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        self.rng, self.batchSize, self.blockSize, self.packed = rng, int(batchSize), int(blockSize), bool(packed)
+        self.rank, self.world = int(rank), int(world)
+        self.backend = backend
+        n = len(self.tokens)
+        if self.packed:
+            stride = n // (self.batchSize * self.world)
+            self.cursors = [(self.rank * self.batchSize + b) * stride for b in range(self.batchSize)]
+        self._ring = []
+        self._pinned = []
+        elems = self.batchSize * self.blockSize
+        for _ in range(2):
+            if pin and backend is not None:
+                a, pa = backend.pinned_array((self.batchSize, self.blockSize), np.int32)
+                b, pb = backend.pinned_array((self.batchSize, self.blockSize), np.int32)
+                self._pinned += [pa, pb]
+            else:
+                a = np.zeros((self.batchSize, self.blockSize), np.int32)
+                b = np.zeros((self.batchSize, self.blockSize), np.int32)
+            assert a.size == elems
+            self._ring.append((a, b))
+        self._idx = 0
+
+    @property
+    def stepsPerEpoch(self) -> int:
+        return len(self.tokens) // (self.batchSize * self.blockSize * self.world)
+
+    def __len__(self) -> int:
+        return len(self.tokens)
+
+    def nextBatch(self):
+        """(inputs, targets): int32 [B, T] host arrays, valid until the call after next."""
+        inputs, targets = self._ring[self._idx]
+        self._idx = (self._idx + 1) % len(self._ring)
+        B, T, N, tok = self.batchSize, self.blockSize, len(self.tokens), self.tokens
+        if not self.packed:
+            if N <= T:
+                raise ValueError(f"Token count ({N}) must exceed block size ({T}) — need at least {T + 1} tokens "
+                                 "for input+target windows")
+            maxStart = N - T
+            for g in range(B * self.world):
+                start = int(math.floor(self.rng.next() * maxStart))
+                b = g - self.rank * B
+                if 0 <= b < B:
+                    inputs[b] = tok[start:start + T]
+                    targets[b] = tok[start + 1:start + T + 1]
+            return inputs, targets
+        for b in range(B):
+            pos, remaining, dst = self.cursors[b], T, 0
+            while remaining > 0:
+                span = min(remaining, N - pos)
+                inputs[b, dst:dst + span] = tok[pos:pos + span]
+                if pos + span < N:
+                    targets[b, dst:dst + span] = tok[pos + 1:pos + span + 1]
+                else:
+                    if span > 1:
+                        targets[b, dst:dst + span - 1] = tok[pos + 1:N]
+                    targets[b, dst + span - 1] = tok[0]
+                dst += span
+                remaining -= span
+                pos += span
+                if pos == N:
+                    pos = 0
+            self.cursors[b] = pos
+        return inputs, targets
+
+    def nextDeviceBatch(self):
+        """The next batch as device tensors (uploaded on the backend's stream; with pinned
+        buffers the copy is asynchronous and the buffer is not reused before the call after
+        next, by which time the copy has been consumed by a step)."""
+        inputs, targets = self.nextBatch()
+        return self.backend.upload(inputs, "i32"), self.backend.upload(targets, "i32")

@@ -238,8 +238,10 @@ def _block_fused(ctx: Ctx, cfg: ModelConfig, x: Variable, P: GPTParams, i: int, 
 
 def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: Tape, tokens: TensorData,
                targets: TensorData | None = None, training: bool = False, attention: str = "fused",
-               dropoutRng=None, release=None, lossGradScale: float = 1.0):
-    """gpt.ts:344-427.  tokens/targets: int32 [B, T].  Returns {"logits": Variable|None, "loss": Variable|None}."""
+               dropoutRng=None, release=None, lossGradScale: float = 1.0, lastOnly: bool = False):
+    """gpt.ts:344-427.  tokens/targets: int32 [B, T].  Returns {"logits": Variable|None, "loss": Variable|None}.
+    ``lastOnly`` (fused route, no targets): project only each sequence's last position —
+    logits [B, 1, V], what sampling reads (sample.ts:62-72) — instead of all T rows."""
     ctx = Ctx(tape, backend, dropoutRng, release)
     Bn, T = tokens.shape
     E = cfg.nEmbd
@@ -263,6 +265,13 @@ def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: 
         if targets is not None:
             tflat = backend.reshape(targets, (Bn * T,))
             return {"logits": None, "loss": ag.lmHeadLoss(ctx, x, head, tflat, lossGradScale)}
+        if lastOnly:
+            idx = backend.upload(np.arange(Bn, dtype=np.int32) * T + (T - 1), "i32")
+            last = backend.embedding(x.data, idx)                  # row gather: [B, E]
+            logits = backend.matmulTransposed(last, ag._compute_weight(head))
+            backend.releaseGpuTensor(idx)
+            backend.releaseGpuTensor(last)
+            return {"logits": ag.Variable(backend.reshape(logits, (Bn, 1, cfg.vocabSize)), False), "loss": None}
         return {"logits": ag.reshape(ctx, ag.linear(ctx, x, head), (Bn, T, cfg.vocabSize)), "loss": None}
 
     # reference-shaped routes

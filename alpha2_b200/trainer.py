@@ -248,3 +248,15 @@ class Trainer:
     # ── state exchange with the host (checkpointing needs exactly this) ───────
     def host_params(self) -> dict:
         return {n: np.array(v.data.data, dtype=np.float32) for n, v in self.entries}
+
+    def load_param(self, name: str, host: np.ndarray) -> None:
+        """Replace one parameter's fp32 master by host values (and rebuild its bf16 compute copy)."""
+        v = dict(self.entries)[name]
+        old, old_shadow = v.data, getattr(v, "shadow", None)
+        v.data = self.B.upload(np.ascontiguousarray(host, dtype=np.float32).reshape(old.shape), "f32")
+        if old_shadow is not None:
+            v.shadow = self.B.castDtype(v.data, old_shadow.dtype)
+        if self.releaseFn is not None:
+            self.releaseFn(old)
+            if old_shadow is not None:
+                self.releaseFn(old_shadow)
