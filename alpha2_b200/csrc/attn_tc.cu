@@ -487,40 +487,45 @@ constexpr int AK_P = AK_DO + AK_STAGES * AT_TILE;          // 2 tiles (key halve
 constexpr int AK_DS = AK_P + 2 * AT_TILE;                  // 2 tiles
 constexpr int AK_BAR = AK_DS + 2 * AT_TILE;
 constexpr int AK_DYN = AK_BAR + 256 + 1024;
+constexpr int ABP_THREADS = AB_THREADS + 128;              // + four epilogue warps
 
-// Pipeline of the dK/dV kernel (tile index `it` walks the query blocks of this key block):
+// Pipeline of the dK/dV kernel.  One CTA per SM walks (batch*head, key block) items, longest
+// first; inside an item the tile index `it` walks the query blocks of the key block:
 //   tensor core, on "tile it-1 stored" : dP(it)  ->  dV,dK += (P,dS)(it-1)  ->  S(it+1)
 //   math warps                          : phase A(it) from S(it) | wait dP(it) and the end of
 //                                         dV,dK(it-1) | phase B(it) stores P,dS | signal
+//   epilogue warps (one per lane quadrant): when an item's last products are done they write
+//                                         dV, dK while everybody else is on the next item
 // S has two TMEM buffers, so the scores of the next tile are ready before the math warps ask
-// for them and the tensor core works while they compute.
-__global__ void __launch_bounds__(AB_THREADS, 1)
+// for them.  K and V of the next item are fetched as soon as the current item's last dP has
+// been issued (the gradient products do not read them).  All barrier phases are running
+// counters over items (n) and tiles (t).
+__global__ void __launch_bounds__(ABP_THREADS, 1)
 attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                       AttnBwdArgs a) {
+                       AttnBwdArgs a, int n_items, int BH) {
   extern __shared__ uint8_t at_smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AK_BAR;
-  const uint32_t kv_full = bar, s_full0 = bar + 8, dp_full = bar + 24, pds_ready = bar + 32, acc_done = bar + 40,
-                 q_full0 = bar + 48, q_empty0 = q_full0 + 8 * AK_STAGES;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 48 + 16 * AK_STAGES);
+  const uint32_t kv_full = bar, kv_empty = bar + 8, s_full0 = bar + 16, dp_full = bar + 32, pds_ready = bar + 40,
+                 acc_done = bar + 48, acc_final = bar + 56, acc_free = bar + 64, q_full0 = bar + 72,
+                 q_empty0 = q_full0 + 8 * AK_STAGES;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 72 + 16 * AK_STAGES);
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (a.T + 127) / 128;
-  const int kb = blockIdx.x;            // key block; it has n_qb - kb query blocks to visit
-  const int bh = blockIdx.y;
-  const int b = bh / a.H, h = bh - b * a.H;
-  const int k0 = kb * 128;
-  const int n_it = n_qb - kb;
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
     mbar_init(kv_full, 1);
+    mbar_init(kv_empty, 1);
     mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
     mbar_init(dp_full, 1);
     mbar_init(pds_ready, AB_MATH_WARPS);
     mbar_init(acc_done, 1);
+    mbar_init(acc_final, 1);
+    mbar_init(acc_free, 4);
     for (int s = 0; s < AK_STAGES; s++) {
       mbar_init(q_full0 + 8 * s, 1);
       mbar_init(q_empty0 + 8 * s, 1);
@@ -539,24 +544,38 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdV = tmem_base + 384, tdK = tmem_base + 448;
 
+  // item -> (batch*head, key block): key block 0 has the most query blocks to visit
+  auto decode = [&](int item, int &bh, int &kb) {
+    kb = item / BH;
+    bh = item - kb * BH;
+  };
+
   if (warp == 0) {
-    // TMA producer: the warp runs the loop, one elected lane issues
-    if (elect_one()) {
-      mbar_expect_tx(kv_full, 2 * AT_TILE);
-      tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, k0, h, b);
-      tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, k0, h, b);
-    }
-    __syncwarp();
-    for (int it = 0; it < n_it; it++) {
-      const int st = it % AK_STAGES;
-      if (!mbar_wait(q_empty0 + 8 * st, ((it / AK_STAGES) & 1) ^ 1, abort_flag)) break;
-      const int q0 = (kb + it) * 128;
+    // TMA producer: the warp runs the loops, one elected lane issues
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, kb;
+      decode(item, bh, kb);
+      const int b = bh / a.H, h = bh - b * a.H, n_it = n_qb - kb;
+      if (!mbar_wait(kv_empty, (n & 1) ^ 1, abort_flag)) break;
       if (elect_one()) {
-        mbar_expect_tx(q_full0 + 8 * st, 2 * AT_TILE);
-        tma_load_4d(sb + AK_Q + st * AT_TILE, &tmap_q, q_full0 + 8 * st, 0, q0, h, b);
-        tma_load_4d(sb + AK_DO + st * AT_TILE, &tmap_do, q_full0 + 8 * st, 0, q0, h, b);
+        mbar_expect_tx(kv_full, 2 * AT_TILE);
+        tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, kb * 128, h, b);
+        tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, kb * 128, h, b);
       }
       __syncwarp();
+      for (int it = 0; it < n_it; it++, t++) {
+        const int st = t % AK_STAGES;
+        if (!mbar_wait(q_empty0 + 8 * st, ((t / AK_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        const int q0 = (kb + it) * 128;
+        if (elect_one()) {
+          mbar_expect_tx(q_full0 + 8 * st, 2 * AT_TILE);
+          tma_load_4d(sb + AK_Q + st * AT_TILE, &tmap_q, q_full0 + 8 * st, 0, q0, h, b);
+          tma_load_4d(sb + AK_DO + st * AT_TILE, &tmap_do, q_full0 + 8 * st, 0, q0, h, b);
+        }
+        __syncwarp();
+      }
     }
   } else if (warp == 1) {
     // MMA issuer: warp-uniform control flow and descriptors, one elected lane issues
@@ -566,53 +585,69 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint64_t d_q_k = make_smem_desc(sb + AK_Q, 16, 1024), d_do_k = make_smem_desc(sb + AK_DO, 16, 1024);
     const uint64_t d_q_n = make_smem_desc(sb + AK_Q, AT_TILE, 1024), d_do_n = make_smem_desc(sb + AK_DO, AT_TILE, 1024);
     const uint64_t d_p = make_smem_desc(sb + AK_P, AT_TILE, 1024), d_ds = make_smem_desc(sb + AK_DS, AT_TILE, 1024);
-    auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer it & 1 (waits for the tile's loads)
-      const int st = it % AK_STAGES;
-      if (!mbar_wait(q_full0 + 8 * st, (it / AK_STAGES) & 1, abort_flag)) return false;
-      tc_fence_after();
-      const uint64_t qd = d_q_k + (uint64_t)((st * AT_TILE) >> 4);
-      const uint32_t t = tS0 + (it & 1) * 128, done = s_full0 + 8 * (it & 1);
-      if (elect_one()) {
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, kb;
+      decode(item, bh, kb);
+      const int n_it = n_qb - kb;
+      auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer (t + it) & 1 (waits for the tile's loads)
+        const int tt = t + it, st = tt % AK_STAGES;
+        if (!mbar_wait(q_full0 + 8 * st, (tt / AK_STAGES) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t qd = d_q_k + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(t, qd + kk * 2, d_k + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(done);
+          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, qd + kk * 2, d_k + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          mma_commit(done);
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dp = [&](int it) {          // dP(it) = dO(it) V^T (loads already awaited by issue_s(it))
+        const uint64_t dd = d_do_k + (uint64_t)((((t + it) % AK_STAGES) * AT_TILE) >> 4);
+        const bool last = it == n_it - 1;
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, dd + kk * 2, d_v + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          mma_commit(dp_full);
+          if (last) mma_commit(kv_empty);    // K and V are not read after the item's last dP
+        }
+        __syncwarp();
+      };
+      ok = mbar_wait(kv_full, n & 1, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
+      if (ok && n_it > 1) ok = issue_s(1);
+      for (int it = 0; it < n_it && ok; it++) {
+        const int tt = t + it;
+        if (!mbar_wait(pds_ready, tt & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (it + 1 < n_it) issue_dp(it + 1);
+        // the epilogue warps must have read the previous item's dV / dK before they are overwritten
+        if (it == 0 && n > 0 && !mbar_wait(acc_free, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const int st = tt % AK_STAGES;
+        const uint64_t qn = d_q_n + (uint64_t)((st * AT_TILE) >> 4), don = d_do_n + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t first = it > 0 ? 1u : 0u, freed = q_empty0 + 8 * st;
+        const bool last = it == n_it - 1;
+        if (elect_one()) {
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++)  // 16 query rows per step
+            mma_bf16_ss(tdV, d_p + kk * 128, don + kk * 128, idesc_g, kk > 0 ? 1u : first);
+#pragma unroll
+          for (int kk = 0; kk < 8; kk++) mma_bf16_ss(tdK, d_ds + kk * 128, qn + kk * 128, idesc_g, kk > 0 ? 1u : first);
+          mma_commit(freed);
+          mma_commit(acc_done);
+          if (last) mma_commit(acc_final);
+        }
+        __syncwarp();
+        if (it + 2 < n_it) ok = issue_s(it + 2);
       }
-      __syncwarp();
-      return true;
-    };
-    auto issue_dp = [&](int it) {          // dP(it) = dO(it) V^T (loads already awaited by issue_s(it))
-      const uint64_t dd = d_do_k + (uint64_t)(((it % AK_STAGES) * AT_TILE) >> 4);
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, dd + kk * 2, d_v + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(dp_full);
-      }
-      __syncwarp();
-    };
-    bool ok = mbar_wait(kv_full, 0, abort_flag);
-    if (ok) ok = issue_s(0);
-    if (ok) issue_dp(0);
-    if (ok && n_it > 1) ok = issue_s(1);
-    for (int it = 0; it < n_it && ok; it++) {
-      if (!mbar_wait(pds_ready, it & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      if (it + 1 < n_it) issue_dp(it + 1);
-      const int st = it % AK_STAGES;
-      const uint64_t qn = d_q_n + (uint64_t)((st * AT_TILE) >> 4), don = d_do_n + (uint64_t)((st * AT_TILE) >> 4);
-      const uint32_t first = it > 0 ? 1u : 0u, freed = q_empty0 + 8 * st;
-      if (elect_one()) {
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++)  // 16 query rows per step
-          mma_bf16_ss(tdV, d_p + kk * 128, don + kk * 128, idesc_g, kk > 0 ? 1u : first);
-#pragma unroll
-        for (int kk = 0; kk < 8; kk++) mma_bf16_ss(tdK, d_ds + kk * 128, qn + kk * 128, idesc_g, kk > 0 ? 1u : first);
-        mma_commit(freed);
-        mma_commit(acc_done);
-      }
-      __syncwarp();
-      if (it + 2 < n_it) ok = issue_s(it + 2);
+      t += n_it;
     }
-  } else {
+  } else if (warp < 2 + AB_MATH_WARPS) {
     const int quad = warp & 3, colq = (warp - 2) >> 2;  // lane quadrant, 32-column quarter
     const int col0 = colq * AB_NC;
     const int row = quad * 32 + lane;
@@ -625,47 +660,69 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     k.scale = a.scale;
     uint8_t *p_row = smem + AK_P + (colq >> 1) * AT_TILE + row * 128;
     uint8_t *ds_row = smem + AK_DS + (colq >> 1) * AT_TILE + row * 128;
+    int t = 0;
     bool ok = true;
-    for (int it = 0; it < n_it && ok; it++) {
-      const int qi = (kb + it) * 128 + row;
-      const bool valid = qi < a.T;
-      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
-      k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-      uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
-      if (!mbar_wait(s_full0 + 8 * (it & 1), (it >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      bwd_phase_a_any(tS0 + (it & 1) * 128 + lane_off + col0, row, col0, it == 0, capped, k, pk, fk);
-      if (!mbar_wait(dp_full, it & 1, abort_flag)) { ok = false; break; }
-      // the gradient products of the previous tile must have finished reading the P / dS tiles
-      if (it > 0 && !mbar_wait(acc_done, (it - 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      bwd_phase_b<true>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, p_row, ds_row);
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(pds_ready);
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      int bh, kb;
+      decode(item, bh, kb);
+      const int n_it = n_qb - kb;
+      for (int it = 0; it < n_it; it++) {
+        const int tt = t + it;
+        const int qi = (kb + it) * 128 + row;
+        const bool valid = qi < a.T;
+        k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
+        k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+        uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
+        if (!mbar_wait(s_full0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        bwd_phase_a_any(tS0 + (tt & 1) * 128 + lane_off + col0, row, col0, it == 0, capped, k, pk, fk);
+        if (!mbar_wait(dp_full, tt & 1, abort_flag)) { ok = false; break; }
+        // the gradient products of the previous tile must have finished reading the P / dS tiles
+        if (tt > 0 && !mbar_wait(acc_done, (tt - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        bwd_phase_b<true>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, p_row, ds_row);
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(pds_ready);
+      }
+      t += n_it;
     }
-    if (ok && mbar_wait(acc_done, (n_it - 1) & 1, abort_flag)) {
+  } else {
+    // epilogue warps: quadrant q writes rows 32q .. 32q+31 of dV and dK of every finished item
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    int n = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+      int bh, kb;
+      decode(item, bh, kb);
+      const int b = bh / a.H, h = bh - b * a.H;
+      if (!mbar_wait(acc_final, n & 1, abort_flag)) break;
       tc_fence_after();
-      // accumulator lanes are keys; the four column quarters store dV[0:32], dV[32:64], dK[0:32], dK[32:64]
-      const int kj = k0 + row, c = colq & 1;
+      const int kj = kb * 128 + row;  // accumulator lanes are keys
       const int64_t off = (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)kj * a.q_st;
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)((colq >> 1) ? a.dk : a.dv) + off;
-      const uint32_t tacc = (colq >> 1) ? tdK : tdV;
-      uint32_t r[32];
-      tmem_ld_32x32(tacc + lane_off + c * 32, r);
-      tmem_ld_wait();
-      if (kj < a.T) {
+#pragma unroll 1
+      for (int c = 0; c < 4; c++) {   // dV[0:32], dV[32:64], dK[0:32], dK[32:64]
+        uint32_t r[32];
+        tmem_ld_32x32((c < 2 ? tdV : tdK) + lane_off + (c & 1) * 32, r);
+        tmem_ld_wait();
+        if (kj < a.T) {
+          __nv_bfloat16 *dst = (__nv_bfloat16 *)(c < 2 ? a.dv : a.dk) + off + (c & 1) * 32;
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          float f[8];
+          for (int q = 0; q < 4; q++) {
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-          Vec16<__nv_bfloat16> v;
-          v.set(f);
-          v.store(dst + c * 32 + q * 8);
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(dst + q * 8);
+          }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_free);
     }
   }
 
@@ -693,36 +750,36 @@ constexpr int AQ_DS = AQ_V + AQ_STAGES * AT_TILE;          // 2 tiles (key halve
 constexpr int AQ_BAR = AQ_DS + 2 * AT_TILE;
 constexpr int AQ_DYN = AQ_BAR + 256 + 1024;
 
-// Same pipeline as the dK/dV kernel with the roles of the operands exchanged: the tile index j
-// walks the key blocks of this query block, (K, V) tiles come through the ring, and the only
+// Same pipeline as the dK/dV kernel with the roles of the operands exchanged: items are
+// (batch*head, query block), the tile index j walks the key blocks of the query block,
+// (K, V) tiles come through the ring, Q and dO are the per-item operands, and the only
 // gradient product is dQ += dS K.
-__global__ void __launch_bounds__(AB_THREADS, 1)
+__global__ void __launch_bounds__(ABP_THREADS, 1)
 attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                       const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                      AttnBwdArgs a) {
+                      AttnBwdArgs a, int n_items, int BH) {
   extern __shared__ uint8_t at_smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AQ_BAR;
-  const uint32_t q_full = bar, s_full0 = bar + 8, dp_full = bar + 24, ds_ready = bar + 32, acc_done = bar + 40,
-                 kv_full0 = bar + 48, kv_empty0 = kv_full0 + 8 * AQ_STAGES;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 48 + 16 * AQ_STAGES);
+  const uint32_t q_full = bar, q_empty = bar + 8, s_full0 = bar + 16, dp_full = bar + 32, ds_ready = bar + 40,
+                 acc_done = bar + 48, acc_final = bar + 56, acc_free = bar + 64, kv_full0 = bar + 72,
+                 kv_empty0 = kv_full0 + 8 * AQ_STAGES;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 72 + 16 * AQ_STAGES);
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (a.T + 127) / 128;
-  const int qb = n_qb - 1 - (int)blockIdx.x;  // long rows first
-  const int bh = blockIdx.y;
-  const int b = bh / a.H, h = bh - b * a.H;
-  const int q0 = qb * 128;
-  const int nb = qb + 1;
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
+    mbar_init(q_empty, 1);
     mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
     mbar_init(dp_full, 1);
     mbar_init(ds_ready, AB_MATH_WARPS);
     mbar_init(acc_done, 1);
+    mbar_init(acc_final, 1);
+    mbar_init(acc_free, 4);
     for (int s = 0; s < AQ_STAGES; s++) {
       mbar_init(kv_full0 + 8 * s, 1);
       mbar_init(kv_empty0 + 8 * s, 1);
@@ -741,22 +798,36 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdQ = tmem_base + 384;
 
+  // item -> (batch*head, query block): the last query block has the most key blocks to visit
+  auto decode = [&](int item, int &bh, int &qb) {
+    qb = n_qb - 1 - item / BH;
+    bh = item - (item / BH) * BH;
+  };
+
   if (warp == 0) {
-    if (elect_one()) {
-      mbar_expect_tx(q_full, 2 * AT_TILE);
-      tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, q0, h, b);
-      tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, q0, h, b);
-    }
-    __syncwarp();
-    for (int j = 0; j < nb; j++) {
-      const int st = j % AQ_STAGES;
-      if (!mbar_wait(kv_empty0 + 8 * st, ((j / AQ_STAGES) & 1) ^ 1, abort_flag)) break;
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
+      if (!mbar_wait(q_empty, (n & 1) ^ 1, abort_flag)) break;
       if (elect_one()) {
-        mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
-        tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
-        tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
+        mbar_expect_tx(q_full, 2 * AT_TILE);
+        tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, qb * 128, h, b);
+        tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, qb * 128, h, b);
       }
       __syncwarp();
+      for (int j = 0; j < nb; j++, t++) {
+        const int st = t % AQ_STAGES;
+        if (!mbar_wait(kv_empty0 + 8 * st, ((t / AQ_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+        if (elect_one()) {
+          mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
+          tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
+          tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
+        }
+        __syncwarp();
+      }
     }
   } else if (warp == 1) {
     constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
@@ -765,104 +836,140 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint64_t d_k_k = make_smem_desc(sb + AQ_K, 16, 1024), d_v_k = make_smem_desc(sb + AQ_V, 16, 1024);
     const uint64_t d_k_n = make_smem_desc(sb + AQ_K, AT_TILE, 1024);
     const uint64_t d_ds = make_smem_desc(sb + AQ_DS, 16, 1024);
-    auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer j & 1 (waits for the tile's loads)
-      const int st = j % AQ_STAGES;
-      if (!mbar_wait(kv_full0 + 8 * st, (j / AQ_STAGES) & 1, abort_flag)) return false;
-      tc_fence_after();
-      const uint64_t kd = d_k_k + (uint64_t)((st * AT_TILE) >> 4);
-      const uint32_t t = tS0 + (j & 1) * 128, done = s_full0 + 8 * (j & 1);
-      if (elect_one()) {
+    int t = 0, n = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int nb = qb + 1;
+      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer (t + j) & 1 (waits for the tile's loads)
+        const int tt = t + j, st = tt % AQ_STAGES;
+        if (!mbar_wait(kv_full0 + 8 * st, (tt / AQ_STAGES) & 1, abort_flag)) return false;
+        tc_fence_after();
+        const uint64_t kd = d_k_k + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1);
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(t, d_q + kk * 2, kd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(done);
-      }
-      __syncwarp();
-      return true;
-    };
-    auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
-      const uint64_t vd = d_v_k + (uint64_t)(((j % AQ_STAGES) * AT_TILE) >> 4);
-      if (elect_one()) {
+          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, d_q + kk * 2, kd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          mma_commit(done);
+        }
+        __syncwarp();
+        return true;
+      };
+      auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
+        const uint64_t vd = d_v_k + (uint64_t)((((t + j) % AQ_STAGES) * AT_TILE) >> 4);
+        const bool last = j == nb - 1;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, d_do + kk * 2, vd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-        mma_commit(dp_full);
-      }
-      __syncwarp();
-    };
-    bool ok = mbar_wait(q_full, 0, abort_flag);
-    if (ok) ok = issue_s(0);
-    if (ok) issue_dp(0);
-    if (ok && nb > 1) ok = issue_s(1);
-    for (int j = 0; j < nb && ok; j++) {
-      if (!mbar_wait(ds_ready, j & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      if (j + 1 < nb) issue_dp(j + 1);
-      const int st = j % AQ_STAGES;
-      const uint64_t kn = d_k_n + (uint64_t)((st * AT_TILE) >> 4);
-      const uint32_t first = j > 0 ? 1u : 0u, freed = kv_empty0 + 8 * st;
-      if (elect_one()) {
+          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, d_do + kk * 2, vd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
+          mma_commit(dp_full);
+          if (last) mma_commit(q_empty);     // Q and dO are not read after the item's last dP
+        }
+        __syncwarp();
+      };
+      ok = mbar_wait(q_full, n & 1, abort_flag);
+      if (ok) ok = issue_s(0);
+      if (ok) issue_dp(0);
+      if (ok && nb > 1) ok = issue_s(1);
+      for (int j = 0; j < nb && ok; j++) {
+        const int tt = t + j;
+        if (!mbar_wait(ds_ready, tt & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        if (j + 1 < nb) issue_dp(j + 1);
+        if (j == 0 && n > 0 && !mbar_wait(acc_free, (n - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        const int st = tt % AQ_STAGES;
+        const uint64_t kn = d_k_n + (uint64_t)((st * AT_TILE) >> 4);
+        const uint32_t first = j > 0 ? 1u : 0u, freed = kv_empty0 + 8 * st;
+        const bool last = j == nb - 1;
+        if (elect_one()) {
 #pragma unroll
-        for (int kk = 0; kk < 8; kk++)  // 16 keys per step; dS tile (kk >> 2), 32 bytes per step inside it
-          mma_bf16_ss(tdQ, d_ds + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), kn + kk * 128, idesc_q,
-                      kk > 0 ? 1u : first);
-        mma_commit(freed);
-        mma_commit(acc_done);
+          for (int kk = 0; kk < 8; kk++)  // 16 keys per step; dS tile (kk >> 2), 32 bytes per step inside it
+            mma_bf16_ss(tdQ, d_ds + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), kn + kk * 128, idesc_q,
+                        kk > 0 ? 1u : first);
+          mma_commit(freed);
+          mma_commit(acc_done);
+          if (last) mma_commit(acc_final);
+        }
+        __syncwarp();
+        if (j + 2 < nb) ok = issue_s(j + 2);
       }
-      __syncwarp();
-      if (j + 2 < nb) ok = issue_s(j + 2);
+      t += nb;
     }
-  } else {
+  } else if (warp < 2 + AB_MATH_WARPS) {
     const int quad = warp & 3, colq = (warp - 2) >> 2;  // lane quadrant, 32-column quarter
     const int col0 = colq * AB_NC;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float LOG2E = 1.4426950408889634f;
     const bool capped = a.cap > 0.f;
-    const int qi = q0 + row;
-    const bool valid = qi < a.T;
     BwdRowConsts k;
     k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
     k.c2 = a.cap * LOG2E;
     k.scale = a.scale;
-    k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
-    k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
     uint8_t *ds_row = smem + AQ_DS + (colq >> 1) * AT_TILE + row * 128;
+    int t = 0;
     bool ok = true;
-    for (int j = 0; j < nb && ok; j++) {
-      uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
-      if (!mbar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      bwd_phase_a_any(tS0 + (j & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, k, pk, fk);
-      if (!mbar_wait(dp_full, j & 1, abort_flag)) { ok = false; break; }
-      // dQ += dS(j-1) K(j-1) must have finished reading the dS tiles
-      if (j > 0 && !mbar_wait(acc_done, (j - 1) & 1, abort_flag)) { ok = false; break; }
-      tc_fence_after();
-      bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, nullptr, ds_row);
-      fence_proxy_async();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(ds_ready);
-    }
-    if (ok && mbar_wait(acc_done, (nb - 1) & 1, abort_flag)) {
-      tc_fence_after();
-      // dQ is 64 columns: the first two column quarters of the math warps store 32 each
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st +
-                           (colq & 1) * 32;
-      uint32_t r[32];
-      if (colq < 2) {  // warp-uniform
-        tmem_ld_32x32(tdQ + lane_off + colq * 32, r);
-        tmem_ld_wait();
+    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int nb = qb + 1;
+      const int qi = qb * 128 + row;
+      const bool valid = qi < a.T;
+      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
+      k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+      for (int j = 0; j < nb; j++) {
+        const int tt = t + j;
+        uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
+        if (!mbar_wait(s_full0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        bwd_phase_a_any(tS0 + (tt & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, k, pk, fk);
+        if (!mbar_wait(dp_full, tt & 1, abort_flag)) { ok = false; break; }
+        // dQ += dS K of the previous tile must have finished reading the dS tiles
+        if (tt > 0 && !mbar_wait(acc_done, (tt - 1) & 1, abort_flag)) { ok = false; break; }
+        tc_fence_after();
+        bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, nullptr, ds_row);
+        fence_proxy_async();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(ds_ready);
       }
-      if (valid && colq < 2) {
+      t += nb;
+    }
+  } else {
+    // epilogue warps: quadrant q writes rows 32q .. 32q+31 of dQ of every finished item
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    int n = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int b = bh / a.H, h = bh - b * a.H;
+      if (!mbar_wait(acc_final, n & 1, abort_flag)) break;
+      tc_fence_after();
+      const int qi = qb * 128 + row;
+      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st;
+#pragma unroll 1
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tdQ + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (qi < a.T) {
 #pragma unroll
-        for (int q = 0; q < 4; q++) {
-          float f[8];
+          for (int q = 0; q < 4; q++) {
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-          Vec16<__nv_bfloat16> v;
-          v.set(f);
-          v.store(dst + q * 8);
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(dst + c * 32 + q * 8);
+          }
         }
       }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_free);
     }
   }
 
@@ -1302,10 +1409,12 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AQ_DYN));
     attr = true;
   }
-  dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
-  attn_tc_bwd_dkv_kernel<<<grid, AB_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  const int BH = (int)(p->batch * p->heads);
+  const int n_items = (int)((p->T + 127) / 128) * BH;
+  const int grid = n_items < g_sm_count ? n_items : g_sm_count;
+  attn_tc_bwd_dkv_kernel<<<grid, ABP_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a, n_items, BH);
   g_launches++;
-  attn_tc_bwd_dq_kernel<<<grid, AB_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a);
+  attn_tc_bwd_dq_kernel<<<grid, ABP_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a, n_items, BH);
   pool_free(delta);
   ALPHA_LAUNCHED();
   return 0;
