@@ -1004,16 +1004,18 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 //               (two S buffers in TMEM), O += P(j) V(j) when P(j) is in shared memory (two P
 //               buffers), so the tensor core works while the math warps compute
 //   warps 2-17  math warps
+//   warps 18-21 epilogue warps (one per lane quadrant): combine the row sums, scale O, write
+//               O and LSE while the other warps are already on the next item
 // All barrier phases are running counters over items and tiles; every wait is bounded.
-constexpr int AF2_THREADS = 64 + 32 * 16;
+constexpr int AF2_THREADS = 64 + 32 * 16 + 128;
 constexpr int AF2_KST = 3, AF2_VST = 4;
 constexpr int AF2_Q = 0;                                   // 2 buffers
 constexpr int AF2_K = 2 * AT_TILE;
 constexpr int AF2_V = AF2_K + AF2_KST * AT_TILE;
 constexpr int AF2_P = AF2_V + AF2_VST * AT_TILE;           // 2 buffers x 2 tiles (key halves)
 constexpr int AF2_BAR = AF2_P + 4 * AT_TILE;
-constexpr int AF2_LSUM = AF2_BAR + 256;                    // [4 column quarters][128 rows] floats
-constexpr int AF2_DYN = AF2_LSUM + 2048 + 1024;
+constexpr int AF2_LSUM = AF2_BAR + 256;                    // [2 items][4 column quarters][128 rows] floats
+constexpr int AF2_DYN = AF2_LSUM + 4096 + 1024;
 constexpr float AF2_MAX_C2 = 50.f;                         // largest cap*log2(e) this kernel accepts
 
 // P for 32 scores of one row (bounded-score softmax).  Returns the largest squared tanh
@@ -1070,9 +1072,9 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AF2_BAR;
   const uint32_t q_full0 = bar, q_empty0 = bar + 16, s_full0 = bar + 32, p_ready0 = bar + 48, p_free0 = bar + 64,
-                 o_done = bar + 80, l_ready = bar + 88, k_full0 = bar + 96, k_empty0 = k_full0 + 8 * AF2_KST,
-                 v_full0 = k_empty0 + 8 * AF2_KST, v_empty0 = v_full0 + 8 * AF2_VST;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AF2_BAR + 96 + 16 * (AF2_KST + AF2_VST));
+                 o_done = bar + 80, l_ready = bar + 88, o_free = bar + 96, k_full0 = bar + 104,
+                 k_empty0 = k_full0 + 8 * AF2_KST, v_full0 = k_empty0 + 8 * AF2_KST, v_empty0 = v_full0 + 8 * AF2_VST;
+  uint32_t *tmem_slot = (uint32_t *)(smem + AF2_BAR + 104 + 16 * (AF2_KST + AF2_VST));
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   float *lsm = reinterpret_cast<float *>(smem + AF2_LSUM);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1089,6 +1091,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     mbar_init(o_done, 1);
     mbar_init(l_ready, 16);
+    mbar_init(o_free, 4);
     for (int s = 0; s < AF2_KST; s++) {
       mbar_init(k_full0 + 8 * s, 1);
       mbar_init(k_empty0 + 8 * s, 1);
@@ -1186,6 +1189,8 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         const int tt = t + j, st = tt % AF2_VST;
         if (!mbar_wait(p_ready0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
         if (!mbar_wait(v_full0 + 8 * st, (tt / AF2_VST) & 1, abort_flag)) { ok = false; break; }
+        // the epilogue warps must have read the previous item's O before it is overwritten
+        if (j == 0 && n > 0 && !mbar_wait(o_free, (n - 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
         const uint64_t pd = d_p + (uint64_t)(((tt & 1) * 2 * AT_TILE) >> 4);
         const uint64_t vd = d_v + (uint64_t)((st * AT_TILE) >> 4);
@@ -1205,7 +1210,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       t += nb;
     }
-  } else {
+  } else if (warp < 18) {
     const int quad = warp & 3, colq = (warp - 2) >> 2;
     const int col0 = colq * 32;
     const int row = quad * 32 + lane;
@@ -1217,7 +1222,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
       int bh, qb;
       decode(item, bh, qb);
-      const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
+      const int nb = qb + 1;
       uint64_t lsum = 0;  // two fp32 zeros
       for (int j = 0; j < nb; j++) {
         const int tt = t + j, buf = tt & 1;
@@ -1249,39 +1254,53 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       }
       if (!ok) break;
       t += nb;
-      // row sums of the four column quarters meet in shared memory
+      // the row sums of the four column quarters go to the epilogue warps
       float la, lb;
       f2_unpack(lsum, la, lb);
-      lsm[colq * 128 + row] = la + lb;
+      lsm[(n & 1) * 512 + colq * 128 + row] = la + lb;
       __syncwarp();
       if (lane == 0) mbar_arrive(l_ready);
-      if (!mbar_wait(l_ready, n & 1, abort_flag)) { ok = false; break; }
-      const float l = (lsm[row] + lsm[128 + row]) + (lsm[256 + row] + lsm[384 + row]);
-      if (!mbar_wait(o_done, n & 1, abort_flag)) { ok = false; break; }
+    }
+  } else {
+    // epilogue warps: quadrant q finishes rows 32q .. 32q+31 of every item
+    const int quad = warp & 3;
+    const int row = quad * 32 + lane;
+    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
+    const float c2 = a.cap * 1.4426950408889634f;
+    int n = 0;
+    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+      int bh, qb;
+      decode(item, bh, qb);
+      const int b = bh / a.H, h = bh - b * a.H;
+      if (!mbar_wait(l_ready, n & 1, abort_flag)) break;
+      const float *lp = lsm + (n & 1) * 512 + row;
+      const float l = (lp[0] + lp[128]) + (lp[256] + lp[384]);
+      if (!mbar_wait(o_done, n & 1, abort_flag)) break;
       tc_fence_after();
       const int qi = qb * 128 + row;
-      uint32_t r[16];
-      tmem_ld_32x16(tO + lane_off + colq * 16, r);
-      tmem_ld_wait();
-      tc_fence_before();
-      if (qi < a.T) {
-        const float inv = 1.f / l;
-        __nv_bfloat16 *orow = (__nv_bfloat16 *)a.o + (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + (int64_t)qi * a.o_st +
-                              colq * 16;
+      const float inv = 1.f / l;
+      __nv_bfloat16 *orow = (__nv_bfloat16 *)a.o + (int64_t)b * a.o_sb + (int64_t)h * a.o_sh + (int64_t)qi * a.o_st;
+#pragma unroll 1
+      for (int c = 0; c < 2; c++) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + lane_off + c * 32, r);
+        tmem_ld_wait();
+        if (qi < a.T) {
 #pragma unroll
-        for (int q = 0; q < 2; q++) {
-          float f[8];
+          for (int q = 0; q < 4; q++) {
+            float f[8];
 #pragma unroll
-          for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]) * inv;
-          Vec16<__nv_bfloat16> v;
-          v.set(f);
-          v.store(orow + q * 8);
+            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]) * inv;
+            Vec16<__nv_bfloat16> v;
+            v.set(f);
+            v.store(orow + c * 32 + q * 8);
+          }
         }
-        if (colq == 0) a.lse[(int64_t)bh * a.T + qi] = (c2 + log2f(l)) * 0.6931471805599453f;
       }
-      // No barrier is needed before the next item: its first tile's P is announced by all
-      // sixteen warps only after each has finished this read of the row sums and of O, and
-      // both are rewritten only after that announcement.
+      if (qi < a.T) a.lse[(int64_t)bh * a.T + qi] = (c2 + log2f(l)) * 0.6931471805599453f;
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(o_free);
     }
   }
 
