@@ -1000,9 +1000,11 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
 //   warp 0      TMA producer: Q (2 buffers), K tiles through a 3-stage ring (a K tile is free as
 //               soon as its score product is done) and V tiles through a 4-stage ring; it
 //               runs ahead into the next item while the current one is being computed
-//   warp 1      MMA issuer: S(j+2) is issued as soon as the math warps have consumed S(j)
-//               (two S buffers in TMEM), O += P(j) V(j) when P(j) is in shared memory (two P
-//               buffers), so the tensor core works while the math warps compute
+//   warp 1      MMA issuer: the score product of the tile two ahead in the CTA's tile stream
+//               (across item boundaries) is issued as soon as the math warps have consumed
+//               S of the current tile (two S buffers in TMEM), O += P(j) V(j) when P(j) is in
+//               shared memory (two P buffers), so the tensor core works while the math warps
+//               compute
 //   warps 2-17  math warps
 //   warps 18-21 epilogue warps (one per lane quadrant): combine the row sums, scale O, write
 //               O and LSE while the other warps are already on the next item
@@ -1157,34 +1159,52 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     constexpr uint32_t idesc_pv = make_idesc_bf16(128, 64, false, true);
     const uint64_t d_q = make_smem_desc(sb + AF2_Q, 16, 1024), d_k = make_smem_desc(sb + AF2_K, 16, 1024);
     const uint64_t d_p = make_smem_desc(sb + AF2_P, 16, 1024), d_v = make_smem_desc(sb + AF2_V, AT_TILE, 1024);
+    // The score products run two tiles ahead of the P V products over the CTA's whole tile
+    // stream, across item boundaries: `la_*` is the cursor of the next S to issue.
+    int la_item = blockIdx.x, la_j = 0, la_n = 0, la_t = 0, la_nb = 0;
+    if (la_item < n_items) {
+      int bh, qb;
+      decode(la_item, bh, qb);
+      la_nb = qb + 1;
+    }
+    auto issue_next_s = [&]() -> bool {   // S of the cursor's tile into buffer la_t & 1, then advance the cursor
+      if (la_item >= n_items) return true;
+      if (la_j == 0 && !mbar_wait(q_full0 + 8 * (la_n & 1), (la_n >> 1) & 1, abort_flag)) return false;
+      const int st = la_t % AF2_KST;
+      if (!mbar_wait(k_full0 + 8 * st, (la_t / AF2_KST) & 1, abort_flag)) return false;
+      tc_fence_after();
+      const uint64_t qd = d_q + (uint64_t)(((la_n & 1) * AT_TILE) >> 4), kd = d_k + (uint64_t)((st * AT_TILE) >> 4);
+      const uint32_t ts = tS0 + (la_t & 1) * 128, done = s_full0 + 8 * (la_t & 1), k_freed = k_empty0 + 8 * st,
+                     q_freed = q_empty0 + 8 * (la_n & 1);
+      const bool last = la_j == la_nb - 1;
+      if (elect_one()) {
+#pragma unroll
+        for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, qd + kk * 2, kd + kk * 2, idesc_qk, kk > 0 ? 1u : 0u);
+        mma_commit(k_freed);
+        mma_commit(done);
+        if (last) mma_commit(q_freed);  // Q is not needed after the item's last score product
+      }
+      __syncwarp();
+      la_t++;
+      if (++la_j == la_nb) {
+        la_item += gridDim.x;
+        la_n++;
+        la_j = 0;
+        if (la_item < n_items) {
+          int bh, qb;
+          decode(la_item, bh, qb);
+          la_nb = qb + 1;
+        }
+      }
+      return true;
+    };
+    bool ok = issue_next_s();
+    if (ok) ok = issue_next_s();
     int t = 0, n = 0;
-    bool ok = true;
     for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
       int bh, qb;
       decode(item, bh, qb);
       const int nb = qb + 1;
-      if (!mbar_wait(q_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag)) break;
-      const uint64_t qd = d_q + (uint64_t)(((n & 1) * AT_TILE) >> 4);
-      const uint32_t q_freed = q_empty0 + 8 * (n & 1);
-      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer (t + j) & 1
-        const int tt = t + j, st = tt % AF2_KST;
-        if (!mbar_wait(k_full0 + 8 * st, (tt / AF2_KST) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint64_t kd = d_k + (uint64_t)((st * AT_TILE) >> 4);
-        const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1), k_freed = k_empty0 + 8 * st;
-        const bool last = j == nb - 1;
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, qd + kk * 2, kd + kk * 2, idesc_qk, kk > 0 ? 1u : 0u);
-          mma_commit(k_freed);
-          mma_commit(done);
-          if (last) mma_commit(q_freed);  // Q is not needed after the item's last score product
-        }
-        __syncwarp();
-        return true;
-      };
-      ok = issue_s(0);
-      if (ok && nb > 1) ok = issue_s(1);
       for (int j = 0; j < nb && ok; j++) {
         const int tt = t + j, st = tt % AF2_VST;
         if (!mbar_wait(p_ready0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
@@ -1206,7 +1226,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
           if (last) mma_commit(o_done);
         }
         __syncwarp();
-        if (j + 2 < nb) ok = issue_s(j + 2);
+        ok = issue_next_s();   // the S buffer of this tile is free: the math warps have consumed it
       }
       t += nb;
     }
