@@ -343,6 +343,14 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
   }
 }
 
+// Work items of the persistent kernels are sorted longest first; round k hands item
+// k*G + c to CTA c in even rounds and item k*G + (G-1-c) in odd rounds, so every CTA gets
+// nearly the same number of tiles.
+__device__ __forceinline__ int snake_item(int k) {
+  const int G = (int)gridDim.x, c = (int)blockIdx.x;
+  return k * G + ((k & 1) ? G - 1 - c : c);
+}
+
 // ── backward math warps ─────────────────────────────────────────────────────────────────
 // Sixteen math warps work on one 128 x 128 (query x key) tile: warp w owns the TMEM lane
 // quadrant w % 4 (32 query rows, one per thread) and the key-column quarter (w - 2) / 4, so a
@@ -554,7 +562,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     // TMA producer: the warp runs the loops, one elected lane issues
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, kb;
       decode(item, bh, kb);
       const int b = bh / a.H, h = bh - b * a.H, n_it = n_qb - kb;
@@ -587,7 +595,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const uint64_t d_p = make_smem_desc(sb + AK_P, AT_TILE, 1024), d_ds = make_smem_desc(sb + AK_DS, AT_TILE, 1024);
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, kb;
       decode(item, bh, kb);
       const int n_it = n_qb - kb;
@@ -662,7 +670,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     uint8_t *ds_row = smem + AK_DS + (colq >> 1) * AT_TILE + row * 128;
     int t = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0, item = snake_item(0); item < n_items && ok; item = snake_item(++rnd)) {
       int bh, kb;
       decode(item, bh, kb);
       const int n_it = n_qb - kb;
@@ -694,7 +702,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     int n = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items; item = snake_item(++n)) {
       int bh, kb;
       decode(item, bh, kb);
       const int b = bh / a.H, h = bh - b * a.H;
@@ -807,7 +815,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   if (warp == 0) {
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
@@ -838,7 +846,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const uint64_t d_ds = make_smem_desc(sb + AQ_DS, 16, 1024);
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int nb = qb + 1;
@@ -910,7 +918,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     uint8_t *ds_row = smem + AQ_DS + (colq >> 1) * AT_TILE + row * 128;
     int t = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x) {
+    for (int rnd = 0, item = snake_item(0); item < n_items && ok; item = snake_item(++rnd)) {
       int bh, qb;
       decode(item, bh, qb);
       const int nb = qb + 1;
@@ -942,7 +950,7 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     int n = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int b = bh / a.H, h = bh - b * a.H;
@@ -1128,7 +1136,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     }
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
@@ -1161,7 +1169,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint64_t d_p = make_smem_desc(sb + AF2_P, 16, 1024), d_v = make_smem_desc(sb + AF2_V, AT_TILE, 1024);
     // The score products run two tiles ahead of the P V products over the CTA's whole tile
     // stream, across item boundaries: `la_*` is the cursor of the next S to issue.
-    int la_item = blockIdx.x, la_j = 0, la_n = 0, la_t = 0, la_nb = 0;
+    int la_item = snake_item(0), la_j = 0, la_n = 0, la_t = 0, la_nb = 0;
     if (la_item < n_items) {
       int bh, qb;
       decode(la_item, bh, qb);
@@ -1187,8 +1195,8 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       __syncwarp();
       la_t++;
       if (++la_j == la_nb) {
-        la_item += gridDim.x;
         la_n++;
+        la_item = snake_item(la_n);
         la_j = 0;
         if (la_item < n_items) {
           int bh, qb;
@@ -1201,7 +1209,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     bool ok = issue_next_s();
     if (ok) ok = issue_next_s();
     int t = 0, n = 0;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int nb = qb + 1;
@@ -1239,7 +1247,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const float c1 = a.scale / a.cap, c2 = a.cap * LOG2E;
     int t = 0, n = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < n_items && ok; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int nb = qb + 1;
@@ -1288,7 +1296,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
     const float c2 = a.cap * 1.4426950408889634f;
     int n = 0;
-    for (int item = blockIdx.x; item < n_items; item += gridDim.x, n++) {
+    for (int item = snake_item(0); item < n_items; item = snake_item(++n)) {
       int bh, qb;
       decode(item, bh, qb);
       const int b = bh / a.H, h = bh - b * a.H;
