@@ -53,27 +53,48 @@ struct GemmTcArgs {
 };
 
 // tanh-approximation GELU with the hardware tanh (MUFU): the epilogues run on bf16 data, whose
-// resolution (2^-8) is far coarser than tanh.approx's error.
-__device__ __forceinline__ float gelu_fast(float x) {
-  const float c = 0.7978845608028654f;
-  return 0.5f * x * (1.f + tc::tanh_approx(c * (x + 0.044715f * x * x * x)));
+// resolution (2^-8) is far coarser than tanh.approx's error.  Two elements at a time with
+// packed fp32 arithmetic: the epilogue warps are alone on their SM sub-partitions, so their
+// instruction count is what limits the GELU epilogues.
+__device__ __forceinline__ void gelu_fast2(float &a, float &b) {
+  const float c = 0.7978845608028654f, c3 = c * 0.044715f;
+  const uint64_t x = tc::f2_pack(a, b);
+  const uint64_t x2 = tc::f2_mul(x, x);
+  float i0, i1;
+  tc::f2_unpack(tc::f2_mul(x, tc::f2_fma(x2, tc::f2_pack(c3, c3), tc::f2_pack(c, c))), i0, i1);
+  const uint64_t t = tc::f2_pack(tc::tanh_approx(i0), tc::tanh_approx(i1));
+  const uint64_t h = tc::f2_mul(x, tc::f2_pack(0.5f, 0.5f));
+  tc::f2_unpack(tc::f2_fma(h, t, h), a, b);
 }
-__device__ __forceinline__ float gelu_grad_fast(float x) {
-  const float c = 0.7978845608028654f;
-  const float t = tc::tanh_approx(c * (x + 0.044715f * x * x * x));
-  return 0.5f * (1.f + t) + 0.5f * x * (1.f - t * t) * c * (1.f + 3.f * 0.044715f * x * x);
+// (ga, gb) *= gelu'(xa, xb)
+__device__ __forceinline__ void gelu_grad_mul2(float &ga, float &gb, float xa, float xb) {
+  const float c = 0.7978845608028654f, c3 = c * 0.044715f;
+  const uint64_t half = tc::f2_pack(0.5f, 0.5f), one = tc::f2_pack(1.f, 1.f);
+  const uint64_t x = tc::f2_pack(xa, xb);
+  const uint64_t x2 = tc::f2_mul(x, x);
+  float i0, i1;
+  tc::f2_unpack(tc::f2_mul(x, tc::f2_fma(x2, tc::f2_pack(c3, c3), tc::f2_pack(c, c))), i0, i1);
+  const uint64_t t = tc::f2_pack(tc::tanh_approx(i0), tc::tanh_approx(i1));
+  const uint64_t q = tc::f2_fma(x2, tc::f2_pack(3.f * c3, 3.f * c3), tc::f2_pack(c, c));   // c (1 + 3 * 0.044715 x^2)
+  const uint64_t sech2 = tc::f2_fma(tc::f2_mul(t, t), tc::f2_pack(-1.f, -1.f), one);      // 1 - t^2
+  const uint64_t w = tc::f2_mul(tc::f2_mul(tc::f2_mul(x, half), sech2), q);               // 0.5 x (1 - t^2) c (...)
+  const uint64_t d = tc::f2_add(tc::f2_fma(t, half, half), w);                            // 0.5 (1 + t) + w
+  tc::f2_unpack(tc::f2_mul(tc::f2_pack(ga, gb), d), ga, gb);
 }
 
 // Per-CTA shared memory.  PAIR: the CTA holds 128 rows of A and BN/2 rows of B per stage.
-template <int BN, bool PAIR>
+// WIDE (pair form with the GELU epilogue, which stores two tiles per chunk): four staging
+// buffers per epilogue warp instead of two, paid for with one pipeline stage.
+template <int BN, bool PAIR, bool WIDE = false>
 struct GemmSmemLayout {
-  static constexpr int STAGES = PAIR ? 6 : 4;
+  static constexpr int STAGES = PAIR ? (WIDE ? 5 : 6) : 4;
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   static constexpr int B_BYTES = B_ROWS * GBK * 2;
   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), 128B-swizzled TMA boxes
   static constexpr int STAGE_OFF = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int STAGE_BYTES = 4 * 2 * 4096;
+  static constexpr int EPI_BUFS = WIDE ? 4 : 2;            // 4 KB staging buffers per epilogue warp
+  static constexpr int STAGE_BYTES = 4 * EPI_BUFS * 4096;
   static constexpr int BAR_OFF = STAGE_OFF + STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256;  // barriers + tmem base + abort flag
   static constexpr int DYN = TOTAL + 1024;     // slack to align the base to 1024 B
@@ -183,7 +204,7 @@ __device__ __forceinline__ void epilogue_store_chunk(const GemmTcArgs &g, const 
 // the matrix edge.  Epilogue operands (residual, saved pre-activation) arrive the same way
 // by a TMA load into the buffer the result will leave from.  Two buffers per warp: they
 // alternate (plain / ADD / GELU') or hold the pre-activation and the activation (GELU).
-template <typename OutT, int BN>
+template <typename OutT, int BN, bool WIDE>
 __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUtensorMap *tmap_c,
                                                   const CUtensorMap *tmap_aux, uint32_t t_row, int row0, int n0,
                                                   int lane, uint8_t *stage, uint32_t stage_u32, uint32_t aux_bar,
@@ -199,10 +220,13 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   for (int c = 0; c < BN / CH; c++) {
     const int col0 = n0 + c * CH;
     if (col0 >= g.N) break;  // warp-uniform
-    const int buf = gelu ? 1 : (int)(chunk_count & 1);
+    // plain / ADD / GELU': buffers alternate.  GELU: buffer pair (pre-activation, activation);
+    // with four buffers the pairs alternate too, with two every chunk waits for its predecessor.
+    const int pre_buf = (gelu && WIDE) ? (int)(chunk_count & 1) * 2 : 0;
+    const int buf = gelu ? pre_buf + 1 : (int)(chunk_count & 1);
     chunk_count++;
     if (lane == 0) {  // the buffer(s) about to be written must have been read out by their last store
-      if (gelu) bulk_wait_read<0>(); else bulk_wait_read<1>();
+      if (gelu && !WIDE) bulk_wait_read<0>(); else bulk_wait_read<1>();
     }
     __syncwarp();
     uint8_t *bp = stage + buf * 4096 + lane * 128;
@@ -229,13 +253,17 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
         float x[V];
         t.load(reinterpret_cast<const OutT *>(bp + ((q ^ sw) << 4)));
         t.get(x);
+        if (g.epilogue == ALPHA_EPI_ADD) {
 #pragma unroll
-        for (int j = 0; j < V; j++)
-          v[q * V + j] = g.epilogue == ALPHA_EPI_ADD ? v[q * V + j] + x[j] : v[q * V + j] * gelu_grad_fast(x[j]);
+          for (int j = 0; j < V; j++) v[q * V + j] += x[j];
+        } else {
+#pragma unroll
+          for (int j = 0; j < V; j += 2) gelu_grad_mul2(v[q * V + j], v[q * V + j + 1], x[j], x[j + 1]);
+        }
       }
     }
     if (gelu) {  // buffer 0 takes the pre-activation, buffer 1 the activation
-      uint8_t *ap = stage + lane * 128;
+      uint8_t *ap = stage + pre_buf * 4096 + lane * 128;
 #pragma unroll
       for (int q = 0; q < 8; q++) {
         Vec16<OutT> t;
@@ -243,7 +271,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
         t.store(reinterpret_cast<OutT *>(ap + ((q ^ sw) << 4)));
       }
 #pragma unroll
-      for (int j = 0; j < CH; j++) v[j] = gelu_fast(v[j]);
+      for (int j = 0; j < CH; j += 2) gelu_fast2(v[j], v[j + 1]);
     }
 #pragma unroll
     for (int q = 0; q < 8; q++) {
@@ -254,7 +282,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
     fence_proxy_async();
     __syncwarp();
     if (lane == 0) {
-      if (gelu) tma_store_2d_hint(tmap_aux, stage_u32, col0, row0, policy);
+      if (gelu) tma_store_2d_hint(tmap_aux, stage_u32 + pre_buf * 4096, col0, row0, policy);
       tma_store_2d_hint(tmap_c, bu, col0, row0, policy);
       bulk_commit();
     }
@@ -262,11 +290,11 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool PAIR>
+template <int BN, bool A_MN, bool B_MN, bool PAIR, bool WIDE>
 __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b,
                                              const CUtensorMap &tmap_c, const CUtensorMap &tmap_aux,
                                              const GemmTcArgs &g) {
-  using L = GemmSmemLayout<BN, PAIR>;
+  using L = GemmSmemLayout<BN, PAIR, WIDE>;
   constexpr int STAGES = L::STAGES;
   constexpr int TILE_M = PAIR ? 2 * GBM : GBM;  // rows of C per tile walker (CTA or CTA pair)
   extern __shared__ uint8_t smem_raw[];
@@ -421,8 +449,8 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
     const int quad = warp & 3;  // the TMEM lane quadrant this warp may read
     int it = 0;
     bool ok = true;
-    uint8_t *stage = smem + L::STAGE_OFF + quad * 8192;
-    const uint32_t stage_u32 = smem_base + L::STAGE_OFF + quad * 8192;
+    uint8_t *stage = smem + L::STAGE_OFF + quad * (L::EPI_BUFS * 4096);
+    const uint32_t stage_u32 = smem_base + L::STAGE_OFF + quad * (L::EPI_BUFS * 4096);
     uint32_t aux_phase = 0, chunk_count = 0;
     if (g.tma_epi && lane == 0) {
       tma_prefetch_desc(&tmap_c);
@@ -451,11 +479,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       if (g.tma_epi) {
         const int row0 = m0 + quad * 32;
         if (row0 < g.M) {  // warp-uniform: a quadrant entirely below the matrix has nothing to store
-          ok = g.out_f32 ? epilogue_tile_tma<float, BN>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage, stage_u32,
-                                                        aux_bar(quad), aux_phase, chunk_count, abort_flag)
-                         : epilogue_tile_tma<__nv_bfloat16, BN>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
-                                                                stage_u32, aux_bar(quad), aux_phase, chunk_count,
-                                                                abort_flag);
+          ok = g.out_f32 ? epilogue_tile_tma<float, BN, WIDE>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
+                                                              stage_u32, aux_bar(quad), aux_phase, chunk_count,
+                                                              abort_flag)
+                         : epilogue_tile_tma<__nv_bfloat16, BN, WIDE>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
+                                                                      stage_u32, aux_bar(quad), aux_phase, chunk_count,
+                                                                      abort_flag);
         }
         release_acc(acc);
         continue;
@@ -503,16 +532,16 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, GemmTcArgs g) {
-  gemm_tc_body<BN, A_MN, B_MN, false>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
+  gemm_tc_body<BN, A_MN, B_MN, false, false>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
 }
 
 // Pair form: clusters of two CTAs, one 256 x 256 tile per pair and step.
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool WIDE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
                     GemmTcArgs g) {
-  gemm_tc_body<256, A_MN, B_MN, true>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
+  gemm_tc_body<256, A_MN, B_MN, true, WIDE>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
 }
 
 // C (+)= sum_s ws[s]  — split order is fixed, so the result is reproducible.  ws holds
@@ -613,13 +642,13 @@ static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CU
 
 // Pair form.  `pairs` = tile walkers wanted; the grid is capped at the number of two-CTA
 // clusters the device can hold at once (asked from the occupancy API on first use).
-template <bool A_MN, bool B_MN>
+template <bool A_MN, bool B_MN, bool WIDE = false>
 static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_,
                                const CUtensorMap &tx, const GemmTcArgs &g, int pairs) {
-  using L = GemmSmemLayout<256, true>;
+  using L = GemmSmemLayout<256, true, WIDE>;
   static int max_pairs = 0;
   if (!max_pairs) {
-    ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * (g_sm_count / 2));
@@ -631,14 +660,14 @@ static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, con
     cfg.attrs = &at;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<A_MN, B_MN>, &cfg) != cudaSuccess || n < 1) {
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel<A_MN, B_MN, WIDE>, &cfg) != cudaSuccess || n < 1) {
       cudaGetLastError();
       n = g_sm_count / 2;
     }
     max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
   }
   const int n = pairs < max_pairs ? pairs : max_pairs;
-  gemm_tc_pair_kernel<A_MN, B_MN><<<2 * n, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
+  gemm_tc_pair_kernel<A_MN, B_MN, WIDE><<<2 * n, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -725,7 +754,9 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   if (pair) {
     rc = a_mn ? launch_pair_variant<true, true>(ta, tb, tcm, txm, g, total)
               : (b_mn ? launch_pair_variant<false, true>(ta, tb, tcm, txm, g, total)
-                      : launch_pair_variant<false, false>(ta, tb, tcm, txm, g, total));
+                      : ((g.tma_epi && g.epilogue == ALPHA_EPI_GELU)
+                             ? launch_pair_variant<false, false, true>(ta, tb, tcm, txm, g, total)
+                             : launch_pair_variant<false, false>(ta, tb, tcm, txm, g, total)));
   } else {
 #define GEMM_VARIANT(BNV)                                                                               \
   (a_mn ? launch_variant<BNV, true, true>(ta, tb, tcm, txm, g, grid)                                    \
