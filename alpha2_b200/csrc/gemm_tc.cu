@@ -83,18 +83,21 @@ __device__ __forceinline__ void gelu_grad_mul2(float &ga, float &gb, float xa, f
 }
 
 // Per-CTA shared memory.  PAIR: the CTA holds 128 rows of A and BN/2 rows of B per stage.
-// WIDE (pair form with the GELU epilogue, which stores two tiles per chunk): four staging
-// buffers per epilogue warp instead of two, paid for with one pipeline stage.
+// WIDE (pair form with the GELU epilogue, whose per-element work is several times that of a
+// plain store): eight epilogue warps instead of four — two per TMEM lane quadrant, taking
+// alternate column chunks — paid for with one pipeline stage.
 template <int BN, bool PAIR, bool WIDE = false>
 struct GemmSmemLayout {
   static constexpr int STAGES = PAIR ? (WIDE ? 5 : 6) : 4;
+  static constexpr int EPI_WARPS = WIDE ? 8 : 4;
+  static constexpr int THREADS = 64 + 32 * EPI_WARPS;
   static constexpr int A_BYTES = GBM * GBK * 2;
   static constexpr int B_ROWS = PAIR ? BN / 2 : BN;
   static constexpr int B_BYTES = B_ROWS * GBK * 2;
   // epilogue staging: 4 warps x 2 buffers x (32 rows x 128 bytes), 128B-swizzled TMA boxes
   static constexpr int STAGE_OFF = STAGES * (A_BYTES + B_BYTES);
-  static constexpr int EPI_BUFS = WIDE ? 4 : 2;            // 4 KB staging buffers per epilogue warp
-  static constexpr int STAGE_BYTES = 4 * EPI_BUFS * 4096;
+  static constexpr int EPI_BUFS = 2;                       // 4 KB staging buffers per epilogue warp
+  static constexpr int STAGE_BYTES = EPI_WARPS * EPI_BUFS * 4096;
   static constexpr int BAR_OFF = STAGE_OFF + STAGE_BYTES;
   static constexpr int TOTAL = BAR_OFF + 256;  // barriers + tmem base + abort flag
   static constexpr int DYN = TOTAL + 1024;     // slack to align the base to 1024 B
@@ -209,7 +212,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
                                                   const CUtensorMap *tmap_aux, uint32_t t_row, int row0, int n0,
                                                   int lane, uint8_t *stage, uint32_t stage_u32, uint32_t aux_bar,
                                                   uint32_t &aux_phase, uint32_t &chunk_count,
-                                                  volatile uint32_t *abort_flag) {
+                                                  volatile uint32_t *abort_flag, int half) {
   constexpr int CH = 128 / (int)sizeof(OutT);  // columns per staged chunk (64 bf16 / 32 f32)
   constexpr int V = Vec16<OutT>::N;
   const bool gelu = g.epilogue == ALPHA_EPI_GELU;
@@ -220,13 +223,14 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   for (int c = 0; c < BN / CH; c++) {
     const int col0 = n0 + c * CH;
     if (col0 >= g.N) break;  // warp-uniform
-    // plain / ADD / GELU': buffers alternate.  GELU: buffer pair (pre-activation, activation);
-    // with four buffers the pairs alternate too, with two every chunk waits for its predecessor.
-    const int pre_buf = (gelu && WIDE) ? (int)(chunk_count & 1) * 2 : 0;
-    const int buf = gelu ? pre_buf + 1 : (int)(chunk_count & 1);
+    if (WIDE && (c & 1) != half) continue;  // the quadrant's other warp takes this chunk
+    // plain / ADD / GELU': the two buffers alternate.  GELU: buffer 0 takes the pre-activation,
+    // buffer 1 the activation, so every chunk waits for the stores of its predecessor.
+    const int pre_buf = 0;
+    const int buf = gelu ? 1 : (int)(chunk_count & 1);
     chunk_count++;
     if (lane == 0) {  // the buffer(s) about to be written must have been read out by their last store
-      if (gelu && !WIDE) bulk_wait_read<0>(); else bulk_wait_read<1>();
+      if (gelu) bulk_wait_read<0>(); else bulk_wait_read<1>();
     }
     __syncwarp();
     uint8_t *bp = stage + buf * 4096 + lane * 128;
@@ -312,7 +316,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
   auto tfull_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + s); };
   auto tempty_bar = [&](int s) { return bar_base + 8u * (2 * STAGES + 2 + s); };
   auto aux_bar = [&](int q) { return bar_base + 8u * (2 * STAGES + 4 + q); };  // one per epilogue warp
-  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * STAGES + 8));
+  uint32_t *tmem_slot = (uint32_t *)(smem + L::BAR_OFF + 8 * (2 * STAGES + 4 + L::EPI_WARPS));
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -326,10 +330,10 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    for (int q = 0; q < 4; q++) mbar_init(aux_bar(q), 1);
+    for (int q = 0; q < L::EPI_WARPS; q++) mbar_init(aux_bar(q), 1);
     for (int s = 0; s < 2; s++) {
       mbar_init(tfull_bar(s), 1);
-      mbar_init(tempty_bar(s), PAIR ? 8 : 4);  // the leader's collects both CTAs' epilogue warps
+      mbar_init(tempty_bar(s), (PAIR ? 2 : 1) * L::EPI_WARPS);  // the leader's collects both CTAs' epilogue warps
     }
     *abort_flag = 0;
     fence_barrier_init();
@@ -447,10 +451,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
   } else {
     // ── epilogue warps (2..5): TMEM -> registers -> global ─────────────────
     const int quad = warp & 3;  // the TMEM lane quadrant this warp may read
+    const int ew = warp - 2, half = ew >> 2;  // epilogue warp index; which of the quadrant's two warps (WIDE)
     int it = 0;
     bool ok = true;
-    uint8_t *stage = smem + L::STAGE_OFF + quad * (L::EPI_BUFS * 4096);
-    const uint32_t stage_u32 = smem_base + L::STAGE_OFF + quad * (L::EPI_BUFS * 4096);
+    uint8_t *stage = smem + L::STAGE_OFF + ew * (L::EPI_BUFS * 4096);
+    const uint32_t stage_u32 = smem_base + L::STAGE_OFF + ew * (L::EPI_BUFS * 4096);
     uint32_t aux_phase = 0, chunk_count = 0;
     if (g.tma_epi && lane == 0) {
       tma_prefetch_desc(&tmap_c);
@@ -480,11 +485,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
         const int row0 = m0 + quad * 32;
         if (row0 < g.M) {  // warp-uniform: a quadrant entirely below the matrix has nothing to store
           ok = g.out_f32 ? epilogue_tile_tma<float, BN, WIDE>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
-                                                              stage_u32, aux_bar(quad), aux_phase, chunk_count,
-                                                              abort_flag)
+                                                              stage_u32, aux_bar(ew), aux_phase, chunk_count,
+                                                              abort_flag, half)
                          : epilogue_tile_tma<__nv_bfloat16, BN, WIDE>(g, &tmap_c, &tmap_aux, t_row, row0, n0, lane, stage,
-                                                                      stage_u32, aux_bar(quad), aux_phase, chunk_count,
-                                                                      abort_flag);
+                                                                      stage_u32, aux_bar(ew), aux_phase, chunk_count,
+                                                                      abort_flag, half);
         }
         release_acc(acc);
         continue;
@@ -495,6 +500,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       for (int c = 0; c < BN / 32; c++) {
         const int col0 = n0 + c * 32;
         if (col0 >= g.N) break;  // warp-uniform
+        if (WIDE && (c & 1) != half) continue;
         uint32_t r[32];
         tmem_ld_32x32(t_row + c * 32, r);
         tmem_ld_wait();
@@ -537,7 +543,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant
 
 // Pair form: clusters of two CTAs, one 256 x 256 tile per pair and step.
 template <bool A_MN, bool B_MN, bool WIDE>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GEMM_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmSmemLayout<256, true, WIDE>::THREADS, 1)
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
                     GemmTcArgs g) {
@@ -652,7 +658,7 @@ static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, con
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
     cfg.gridDim = dim3(2 * (g_sm_count / 2));
-    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.blockDim = dim3(L::THREADS);
     cfg.dynamicSmemBytes = L::DYN;
     cudaLaunchAttribute at;
     at.id = cudaLaunchAttributeClusterDimension;
@@ -667,7 +673,7 @@ static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, con
     max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
   }
   const int n = pairs < max_pairs ? pairs : max_pairs;
-  gemm_tc_pair_kernel<A_MN, B_MN, WIDE><<<2 * n, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
+  gemm_tc_pair_kernel<A_MN, B_MN, WIDE><<<2 * n, L::THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
   ALPHA_LAUNCHED();
   return 0;
 }
