@@ -9,10 +9,13 @@
 // CPU loop.
 //
 // Backward plan (all on the device, no host round trip):
-//   1. rank[i]   = #{ j < i : idx[j] == idx[i] }            (tiled O(n^2) compare, n = B*T)
+//   1. rank[i]   = #{ j < i : idx[j] == idx[i] }            (tiled O(n^2) compare over a 2-D grid
+//                                                             of tile pairs, n = B*T)
 //   2. count[v]  = occurrences of v ; start[v] = exclusive prefix sum
 //   3. order[start[idx[i]] + rank[i]] = i
 //   4. row v: acc = (accumulate ? dW[v] : 0); for k in start[v]..start[v+1]: acc += g[order[k]]
+//      (bf16 gradients: rows named more than 64 times — frequent tokens — are summed by a whole
+//      block each, as a fixed tree over five segments of the occurrence list)
 // Scratch: (2 n + vocab + 1) int32.  Algorithmic bytes: n*dim*e read + vocab*dim*4 written.
 #include "common.cuh"
 
@@ -84,60 +87,60 @@ __global__ void __launch_bounds__(256) embedding_pos_fwd_kernel(const T *__restr
 
 constexpr int RANK_TILE = 256;
 
+// rank[i] += #{ j in tile tj, j < i : idx[j] == idx[i] } for i in tile ti (tj <= ti); rank must
+// be zero on entry.  Integer atomics: the result does not depend on the order of the blocks.
 __global__ void __launch_bounds__(RANK_TILE) emb_rank_kernel(const int32_t *__restrict__ idx, int32_t *__restrict__ rank,
                                                              int32_t *__restrict__ count, int64_t n, int64_t vocab) {
+  const int ti = blockIdx.y, tj = blockIdx.x;
+  if (tj > ti) return;
   __shared__ int32_t tile[RANK_TILE];
-  const int64_t i = (int64_t)blockIdx.x * RANK_TILE + threadIdx.x;
+  const int64_t i = (int64_t)ti * RANK_TILE + threadIdx.x, j = (int64_t)tj * RANK_TILE + threadIdx.x;
+  tile[threadIdx.x] = j < n ? idx[j] : -2;
   const int32_t mine = i < n ? idx[i] : -1;
+  __syncthreads();
+  const int lim = tj < ti ? RANK_TILE : (int)threadIdx.x;  // only j < i
   int32_t r = 0;
-  for (int64_t j0 = 0; j0 <= (int64_t)blockIdx.x * RANK_TILE; j0 += RANK_TILE) {
-    __syncthreads();
-    const int64_t j = j0 + threadIdx.x;
-    tile[threadIdx.x] = j < n ? idx[j] : -2;
-    __syncthreads();
-    const int lim = (int)((i - j0) < RANK_TILE ? (i - j0) : RANK_TILE);  // only j < i
 #pragma unroll 8
-    for (int k = 0; k < lim; k++) r += (tile[k] == mine);
-  }
+  for (int k = 0; k < lim; k++) r += (tile[k] == mine);
   if (i < n) {
-    rank[i] = r;
-    if (mine >= 0 && mine < vocab) atomicAdd(&count[mine], 1);
+    if (r) atomicAdd(&rank[i], r);
+    if (tj == ti && mine >= 0 && mine < vocab) atomicAdd(&count[mine], 1);
   }
 }
 
 // One block: exclusive prefix sum of count[0..vocab) into start[0..vocab]; in place allowed.
+// Every thread owns a run of consecutive entries: it sums its run, the 1024 run sums are
+// scanned with shuffles, then the thread writes its run.
 __global__ void __launch_bounds__(1024) emb_scan_kernel(const int32_t *count, int32_t *start, int64_t vocab) {
   __shared__ int32_t warp_tot[32];
-  __shared__ int32_t carry;
-  if (threadIdx.x == 0) carry = 0;
-  __syncthreads();
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  for (int64_t base = 0; base < vocab + 1; base += 1024) {
-    const int64_t i = base + threadIdx.x;
-    const int32_t v = i < vocab ? count[i] : 0;
-    int32_t incl = v;
+  const int64_t per = (vocab + 1 + 1023) / 1024;
+  const int64_t b = (int64_t)threadIdx.x * per, e = (b + per < vocab + 1) ? b + per : vocab + 1;
+  int32_t sum = 0;
+  for (int64_t i = b; i < e; i++) sum += i < vocab ? count[i] : 0;
+  int32_t incl = sum;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+    if (lane >= o) incl += t;
+  }
+  if (lane == 31) warp_tot[wid] = incl;
+  __syncthreads();
+  if (wid == 0) {
+    int32_t w = warp_tot[lane], wi = w;
 #pragma unroll
     for (int o = 1; o < 32; o <<= 1) {
-      const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-      if (lane >= o) incl += t;
+      const int32_t t = __shfl_up_sync(0xffffffffu, wi, o);
+      if (lane >= o) wi += t;
     }
-    if (lane == 31) warp_tot[wid] = incl;
-    __syncthreads();
-    if (wid == 0) {
-      int32_t w = warp_tot[lane], wi = w;
-#pragma unroll
-      for (int o = 1; o < 32; o <<= 1) {
-        const int32_t t = __shfl_up_sync(0xffffffffu, wi, o);
-        if (lane >= o) wi += t;
-      }
-      warp_tot[lane] = wi - w;  // exclusive offset of each warp
-    }
-    __syncthreads();
-    const int32_t excl = carry + warp_tot[wid] + incl - v;
-    if (i <= vocab) start[i] = excl;
-    __syncthreads();
-    if (threadIdx.x == 1023) carry = excl + v;
-    __syncthreads();
+    warp_tot[lane] = wi - w;  // exclusive offset of each warp
+  }
+  __syncthreads();
+  int32_t acc = warp_tot[wid] + incl - sum;
+  for (int64_t i = b; i < e; i++) {
+    const int32_t v = i < vocab ? count[i] : 0;
+    start[i] = acc;
+    acc += v;
   }
 }
 
@@ -151,21 +154,33 @@ __global__ void __launch_bounds__(256) emb_order_kernel(const int32_t *__restric
 }
 
 // One thread per (row, 4 output columns); consecutive threads cover consecutive columns.
+// Rows that no index names are left alone when accumulating.  With `hot_limit` > 0 a row named
+// more than hot_limit times is not summed here: it is appended to hot_rows (its order in that
+// list does not matter, each row is summed on its own) for emb_hot_rows_kernel.
 template <typename T>
 __global__ void __launch_bounds__(256) emb_rowsum_kernel(const T *__restrict__ g, const int32_t *__restrict__ start,
                                                          const int32_t *__restrict__ order, float *__restrict__ dw,
-                                                         int64_t vocab, int64_t dim, int accumulate) {
+                                                         int64_t vocab, int64_t dim, int accumulate, int hot_limit,
+                                                         int32_t *hot_rows, int32_t *hot_count, int hot_cap) {
   const int64_t per_row = (dim + 3) / 4;
   const int64_t total = vocab * per_row;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
   for (int64_t w = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; w < total; w += stride) {
     const int64_t v = w / per_row, c = (w - v * per_row) * 4;
     const int nc = (int)(dim - c < 4 ? dim - c : 4);
+    const int32_t s = start[v], e = start[v + 1];
+    if (accumulate && s == e) continue;
+    if (hot_limit > 0 && e - s > hot_limit) {
+      if (c == 0) {
+        const int slot = atomicAdd(hot_count, 1);
+        if (slot < hot_cap) hot_rows[slot] = (int32_t)v;
+      }
+      continue;
+    }
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
     float *dst = dw + v * dim + c;
     if (accumulate)
       for (int j = 0; j < nc; j++) acc[j] = dst[j];
-    const int32_t s = start[v], e = start[v + 1];
     int32_t k = s;
     // loads are independent of the running sums: batch 8 rows of loads, then add in order
     for (; k + 8 <= e; k += 8) {
@@ -186,6 +201,67 @@ __global__ void __launch_bounds__(256) emb_rowsum_kernel(const T *__restrict__ g
       for (int j = 0; j < nc; j++) acc[j] += to_f32(src[j]);
     }
     for (int j = 0; j < nc; j++) dst[j] = acc[j];
+  }
+}
+
+// Rows named many times (frequent tokens): a whole block per row.  The row's occurrence list is
+// cut into blockDim.y contiguous segments, segment s is summed in order by the threads
+// (threadIdx.x = 4-column group), and the segment sums are added in segment order — a fixed
+// summation tree, so the result is reproducible (it is not the strictly sequential order of
+// the reference loop, which is why fp32 parity runs do not use this kernel).
+constexpr int HOT_COLS = 192;   // column groups per pass (768 columns)
+constexpr int HOT_SEGS = 5;
+template <typename T>
+__global__ void __launch_bounds__(HOT_COLS * HOT_SEGS) emb_hot_rows_kernel(
+    const T *__restrict__ g, const int32_t *__restrict__ start, const int32_t *__restrict__ order,
+    float *__restrict__ dw, int64_t dim, int accumulate, const int32_t *__restrict__ hot_rows,
+    const int32_t *__restrict__ hot_count, int hot_cap) {
+  __shared__ float part[HOT_SEGS][HOT_COLS][4];
+  const int n_hot = *hot_count < hot_cap ? *hot_count : hot_cap;
+  const int cg = threadIdx.x, seg = threadIdx.y;
+  for (int hidx = blockIdx.x; hidx < n_hot; hidx += gridDim.x) {
+    const int64_t v = hot_rows[hidx];
+    const int32_t s = start[v], e = start[v + 1];
+    const int32_t len = (e - s + HOT_SEGS - 1) / HOT_SEGS;
+    const int32_t ks = s + seg * len, ke = ks + len < e ? ks + len : e;
+    for (int64_t c0 = 0; c0 < dim; c0 += HOT_COLS * 4) {
+      const int64_t c = c0 + cg * 4;
+      const int nc = c < dim ? (int)(dim - c < 4 ? dim - c : 4) : 0;
+      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+      if (nc > 0) {
+        int32_t k = ks;
+        for (; k + 8 <= ke; k += 8) {
+          float t[8][4];
+#pragma unroll
+          for (int u = 0; u < 8; u++) {
+            const T *src = g + (int64_t)order[k + u] * dim + c;
+#pragma unroll
+            for (int j = 0; j < 4; j++) t[u][j] = j < nc ? to_f32(src[j]) : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 8; u++)
+#pragma unroll
+            for (int j = 0; j < 4; j++) acc[j] += t[u][j];
+        }
+        for (; k < ke; k++) {
+          const T *src = g + (int64_t)order[k] * dim + c;
+          for (int j = 0; j < nc; j++) acc[j] += to_f32(src[j]);
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; j++) part[seg][cg][j] = acc[j];
+      __syncthreads();
+      if (seg == 0 && nc > 0) {
+        float *dst = dw + v * dim + c;
+        for (int j = 0; j < nc; j++) {
+          float t = accumulate ? dst[j] : 0.f;
+#pragma unroll
+          for (int q = 0; q < HOT_SEGS; q++) t += part[q][cg][j];
+          dst[j] = t;
+        }
+      }
+      __syncthreads();
+    }
   }
 }
 
@@ -248,25 +324,39 @@ int alpha_embedding_bwd(alpha_buf indices, alpha_buf grad, alpha_buf dw, int64_t
     return 0;
   }
   void *scratch = nullptr;
-  const size_t n_ints = (size_t)2 * n_idx + vocab + 1;
+  constexpr int HOT_CAP = 1024;
+  const size_t n_ints = (size_t)2 * n_idx + vocab + 1 + HOT_CAP + 1;
   if (pool_alloc(n_ints * sizeof(int32_t), &scratch)) return 1;
   int32_t *rank = (int32_t *)scratch, *order = rank + n_idx, *start = order + n_idx;
-  ALPHA_CUDA(cudaMemsetAsync(start, 0, (size_t)(vocab + 1) * sizeof(int32_t), g_stream));
+  int32_t *hot_rows = start + vocab + 1, *hot_count = hot_rows + HOT_CAP;
+  ALPHA_CUDA(cudaMemsetAsync(rank, 0, (size_t)n_idx * sizeof(int32_t), g_stream));
+  ALPHA_CUDA(cudaMemsetAsync(start, 0, (size_t)(vocab + 1 + HOT_CAP + 1) * sizeof(int32_t), g_stream));
   const int32_t *idx = ptr<int32_t>(indices);
-  emb_rank_kernel<<<(unsigned)((n_idx + RANK_TILE - 1) / RANK_TILE), RANK_TILE, 0, g_stream>>>(idx, rank, start, n_idx,
-                                                                                               vocab);
+  const unsigned nt = (unsigned)((n_idx + RANK_TILE - 1) / RANK_TILE);
+  emb_rank_kernel<<<dim3(nt, nt), RANK_TILE, 0, g_stream>>>(idx, rank, start, n_idx, vocab);
   g_launches++;
   emb_scan_kernel<<<1, 1024, 0, g_stream>>>(start, start, vocab);
   g_launches++;
   emb_order_kernel<<<(unsigned)((n_idx + 255) / 256), 256, 0, g_stream>>>(idx, rank, start, order, n_idx, vocab);
   g_launches++;
   const int grid = grid_for(vocab * ((dim + 3) / 4), 256, 8);
-  if (grad_dtype == ALPHA_F32)
+  if (grad_dtype == ALPHA_F32) {
+    // strictly sequential sums: bit-identical to the reference loop
     emb_rowsum_kernel<float><<<grid, 256, 0, g_stream>>>(ptr<float>(grad), start, order, ptr<float>(dw), vocab, dim,
-                                                         accumulate);
-  else
+                                                         accumulate, 0, nullptr, nullptr, 0);
+  } else {
+    // more than HOT_CAP frequent rows cannot occur: a row is hot above 64 occurrences and
+    // n_idx / 64 <= HOT_CAP is checked here
+    const int hot_limit = n_idx / 64 <= HOT_CAP ? 64 : 0;
     emb_rowsum_kernel<__nv_bfloat16><<<grid, 256, 0, g_stream>>>(ptr<__nv_bfloat16>(grad), start, order,
-                                                                 ptr<float>(dw), vocab, dim, accumulate);
+                                                                 ptr<float>(dw), vocab, dim, accumulate, hot_limit,
+                                                                 hot_rows, hot_count, HOT_CAP);
+    if (hot_limit > 0) {
+      g_launches++;
+      emb_hot_rows_kernel<__nv_bfloat16><<<g_sm_count, dim3(HOT_COLS, HOT_SEGS), 0, g_stream>>>(
+          ptr<__nv_bfloat16>(grad), start, order, ptr<float>(dw), dim, accumulate, hot_rows, hot_count, HOT_CAP);
+    }
+  }
   pool_free(scratch);
   ALPHA_LAUNCHED();
   return 0;

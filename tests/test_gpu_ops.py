@@ -184,8 +184,24 @@ def test_embedding_gather_is_bit_exact_and_scatter_is_ordered(B, dtype):
     dw = B.embeddingBackward(I, B.upload(g, dtype), V).data
     # the oracle's sequential f32 scatter-add (packages/autograd/src/ops.ts:495-505)
     ref = np.zeros((V, E), f32)
-    for i, v in enumerate(idx.reshape(-1)):
-        ref[v] = ref[v] + g.reshape(-1, E)[i]
+    flat_idx, flat_g = idx.reshape(-1), g.reshape(-1, E)
+    for i, v in enumerate(flat_idx):
+        ref[v] = ref[v] + flat_g[i]
+    if dtype == "bf16":
+        # bf16 gradients: a row named more than 64 times is summed as a fixed tree — five
+        # contiguous segments of its occurrence list, each summed in order, added in order
+        counts = np.bincount(flat_idx, minlength=V)
+        assert counts.max() > 64                                                     # the case is exercised
+        for v in np.nonzero(counts > 64)[0]:
+            occ = np.nonzero(flat_idx == v)[0]
+            seg = -(-len(occ) // 5)
+            tot = np.zeros(E, f32)
+            for q in range(5):
+                part = np.zeros(E, f32)
+                for i in occ[q * seg:(q + 1) * seg]:
+                    part = part + flat_g[i]
+                tot = tot + part
+            ref[v] = tot
     assert np.array_equal(dw, ref)                                                   # same order => same bits
     # tok + pos in one kernel
     wpe = r.standard_normal((N // 4, E)).astype(f32)
