@@ -11,7 +11,7 @@
 // bytes: 100 KB for V=50257 in bf16), so the fused kernel reads each logit from HBM once
 // and writes each gradient once: algorithmic bytes per row = V*e read + V*e written.
 // Row losses go to a scratch vector and are averaged by one block in index order.
-#include "common.cuh"
+#include "tc_common.cuh"
 
 namespace alpha {
 
@@ -107,6 +107,110 @@ __global__ void __launch_bounds__(CE_THREADS) ce_rows_kernel(const T *__restrict
   }
 }
 
+// bf16 rows staged in shared memory, lean arithmetic (the generic staged kernel above spends
+// ~28 thread instructions per logit and is bound by instruction issue, not by HBM):
+//   pass 1  global -> shared with 16-byte copies, row maximum (3-input max on unpacked pairs)
+//   pass 2  sum of exp2(x*log2e - max*log2e): one packed FMA per pair + one exp2 per element
+//   pass 3  the same exponentials times (grad scale / sum), packed, rounded to bf16, stored;
+//           the thread that owns the target's 16-byte vector subtracts the one-hot term
+// exp2 is evaluated twice per logit (passes 2 and 3) rather than kept, so the shared copy
+// stays read-only and the probabilities are rounded once.
+__device__ __forceinline__ void bf16x8_to_pairs(const uint4 &v, uint64_t (&p)[4]) {
+  const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int q = 0; q < 4; q++) p[q] = tc::bf16x2_to_f2(w[q]);
+}
+
+__global__ void __launch_bounds__(CE_THREADS, 2)
+ce_rows_bf16_kernel(const __nv_bfloat16 *__restrict__ logits, const int32_t *__restrict__ targets,
+                    __nv_bfloat16 *dlogits, float *__restrict__ row_loss, const float *__restrict__ grad_out_dev,
+                    float grad_scale, int64_t N, int V, int64_t ld, int mode) {
+  extern __shared__ __align__(16) unsigned char smem_raw[];
+  __shared__ float red[32];
+  uint4 *row_s = reinterpret_cast<uint4 *>(smem_raw);
+  const __nv_bfloat16 *row_e = reinterpret_cast<const __nv_bfloat16 *>(smem_raw);
+  const float LOG2E = 1.4426950408889634f;
+  const float gs = (grad_out_dev ? grad_out_dev[0] : 1.f) * grad_scale / (float)N;
+  const int nvec = V / 8;
+  for (int64_t r = blockIdx.x; r < N; r += gridDim.x) {
+    const __nv_bfloat16 *row = logits + r * ld;
+    const uint4 *row_v = reinterpret_cast<const uint4 *>(row);
+    const int tgt = targets[r];
+    // the target's logit is read before dlogits (which may alias logits) is written
+    float lt = 0.f;
+    if (threadIdx.x == 0 && tgt >= 0 && tgt < V) lt = __bfloat162float(row[tgt]);
+    float mx = -INFINITY;
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      const uint4 v = row_v[i];
+      row_s[i] = v;
+      uint64_t p[4];
+      bf16x8_to_pairs(v, p);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        float a, b;
+        tc::f2_unpack(p[q], a, b);
+        mx = tc::fmax3(mx, a, b);
+      }
+    }
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+      const __nv_bfloat16 t = row[c];
+      reinterpret_cast<__nv_bfloat16 *>(smem_raw)[c] = t;
+      mx = fmaxf(mx, __bfloat162float(t));
+    }
+    mx = block_max(mx, red);  // also orders the shared-memory row before it is re-read
+    const float nmx2 = -mx * LOG2E;
+    const uint64_t l2 = tc::f2_pack(LOG2E, LOG2E), nm = tc::f2_pack(nmx2, nmx2);
+    uint64_t s2 = tc::f2_pack(0.f, 0.f);
+    for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+      uint64_t p[4];
+      bf16x8_to_pairs(row_s[i], p);
+#pragma unroll
+      for (int q = 0; q < 4; q++) {
+        float a, b;
+        tc::f2_unpack(tc::f2_fma(p[q], l2, nm), a, b);
+        s2 = tc::f2_add(s2, tc::f2_pack(tc::ex2_approx(a), tc::ex2_approx(b)));
+      }
+    }
+    float sa, sb;
+    tc::f2_unpack(s2, sa, sb);
+    float s = sa + sb;
+    for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS)
+      s += tc::ex2_approx(fmaf(__bfloat162float(row_e[c]), LOG2E, nmx2));
+    s = block_sum(s, red);
+    if ((mode & 1) && threadIdx.x == 0) row_loss[r] = (mx + logf(s)) - lt;
+    if (mode & 2) {
+      const float k = gs / s;
+      const uint64_t k2 = tc::f2_pack(k, k);
+      uint4 *drow = reinterpret_cast<uint4 *>(dlogits + r * ld);
+      const int tvec = (tgt >= 0 && tgt < V) ? tgt >> 3 : -1;
+      for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
+        uint64_t p[4];
+        bf16x8_to_pairs(row_s[i], p);
+        float o[8];
+#pragma unroll
+        for (int q = 0; q < 4; q++) {
+          float a, b;
+          tc::f2_unpack(tc::f2_fma(p[q], l2, nm), a, b);
+          tc::f2_unpack(tc::f2_mul(tc::f2_pack(tc::ex2_approx(a), tc::ex2_approx(b)), k2), o[2 * q], o[2 * q + 1]);
+        }
+        if (i == tvec) o[tgt & 7] -= gs;
+        uint4 w;
+        w.x = tc::bf16x2_pack(o[0], o[1]);
+        w.y = tc::bf16x2_pack(o[2], o[3]);
+        w.z = tc::bf16x2_pack(o[4], o[5]);
+        w.w = tc::bf16x2_pack(o[6], o[7]);
+        drow[i] = w;
+      }
+      __nv_bfloat16 *dtail = dlogits + r * ld;
+      for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
+        const float pr = tc::ex2_approx(fmaf(__bfloat162float(row_e[c]), LOG2E, nmx2)) * k;
+        dtail[c] = __float2bfloat16(pr - (c == tgt ? gs : 0.f));
+      }
+    }
+    __syncthreads();  // the staged row is overwritten by the next iteration
+  }
+}
+
 __global__ void __launch_bounds__(1024) ce_mean_kernel(const float *__restrict__ row_loss, int64_t N,
                                                        float *__restrict__ out) {
   __shared__ float red[32];
@@ -141,9 +245,20 @@ static int ce_launch(alpha_buf logits, alpha_buf targets, alpha_buf dlogits, alp
       ALPHA_CUDA(cudaFuncSetAttribute(ce_rows_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
       attr_set = true;
     }
-    ce_rows_kernel<T, true><<<grid, CE_THREADS, row_bytes, g_stream>>>(
-        ptr<T>(logits), ptr<int32_t>(targets), ptr<T>(dlogits), (float *)row_loss,
-        grad_out ? ptr<float>(grad_out) : nullptr, grad_scale, N, (int)V, ld, mode);
+    if constexpr (sizeof(T) == 2) {
+      static bool attr2_set = false;
+      if (!attr2_set) {
+        ALPHA_CUDA(cudaFuncSetAttribute(ce_rows_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+        attr2_set = true;
+      }
+      ce_rows_bf16_kernel<<<grid, CE_THREADS, row_bytes, g_stream>>>(
+          ptr<__nv_bfloat16>(logits), ptr<int32_t>(targets), ptr<__nv_bfloat16>(dlogits), (float *)row_loss,
+          grad_out ? ptr<float>(grad_out) : nullptr, grad_scale, N, (int)V, ld, mode);
+    } else {
+      ce_rows_kernel<T, true><<<grid, CE_THREADS, row_bytes, g_stream>>>(
+          ptr<T>(logits), ptr<int32_t>(targets), ptr<T>(dlogits), (float *)row_loss,
+          grad_out ? ptr<float>(grad_out) : nullptr, grad_scale, N, (int)V, ld, mode);
+    }
   } else {
     ce_rows_kernel<T, false><<<grid, CE_THREADS, 0, g_stream>>>(
         ptr<T>(logits), ptr<int32_t>(targets), ptr<T>(dlogits), (float *)row_loss,
