@@ -709,6 +709,144 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
   }
 }
 
+// Forward with the same structure: four worker warps, one row each per group, x streamed
+// through a 4-stage bulk-copy ring; weight and bias rows sit in shared memory.
+constexpr int LRF_STAGES = 4;
+
+template <typename T, int NV, bool RMS>
+__global__ void __launch_bounds__(LR_THREADS, 4)
+ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b, T *__restrict__ y,
+            int64_t rows, int dim, float eps, uint32_t *err) {
+  using namespace tc;
+  constexpr int V = Vec16<T>::N;
+  constexpr int NE = NV * V;
+  extern __shared__ __align__(128) uint8_t lr_smem[];
+  const uint32_t row_bytes = (uint32_t)dim * sizeof(T);
+  const uint32_t stage_bytes = LR_WARPS * row_bytes;
+  const uint32_t ring = smem_u32(lr_smem);
+  const uint32_t bar = ring + LRF_STAGES * stage_bytes;
+  auto full_bar = [&](int s) { return bar + 8u * s; };
+  auto empty_bar = [&](int s) { return bar + 8u * (LRF_STAGES + s); };
+  volatile uint32_t *abort_flag = (volatile uint32_t *)(lr_smem + LRF_STAGES * stage_bytes + 16 * LRF_STAGES);
+  float *w_sm = reinterpret_cast<float *>(lr_smem + LRF_STAGES * stage_bytes + 128);
+  float *b_sm = w_sm + dim;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  for (int c = threadIdx.x; c < dim; c += LR_THREADS) {
+    w_sm[c] = w[c];
+    b_sm[c] = RMS ? 0.f : b[c];
+  }
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < LRF_STAGES; s++) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), LR_WARPS);
+    }
+    *abort_flag = 0;
+    fence_barrier_init();
+    fence_proxy_async();
+  }
+  __syncthreads();
+  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
+  if (warp == LR_WARPS) {
+    int i = 0;
+    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
+      const int s = i % LRF_STAGES;
+      if (!mbar_wait(empty_bar(s), ((i / LRF_STAGES) & 1) ^ 1, abort_flag)) break;
+      const int64_t r0 = grp * LR_WARPS;
+      const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
+      if (elect_one()) {
+        mbar_expect_tx(full_bar(s), bytes);
+        bulk_load_1d(ring + s * stage_bytes, x + r0 * dim, bytes, full_bar(s));
+      }
+      __syncwarp();
+    }
+  } else {
+    const float inv_dim = 1.f / (float)dim;
+    int i = 0;
+    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
+      const int s = i % LRF_STAGES;
+      if (!mbar_wait(full_bar(s), (i / LRF_STAGES) & 1, abort_flag)) break;
+      const int64_t r = grp * LR_WARPS + warp;
+      const uint8_t *src = lr_smem + s * stage_bytes + warp * row_bytes;
+      float xv[NE];
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        Vec16<T> t;
+        t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
+        t.get(&xv[v * V]);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(empty_bar(s));
+      if (r >= rows) continue;
+      float sum = 0.f;
+#pragma unroll
+      for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
+      sum = warp_sum(sum);
+      float mean = 0.f, rstd;
+      if (RMS) {
+        rstd = rsqrtf(sum * inv_dim + eps);
+      } else {
+        mean = sum * inv_dim;
+        float q = 0.f;
+#pragma unroll
+        for (int j = 0; j < NE; j++) {
+          const float d = xv[j] - mean;
+          q += d * d;
+        }
+        q = warp_sum(q);
+        rstd = 1.f / sqrtf(q * inv_dim + eps);
+      }
+      T *yr = y + r * dim;
+#pragma unroll
+      for (int v = 0; v < NV; v++) {
+        float o[V];
+#pragma unroll
+        for (int j4 = 0; j4 < V; j4 += 4) {
+          const int c = (v * 32 + lane) * V + j4;
+          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + c);
+          const float4 b4 = *reinterpret_cast<const float4 *>(b_sm + c);
+          o[j4] = (xv[v * V + j4] - mean) * rstd * w4.x + b4.x;
+          o[j4 + 1] = (xv[v * V + j4 + 1] - mean) * rstd * w4.y + b4.y;
+          o[j4 + 2] = (xv[v * V + j4 + 2] - mean) * rstd * w4.z + b4.z;
+          o[j4 + 3] = (xv[v * V + j4 + 3] - mean) * rstd * w4.w + b4.w;
+        }
+        Vec16<T> t;
+        t.set(o);
+        t.store(yr + (v * 32 + lane) * V);
+      }
+    }
+  }
+  if (*abort_flag) {  // a bounded wait ran out: let copies in flight land before the block's memory goes away
+    const long long t0 = clock64();
+    while (clock64() - t0 < 2000000ll) {
+    }
+    if (threadIdx.x == 0 && err) atomicExch(err, 0xB2000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  }
+}
+
+template <typename T, int NV, bool RMS>
+static int launch_fwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows, int64_t dim, float eps) {
+  const size_t smem = (size_t)LRF_STAGES * LR_WARPS * dim * sizeof(T) + 128 + 2 * dim * sizeof(float);
+  static bool attr = false;
+  if (!attr) {
+    ALPHA_CUDA(cudaFuncSetAttribute(ln_fwd_ring<T, NV, RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+    attr = true;
+  }
+  ln_fwd_ring<T, NV, RMS><<<grid_for(rows, LR_WARPS, 4), LR_THREADS, smem, g_stream>>>(
+      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word());
+  return 0;
+}
+template <typename T, bool RMS>
+static int launch_fwd_ring(int nv, alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows, int64_t dim,
+                           float eps) {
+  constexpr int K = sizeof(T) == 2 ? 1 : 2;
+  switch (nv) {
+    case 1 * K: return launch_fwd_ring_nv<T, 1 * K, RMS>(x, w, b, y, rows, dim, eps);
+    case 2 * K: return launch_fwd_ring_nv<T, 2 * K, RMS>(x, w, b, y, rows, dim, eps);
+    case 3 * K: return launch_fwd_ring_nv<T, 3 * K, RMS>(x, w, b, y, rows, dim, eps);
+  }
+  return set_error("layernorm forward: unsupported vector count %d", nv);
+}
+
 // ── generic fallback (any dim / alignment): one block per row, scalar accesses ──────────
 template <typename T, bool RMS>
 __global__ void __launch_bounds__(256) ln_fwd_block(const T *x, const float *w, const float *b, T *y, int64_t rows,
@@ -809,7 +947,10 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   ProfScope prof(PROF_NORM, 2.0 * rows * dim * sizeof(T));
   constexpr int V = Vec16<T>::N;
   const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
-  if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
+  constexpr int RK = sizeof(T) == 2 ? 1 : 2;
+  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
+    if (launch_fwd_ring<T, RMS>((int)(dim / (32 * V)), x, w, b, y, rows, dim, eps)) return 1;
+  } else if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
     const int nvec = (int)(dim / V);
     if (nvec <= LN_CTA) {
       const int nt = (nvec + 31) / 32 * 32;
