@@ -75,6 +75,7 @@ SIGNATURES = {
     "alpha_alloc": [C.c_size_t, C.POINTER(C.c_uint64)], "alpha_free": [_B],
     "alpha_mem_stats": [C.POINTER(MemStats)], "alpha_purge_pools": [],
     "alpha_memset": [_B, _I, C.c_size_t], "alpha_h2d": [_B, _P, C.c_size_t], "alpha_d2h": [_P, _B, C.c_size_t],
+    "alpha_d2h_async": [_P, _B, C.c_size_t],
     "alpha_d2d": [_B, _B, C.c_size_t], "alpha_host_alloc": [C.c_size_t, C.POINTER(C.c_void_p)],
     "alpha_host_free": [_P],
     "alpha_fill": [_B, _L, _F, _I], "alpha_binary": [_I, _B, _B, _B, _L, _I],

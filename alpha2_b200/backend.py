@@ -138,6 +138,31 @@ class TensorData:
         return float(self.data.reshape(-1)[0])
 
 
+class AsyncScalar:
+    """A pending device-to-host read of one f32 / i32 element (see CudaBackend.readScalarAsync).
+    Pinned slots and events are recycled through the backend: no allocation per read."""
+
+    def __init__(self, backend: "CudaBackend", t: TensorData):
+        if t.dtype == "bf16":
+            raise AlphaCudaError("readScalarAsync: f32 or i32 tensors only")
+        self._b = backend
+        self._int = t.dtype == "i32"
+        self._slot = backend._scalar_slot()
+        arr, pin, ev = self._slot
+        check(backend.lib.alpha_d2h_async(pin, t.ptr, 4))
+        check(backend.lib.alpha_event_record(ev.value))
+        self._val = None
+
+    def get(self) -> float:
+        if self._val is None:
+            arr, pin, ev = self._slot
+            check(self._b.lib.alpha_event_sync(ev.value))
+            self._val = float(arr.view(np.int32)[0]) if self._int else float(arr[0])
+            self._b._scalar_free.append(self._slot)
+            self._slot = None
+        return self._val
+
+
 class CudaBackend:
     """interfaces.ts:38-151 on a B200.  ``dtype`` strings: "f32", "bf16", "i32"."""
 
@@ -260,6 +285,21 @@ class CudaBackend:
 
     def free_pinned(self, handle) -> None:
         check(self.lib.alpha_host_free(handle))
+
+    def _scalar_slot(self):
+        free = self.__dict__.setdefault("_scalar_free", [])
+        if free:
+            return free.pop()
+        arr, pin = self.pinned_array((1,), np.float32)
+        ev = C.c_uint64()
+        check(self.lib.alpha_event_create(C.byref(ev)))
+        return (arr, pin, ev)
+
+    def readScalarAsync(self, t: TensorData) -> "AsyncScalar":
+        """Start copying a one-element tensor to pinned host memory; ``.get()`` on the returned
+        handle waits only for that copy, not for work enqueued after this call — so the loss of
+        step i can be read while step i+1 is already running."""
+        return AsyncScalar(self, t)
 
     # ── elementwise (interfaces.ts:49-71) ────────────────────────────────────
     def _binary(self, op: int, a: TensorData, b: TensorData) -> TensorData:

@@ -339,6 +339,16 @@ int alpha_d2h(void *host_dst, alpha_buf src, size_t bytes) {
   return 0;
 }
 
+// Enqueues the copy and returns; host_dst must be pinned (alpha_host_alloc) and may be read
+// once an event recorded after this call has completed (alpha_event_record / alpha_event_sync).
+int alpha_d2h_async(void *host_dst, alpha_buf src, size_t bytes) {
+  ALPHA_REQUIRE_INIT();
+  if (bytes == 0) return 0;
+  ALPHA_CHECK(host_dst != nullptr && src != 0, "alpha_d2h_async: null pointer");
+  ALPHA_CUDA(cudaMemcpyAsync(host_dst, ptr<void>(src), bytes, cudaMemcpyDeviceToHost, g_stream));
+  return 0;
+}
+
 int alpha_d2d(alpha_buf dst, alpha_buf src, size_t bytes) {
   ALPHA_REQUIRE_INIT();
   if (bytes == 0) return 0;

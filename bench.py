@@ -299,9 +299,17 @@ def main() -> None:
     losses = []
 
     def region_b():
+        # every step: tokens from pinned host memory, loss copied back to the host.  The copy
+        # of step i is enqueued behind step i and collected after step i+1 has been enqueued,
+        # so the host never stalls the device (the last one is collected inside the region).
+        pending = None
         for i in range(args.steps):
             out = tr.train_step([device_tokens(args.warmup + i)], read_back=False)
-            losses.append(out["lossTensor"].item())          # device -> host read every step
+            nxt = B.readScalarAsync(out["lossTensor"])
+            if pending is not None:
+                losses.append(pending.get())
+            pending = nxt
+        losses.append(pending.get())
     ms_b = timed(region_b)
     clocks = sampler.stop() if rank == 0 else {}
     B.checkAsyncError()

@@ -104,6 +104,10 @@ int alpha_purge_pools(void);
 int alpha_memset(alpha_buf dst, int byte_value, size_t bytes);
 int alpha_h2d(alpha_buf dst, const void *host_src, size_t bytes);   /* async if host_src is pinned */
 int alpha_d2h(void *host_dst, alpha_buf src, size_t bytes);         /* waits for the copy */
+/* Enqueue only: host_dst is pinned memory, valid after an event recorded behind the call
+ * has completed.  Lets a host read the result of step i while step i+1 is already queued
+ * (the reference's trainer reads its loss synchronously, trainer.ts:1247). */
+int alpha_d2h_async(void *host_dst, alpha_buf src, size_t bytes);
 int alpha_d2d(alpha_buf dst, alpha_buf src, size_t bytes);
 int alpha_host_alloc(size_t bytes, void **out);                     /* pinned host memory */
 int alpha_host_free(void *p);

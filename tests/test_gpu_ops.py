@@ -530,3 +530,12 @@ def test_allocator_reuses_blocks(B):
     s1 = B.gpuMemStats()
     assert s1["deviceMallocs"] == s0["deviceMallocs"] and s1["allocs"] >= s0["allocs"] + 50
     assert s1["bytesInUse"] == s0["bytesInUse"]
+
+
+def test_async_scalar_read(B):
+    """alpha_d2h_async + event: the value is that of the tensor when the read was enqueued."""
+    t = B.full((), 3.5)
+    h = B.readScalarAsync(t)
+    B.scaleInplace(t, 2.0)                  # enqueued after the read
+    assert h.get() == 3.5 and h.get() == 3.5
+    assert t.item() == 7.0
