@@ -1024,8 +1024,8 @@ constexpr int AF2_K = 2 * AT_TILE;
 constexpr int AF2_V = AF2_K + AF2_KST * AT_TILE;
 constexpr int AF2_P = AF2_V + AF2_VST * AT_TILE;           // 2 buffers x 2 tiles (key halves)
 constexpr int AF2_BAR = AF2_P + 4 * AT_TILE;
-constexpr int AF2_LSUM = AF2_BAR + 256;                    // [2 items][4 column quarters][128 rows] floats
-constexpr int AF2_DYN = AF2_LSUM + 4096 + 1024;
+constexpr int AF2_LSUM = AF2_BAR + 256;                    // [4 items][4 column quarters][128 rows] floats
+constexpr int AF2_DYN = AF2_LSUM + 8192 + 1024;
 constexpr float AF2_MAX_C2 = 50.f;                         // largest cap*log2(e) this kernel accepts
 
 // P for 32 scores of one row (bounded-score softmax).  Returns the largest squared tanh
@@ -1082,9 +1082,9 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AF2_BAR;
   const uint32_t q_full0 = bar, q_empty0 = bar + 16, s_full0 = bar + 32, p_ready0 = bar + 48, p_free0 = bar + 64,
-                 o_done = bar + 80, l_ready = bar + 88, o_free = bar + 96, k_full0 = bar + 104,
+                 o_done = bar + 80, o_free = bar + 88, l_ready0 = bar + 96, k_full0 = bar + 128,
                  k_empty0 = k_full0 + 8 * AF2_KST, v_full0 = k_empty0 + 8 * AF2_KST, v_empty0 = v_full0 + 8 * AF2_VST;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AF2_BAR + 104 + 16 * (AF2_KST + AF2_VST));
+  uint32_t *tmem_slot = (uint32_t *)(smem + AF2_BAR + 128 + 16 * (AF2_KST + AF2_VST));
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   float *lsm = reinterpret_cast<float *>(smem + AF2_LSUM);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -1100,7 +1100,10 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       mbar_init(p_free0 + 8 * i, 1);
     }
     mbar_init(o_done, 1);
-    mbar_init(l_ready, 16);
+    // The math warps can finish two more items while the epilogue warps are still on item n
+    // (two S and two P buffers let them run two tiles past the tensor core, and a short item is
+    // one tile), so the row sums and their barrier are kept per item in a ring of four.
+    for (int i = 0; i < 4; i++) mbar_init(l_ready0 + 8 * i, 16);
     mbar_init(o_free, 4);
     for (int s = 0; s < AF2_KST; s++) {
       mbar_init(k_full0 + 8 * s, 1);
@@ -1285,9 +1288,9 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       // the row sums of the four column quarters go to the epilogue warps
       float la, lb;
       f2_unpack(lsum, la, lb);
-      lsm[(n & 1) * 512 + colq * 128 + row] = la + lb;
+      lsm[(n & 3) * 512 + colq * 128 + row] = la + lb;
       __syncwarp();
-      if (lane == 0) mbar_arrive(l_ready);
+      if (lane == 0) mbar_arrive(l_ready0 + 8 * (n & 3));
     }
   } else {
     // epilogue warps: quadrant q finishes rows 32q .. 32q+31 of every item
@@ -1300,8 +1303,8 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
       int bh, qb;
       decode(item, bh, qb);
       const int b = bh / a.H, h = bh - b * a.H;
-      if (!mbar_wait(l_ready, n & 1, abort_flag)) break;
-      const float *lp = lsm + (n & 1) * 512 + row;
+      if (!mbar_wait(l_ready0 + 8 * (n & 3), (n >> 2) & 1, abort_flag)) break;
+      const float *lp = lsm + (n & 3) * 512 + row;
       const float l = (lp[0] + lp[128]) + (lp[256] + lp[384]);
       if (!mbar_wait(o_done, n & 1, abort_flag)) break;
       tc_fence_after();

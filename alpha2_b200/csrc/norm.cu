@@ -11,6 +11,7 @@
 // sums over the rows it walks, writes one partial row to scratch, and a second kernel adds
 // the partial rows in block order.  Algorithmic bytes per row: forward 2*dim*e, backward
 // 3*dim*e (e = element size) — the scratch adds 2*grid*dim*4 bytes per call.
+#include <stdlib.h>
 #include "tc_common.cuh"
 
 namespace alpha {
@@ -716,7 +717,7 @@ constexpr int LRF_STAGES = 4;
 template <typename T, int NV, bool RMS>
 __global__ void __launch_bounds__(LR_THREADS, 4)
 ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b, T *__restrict__ y,
-            int64_t rows, int dim, float eps, uint32_t *err) {
+            int64_t rows, int dim, float eps, uint32_t *err, int dbg) {
   using namespace tc;
   constexpr int V = Vec16<T>::N;
   constexpr int NE = NV * V;
@@ -774,9 +775,10 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
         t.get(&xv[v * V]);
       }
+      if (dbg == 2) fence_proxy_async();
       __syncwarp();
-      if (lane == 0) mbar_arrive(empty_bar(s));
-      if (r >= rows) continue;
+      if (dbg != 1 && lane == 0) mbar_arrive(empty_bar(s));
+      if (r >= rows) { if (dbg == 1) { __syncwarp(); if (lane == 0) mbar_arrive(empty_bar(s)); } continue; }
       float sum = 0.f;
 #pragma unroll
       for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
@@ -813,6 +815,7 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         t.set(o);
         t.store(yr + (v * 32 + lane) * V);
       }
+      if (dbg == 1) { __syncwarp(); if (lane == 0) mbar_arrive(empty_bar(s)); }
     }
   }
   if (*abort_flag) {  // a bounded wait ran out: let copies in flight land before the block's memory goes away
@@ -832,7 +835,8 @@ static int launch_fwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y
     attr = true;
   }
   ln_fwd_ring<T, NV, RMS><<<grid_for(rows, LR_WARPS, 4), LR_THREADS, smem, g_stream>>>(
-      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word());
+      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word(),
+      getenv("ALPHA_LN_DBG") ? atoi(getenv("ALPHA_LN_DBG")) : 0);
   return 0;
 }
 template <typename T, bool RMS>
@@ -948,7 +952,7 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   constexpr int V = Vec16<T>::N;
   const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
   constexpr int RK = sizeof(T) == 2 ? 1 : 2;
-  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
+  if (!getenv("ALPHA_LN_NORING") && fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
     if (launch_fwd_ring<T, RMS>((int)(dim / (32 * V)), x, w, b, y, rows, dim, eps)) return 1;
   } else if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
     const int nvec = (int)(dim / V);

@@ -49,18 +49,29 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Returns false when the wait gave up (limit reached, or another role already aborted).
+// Whole-warp wait: all 32 lanes of a warp call it together.  Returns false when the wait gave
+// up (limit reached, or another role already aborted).  The lanes poll independently and may
+// leave the loop in different iterations; the vote at the end brings the warp back together
+// before the warp-collective instructions that follow a wait (tcgen05.ld / .st, elect.sync)
+// and gives every lane the same answer.  Without it a wait that really had to spin could
+// leave the warp split, and a tcgen05.ld issued by part of a warp returns garbage.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const long long t0 = clock64();
-  while (true) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*abort_flag) return false;
-    if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
-      *abort_flag = 1;
-      return false;
+  bool ok = mbar_try_wait(bar, parity);
+  if (!ok) {
+    const long long t0 = clock64();
+    while (true) {
+      if (mbar_try_wait(bar, parity)) {
+        ok = true;
+        break;
+      }
+      if (*abort_flag) break;
+      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+        *abort_flag = 1;
+        break;
+      }
     }
   }
+  return __all_sync(0xffffffffu, ok);
 }
 
 // 2-D tiled TMA load global -> shared, completion counted on an mbarrier.  x is the

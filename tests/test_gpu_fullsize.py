@@ -1,0 +1,195 @@
+"""The hot path at the benchmark's full sizes (GPT-2-124M shape: N = 16384 tokens, E = 768,
+F = 3072, H = 12, D = 64, T = 1024, V = 50257), checked through properties that do not need
+an O(size) oracle run: checksums that the mathematics fixes (a GEMM against a vector, the
+rows of a softmax, the columns of dV), invariances (causality), slices compared with the
+dense oracle, and bit-reproducibility of whole steps.  Everything goes through the C ABI.
+"""
+import math
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+f32 = np.float32
+
+N, E, F, H, D, T, V, BATCH = 16384, 768, 3072, 12, 64, 1024, 50257, 16
+
+
+@pytest.fixture(scope="module")
+def B():
+    from alpha2_b200.backend import CudaBackend
+    b = CudaBackend(0)
+    yield b
+    b.checkAsyncError()
+
+
+def bf16_round(x):
+    from alpha2_b200.backend import bf16_to_f32, f32_to_bf16_bits
+    return bf16_to_f32(f32_to_bf16_bits(np.asarray(x, f32))).reshape(np.shape(x))
+
+
+@pytest.mark.parametrize("layout,M,Nn,K", [("nt", N, F, E), ("nt", N, E, F), ("nn", N, E, 3 * E), ("tn", F, E, N),
+                                           ("tn", 3 * E, E, N)])
+def test_gemm_checksums_at_full_size(B, layout, M, Nn, K):
+    """C 1 = A (B 1) and 1^T C = (1^T A) B: two O(size) host products pin every tile of C."""
+    from alpha2_b200 import _lib as L
+    from alpha2_b200._lib import check
+    r = np.random.default_rng(M + Nn + K)
+    sa, sb = {"nt": ((M, K), (Nn, K)), "nn": ((M, K), (K, Nn)), "tn": ((K, M), (K, Nn))}[layout]
+    a = bf16_round(r.standard_normal(sa) * 0.05)
+    b = bf16_round(r.standard_normal(sb) * 0.05)
+    A, Bm = B.upload(a, "bf16"), B.upload(b, "bf16")
+    Cm = B.zeros((M, Nn), "f32")
+    code = {"nt": L.GEMM_NT, "nn": L.GEMM_NN, "tn": L.GEMM_TN}[layout]
+    check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cm.ptr, M, Nn, K, sa[1], sb[1], Nn, L.BF16, L.F32, L.EPI_NONE, 0, 0, 0))
+    Cm.invalidate_host()
+    a64, b64 = a.astype(np.float64), b.astype(np.float64)
+    if layout == "nt":
+        rows, cols = a64 @ b64.sum(0), a64.sum(0) @ b64.T
+    elif layout == "nn":
+        rows, cols = a64 @ b64.sum(1), a64.sum(0) @ b64
+    else:
+        rows, cols = a64.T @ b64.sum(1), a64.sum(1) @ b64
+    got = Cm.data.astype(np.float64)
+    scale = math.sqrt(K) * 0.05 * 0.05
+    assert np.max(np.abs(got.sum(1) - rows)) < 1e-4 * scale * Nn
+    assert np.max(np.abs(got.sum(0) - cols)) < 1e-4 * scale * M
+
+
+def _qkv(seed):
+    r = np.random.default_rng(seed)
+    return bf16_round(r.standard_normal((N, 3 * E))), bf16_round(r.standard_normal((N, E)))
+
+
+def test_attention_at_full_size(B):
+    from oracle.gpt import flash_attention_dense, flash_attention_dense_backward
+    qkv, dout = _qkv(3)
+    qkv[:, 2 * E] = 1.0                       # first V column of head 0 is all ones
+    scale = 1 / math.sqrt(D)
+    QKV, dO = B.upload(qkv, "bf16"), B.upload(dout, "bf16")
+    out, lse = B.attentionQkv(QKV, BATCH, T, H, scale, 30.0)
+    o = out.data.reshape(BATCH, T, H, D)
+    # softmax rows sum to one: that column of O is one everywhere
+    assert np.max(np.abs(o[:, :, 0, 0] - 1.0)) < 2 ** -7
+    # two (batch, head) slices against the dense oracle at the full context length
+    split = lambda m, b, h, off: m.reshape(BATCH, T, -1)[b, :, off + h * D: off + (h + 1) * D][None]
+    dqkv = B.attentionQkvBackward(QKV, out, dO, lse, BATCH, T, H, scale, 30.0).data
+    for b, h in ((0, 0), (BATCH - 1, H - 1)):
+        q, k, v = (split(qkv, b, h, i * E) for i in range(3))
+        o_ref, lse_ref = flash_attention_dense(q, k, v, T, scale, 30.0)
+        assert np.max(np.abs(o[b, :, h] - o_ref[0])) < 2e-2 * np.max(np.abs(o_ref))
+        assert np.max(np.abs(lse.data.reshape(BATCH, H, T)[b, h] - lse_ref[0])) < 2e-3
+        dq, dk, dv = flash_attention_dense_backward(q, k, v, o[b, :, h][None], split(dout, b, h, 0),
+                                                    lse.data.reshape(BATCH, H, T)[b, h][None], T, scale, 30.0)
+        for i, ref in enumerate((dq, dk, dv)):
+            got = split(dqkv, b, h, i * E)
+            assert np.max(np.abs(got - ref)) < 4e-2 * np.max(np.abs(ref)), (b, h, i)
+    # columns of dV: sum_k dV[k] = sum_q dO[q] for every (batch, head), because P's rows sum to one
+    dv_all = dqkv[:, 2 * E:].reshape(BATCH, T, H, D).astype(np.float64).sum(1)
+    do_all = dout.reshape(BATCH, T, H, D).astype(np.float64).sum(1)
+    assert np.max(np.abs(dv_all - do_all)) < 0.05 * math.sqrt(T)
+    # causality: changing keys and values from position t0 on leaves earlier outputs bit-identical
+    t0 = 640
+    qkv2 = qkv.reshape(BATCH, T, 3 * E).copy()
+    qkv2[:, t0:, E:] = bf16_round(np.random.default_rng(9).standard_normal((BATCH, T - t0, 2 * E)))
+    out2, _ = B.attentionQkv(B.upload(qkv2.reshape(N, 3 * E), "bf16"), BATCH, T, H, scale, 30.0)
+    assert np.array_equal(out2.data.reshape(BATCH, T, E)[:, :t0], out.data.reshape(BATCH, T, E)[:, :t0])
+
+
+def test_attention_with_large_scores_at_full_size(B):
+    """Scores far outside the tanh polynomial's range (|s|/cap up to ~0.7): every tile takes
+    the hardware-tanh branch, the math warps run slower than the tensor core, and the result
+    must still be bit-reproducible and match the dense oracle."""
+    from oracle.gpt import flash_attention_dense
+    r = np.random.default_rng(8)
+    qkv = bf16_round(r.standard_normal((N, 3 * E)) * 2.0)
+    QKV = B.upload(qkv, "bf16")
+    scale = 1 / math.sqrt(D)
+    outs = [np.array(B.attentionQkv(QKV, BATCH, T, H, scale, 30.0)[0].data) for _ in range(4)]
+    assert all(np.array_equal(outs[0], o) for o in outs[1:])
+    assert float(np.abs(outs[0]).max()) < 16.0
+    o = outs[0].reshape(BATCH, T, H, D)
+    q4 = qkv.reshape(BATCH, T, 3, H, D)
+    for b, h in ((1, 3), (BATCH - 1, 0)):
+        o_ref, _ = flash_attention_dense(q4[b, :, 0, h][None], q4[b, :, 1, h][None], q4[b, :, 2, h][None], T, scale, 30.0)
+        assert np.max(np.abs(o[b, :, h] - o_ref[0])) < 2e-2 * np.max(np.abs(o_ref))
+    dout = bf16_round(r.standard_normal((N, E)))
+    out, lse = B.attentionQkv(QKV, BATCH, T, H, scale, 30.0)
+    dO = B.upload(dout, "bf16")
+    grads = [np.array(B.attentionQkvBackward(QKV, out, dO, lse, BATCH, T, H, scale, 30.0).data) for _ in range(3)]
+    assert all(np.array_equal(grads[0], g) for g in grads[1:]) and np.isfinite(grads[0]).all()
+
+
+def test_cross_entropy_at_full_size(B):
+    from alpha2_b200 import _lib as L
+    from alpha2_b200._lib import check
+    r = np.random.default_rng(4)
+    ld = (V + 63) // 64 * 64
+    logits = bf16_round(r.standard_normal((N, ld)) * 2)
+    targets = r.integers(0, V, N).astype(np.int32)
+    Lg, Tg = B.upload(logits, "bf16"), B.upload(targets, "i32")
+    dl, loss = B.zeros((N, ld), "bf16"), B.zeros((), "f32")
+    check(B.lib.alpha_softmax_ce_fwd_bwd(Lg.ptr, Tg.ptr, dl.ptr, loss.ptr, N, V, ld, 1.0, L.BF16))
+    dl.invalidate_host()
+    loss.invalidate_host()
+    g = dl.data[:, :V]
+    # softmax - onehot sums to zero along every row (bf16 rounding noise only)
+    assert np.max(np.abs(g.astype(np.float64).sum(1))) * N < 0.05
+    # sampled rows against f64
+    rows = r.integers(0, N, 48)
+    x = logits[rows, :V].astype(np.float64)
+    lse = np.log(np.exp(x - x.max(1, keepdims=True)).sum(1)) + x.max(1)
+    p = np.exp(x - lse[:, None])
+    p[np.arange(48), targets[rows]] -= 1
+    assert np.max(np.abs(g[rows] * N - p)) < 2 ** -8 * max(1.0, np.max(np.abs(p))) + 1e-6
+    # the mean loss: exact on the sample, and the full mean within the sample's spread
+    all_lse = np.empty(N)
+    for s in range(0, N, 2048):
+        xs = logits[s:s + 2048, :V].astype(np.float64)
+        all_lse[s:s + 2048] = np.log(np.exp(xs - xs.max(1, keepdims=True)).sum(1)) + xs.max(1)
+    want = float(np.mean(all_lse - logits[np.arange(N), targets].astype(np.float64)))
+    assert abs(loss.item() - want) < 2e-4 * want
+
+
+def test_layernorm_and_embedding_at_full_size(B):
+    r = np.random.default_rng(5)
+    x = bf16_round(r.standard_normal((N, E)) * 3 + 1)
+    g = bf16_round(r.standard_normal((N, E)))
+    w, b = B.ones((E,)), B.zeros((E,))
+    X, G = B.upload(x, "bf16"), B.upload(g, "bf16")
+    y = B.layerNorm(X, w, b, 1e-5).data.astype(np.float64)
+    assert np.max(np.abs(y.mean(1))) < 2e-3 and np.max(np.abs(y.var(1) - 1)) < 2e-2
+    bw = B.layerNormBackward(X, w, G, 1e-5)
+    dx, dw, db = bw["dx"], bw["dw"], bw["db"]
+    d = dx.data.astype(np.float64)
+    xhat = (x - x.mean(1, keepdims=True)) / np.sqrt(x.var(1, keepdims=True) + 1e-5)
+    # dx is orthogonal to 1 and to xhat, up to the bf16 rounding of 768 stored values per row
+    assert np.max(np.abs(d.sum(1))) < 0.25 and np.max(np.abs((d * xhat).sum(1))) < 0.5
+    assert np.max(np.abs(db.data - g.astype(np.float64).sum(0))) < 1e-2                    # column checksums
+    assert np.max(np.abs(dw.data - (g.astype(np.float64) * xhat).sum(0))) < 5e-2
+    # embedding backward: the checksum of checksums — all gradient mass lands in dW
+    idx = np.minimum(r.zipf(1.1, size=N) - 1, V - 1).astype(np.int32)
+    dW = B.embeddingBackward(B.upload(idx, "i32"), G, V)
+    assert np.max(np.abs(dW.data.astype(np.float64).sum(0) - g.astype(np.float64).sum(0))) < 1e-2
+    assert not dW.data[np.setdiff1d(np.arange(V), idx)[:1000]].any()                       # untouched rows stay zero
+
+
+def test_train_steps_at_full_size_are_reproducible(B):
+    """Three optimizer steps at the benchmark shape, twice from the same seed: identical bits
+    (no kernel on the path adds floats in a scheduling-dependent order), first loss = ln V."""
+    from alpha2_b200.data import zipf_batches
+    from alpha2_b200.gpt import ModelConfig
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    mc = ModelConfig(vocabSize=V, blockSize=T, nLayer=12, nEmbd=E, nHead=H, tied=True, init="plain", compute_dtype="bf16")
+    batches = zipf_batches(77, 3, BATCH, T, V)
+    runs = []
+    for _ in range(2):
+        tr = Trainer(B, mc, TrainConfig(iters=1000, batchSize=BATCH, warmupIters=100, seed=42))
+        res = [tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))]) for t, g in batches]
+        runs.append(([x["loss"] for x in res], [x["gradNorm"] for x in res],
+                     np.array(tr.params["layer.5.attn.wqkv"].data.data[:4, :8])))
+        del tr
+        B.purgeBufferPools()
+    assert runs[0][0] == runs[1][0] and runs[0][1] == runs[1][1] and np.array_equal(runs[0][2], runs[1][2])
+    # N(0, 0.02) weights with a tied head: the first loss sits a little above ln V = 10.82
+    assert abs(runs[0][0][0] - math.log(V)) < 0.5 and all(math.isfinite(v) for v in runs[0][0] + runs[0][1])
