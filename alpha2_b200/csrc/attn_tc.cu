@@ -674,12 +674,21 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       int bh, kb;
       decode(item, bh, kb);
       const int n_it = n_qb - kb;
-      for (int it = 0; it < n_it; it++) {
-        const int tt = t + it;
+      // the row's LSE and delta for the next tile are fetched one tile ahead, so that their
+      // global-memory latency is not paid at the start of every tile
+      auto fetch_row = [&](int it, float &lse_raw, float &dl) {
         const int qi = (kb + it) * 128 + row;
         const bool valid = qi < a.T;
-        k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
-        k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+        lse_raw = valid ? a.lse[(int64_t)bh * a.T + qi] : INFINITY;
+        dl = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
+      };
+      float lse_nxt, dl_nxt;
+      fetch_row(0, lse_nxt, dl_nxt);
+      for (int it = 0; it < n_it; it++) {
+        const int tt = t + it;
+        k.lse2 = lse_nxt * LOG2E;
+        k.delta = dl_nxt;
+        if (it + 1 < n_it) fetch_row(it + 1, lse_nxt, dl_nxt);
         uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
         if (!mbar_wait(s_full0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
         tc_fence_after();
