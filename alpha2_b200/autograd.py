@@ -618,3 +618,28 @@ def lmHeadLoss(ctx, x: Variable, w: Variable, targets: TensorData, gradScale: fl
         state["dl"] = None
         return [dx, dw]
     return _record(ctx, loss, [x, w], bw, cleanup)
+
+
+def checkpoint(ctx, fn, input: Variable) -> Variable:
+    """Activation checkpointing (packages/autograd/src/checkpoint.ts:36-87): run ``fn(innerCtx,
+    input)`` on a throw-away tape, keep only its output, and record ONE entry on the outer tape
+    whose backward re-runs ``fn`` on a fresh tape, backpropagates through it (parameter
+    gradients accumulate directly on the captured parameters) and returns the input gradient.
+    Memory per segment drops from all its intermediates to its input; compute grows by one
+    forward of the segment.  Only for deterministic segments (dropout 0)."""
+    B = ctx.backend
+    tmp = Ctx(Tape(), B, ctx.dropoutRng, None)
+    tmp_out = fn(tmp, input)
+    out_data = tmp_out.data
+    tmp.tape.clear(ctx.release, tmp_out)                      # intermediates go, the output stays
+
+    def bw(g, backend, release, needs):
+        re_input = Variable(input.data, True)
+        re = Ctx(Tape(), backend, ctx.dropoutRng, None)
+        re_out = fn(re, re_input)
+        re.tape.backward(re_out, backend, release, backend.clone(g))
+        grad = re_input.grad
+        re_input.grad = None
+        re.tape.clear(release)
+        return [grad if grad is not None else backend.zeros(input.data.shape, input.data.dtype)]
+    return _record(ctx, out_data, [input], bw)

@@ -238,10 +238,13 @@ def _block_fused(ctx: Ctx, cfg: ModelConfig, x: Variable, P: GPTParams, i: int, 
 
 def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: Tape, tokens: TensorData,
                targets: TensorData | None = None, training: bool = False, attention: str = "fused",
-               dropoutRng=None, release=None, lossGradScale: float = 1.0, lastOnly: bool = False):
+               dropoutRng=None, release=None, lossGradScale: float = 1.0, lastOnly: bool = False,
+               activationCheckpointing: bool = False):
     """gpt.ts:344-427.  tokens/targets: int32 [B, T].  Returns {"logits": Variable|None, "loss": Variable|None}.
     ``lastOnly`` (fused route, no targets): project only each sequence's last position —
-    logits [B, 1, V], what sampling reads (sample.ts:62-72) — instead of all T rows."""
+    logits [B, 1, V], what sampling reads (sample.ts:62-72) — instead of all T rows.
+    ``activationCheckpointing`` (with ``training``): every transformer block becomes one
+    checkpointed segment (gpt.ts:393-403), recomputed during backward."""
     ctx = Ctx(tape, backend, dropoutRng, release)
     Bn, T = tokens.shape
     E = cfg.nEmbd
@@ -260,7 +263,10 @@ def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: 
         else:
             x = ag.embeddingPos(ctx, P["wte"], P["wpe"], tokens)      # [B*T, E]
         for i in range(cfg.nLayer):
-            x = _block_fused(ctx, cfg, x, P, i, Bn, T)
+            if activationCheckpointing and training:
+                x = ag.checkpoint(ctx, lambda c, xi, i=i: _block_fused(c, cfg, xi, P, i, Bn, T), x)
+            else:
+                x = _block_fused(ctx, cfg, x, P, i, Bn, T)
         x = _norm(ctx, cfg, x, P, "lnF")
         if targets is not None:
             tflat = backend.reshape(targets, (Bn * T,))
@@ -292,7 +298,11 @@ def gptForward(cfg: ModelConfig, params: GPTParams, backend: CudaBackend, tape: 
         mask = backend.causalMask(T)
         _mask_cache[(T, backend.device)] = mask
     for i in range(cfg.nLayer):
-        x = _block_reference(ctx, cfg, x, P, i, Bn, T, mask, attention, training)
+        if activationCheckpointing and training:
+            x = ag.checkpoint(ctx, lambda c, xi, i=i: _block_reference(c, cfg, xi, P, i, Bn, T, mask, attention,
+                                                                       training), x)
+        else:
+            x = _block_reference(ctx, cfg, x, P, i, Bn, T, mask, attention, training)
     x = _norm(ctx, cfg, x, P, "lnF")
     flat = ag.reshape(ctx, x, (Bn * T, E))
     logits = ag.reshape(ctx, _lin(ctx, flat, head), (Bn, T, cfg.vocabSize))

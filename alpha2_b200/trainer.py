@@ -120,7 +120,7 @@ class DataParallel:
 class Trainer:
     def __init__(self, backend: CudaBackend, modelConfig: ModelConfig, trainConfig: TrainConfig,
                  params=None, attention: str = "fused", fused: bool = True, dp: DataParallel | None = None,
-                 release: bool = True):
+                 release: bool = True, activationCheckpointing: bool = False):
         self.B, self.mc, self.tc = backend, modelConfig, trainConfig
         if params is None:
             rng = SeededRng(trainConfig.seed)
@@ -132,6 +132,7 @@ class Trainer:
                          noDecayNames=noDecayNames(modelConfig))
         self.tape = Tape()
         self.attention, self.fused, self.dp = attention, fused, dp
+        self.activationCheckpointing = activationCheckpointing      # trainer.ts:559,1203
         self.step_index = 0
         self.releaseFn = backend.releaseGpuTensor if release else None
 
@@ -150,7 +151,8 @@ class Trainer:
         loss_td = None
         for mi, (tokens, targets) in enumerate(batches):
             out = gptForward(self.mc, self.params, B, self.tape, tokens, targets, training=True,
-                             attention=self.attention, release=self.releaseFn)
+                             attention=self.attention, release=self.releaseFn,
+                             activationCheckpointing=self.activationCheckpointing)
             loss = out["loss"]
             if accum > 1:                                      # trainer.ts:1210-1226
                 scaled = B.scale(loss.data, 1 / accum)

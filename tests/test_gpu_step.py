@@ -148,3 +148,23 @@ def test_config5_shape_small(B):
     tcfg = dict(iters=10, batchSize=4, seed=3)
     run_parity(B, mc, tcfg, batches, "fused", True, 3, 1e-4, 1e-4)
     run_parity(B, mc, tcfg, batches, "fused", True, 3, 2e-2, 0, dtype="bf16", check_params=False)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_activation_checkpointing_on_the_device(B, dtype):
+    """Every block recomputed during backward (packages/autograd/src/checkpoint.ts): same
+    losses and parameters as the plain run, bit for bit (the kernels are deterministic)."""
+    from alpha2_b200.gpt import ModelConfig
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    mc = ModelConfig(vocabSize=512, blockSize=128, nLayer=3, nEmbd=128, nHead=2, tied=True, init="plain",
+                     compute_dtype=dtype)
+    batches = otrain.zipf_batches(9, 3, 4, 128, 512)
+    runs = []
+    for ck in (False, True):
+        tr = Trainer(B, mc, TrainConfig(iters=10, batchSize=4, gradClip=1.0, seed=11), activationCheckpointing=ck)
+        losses = [tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))])["loss"] for t, g in batches]
+        runs.append((losses, {n: np.array(v.data.data) for n, v in tr.entries}))
+    assert runs[0][0] == runs[1][0]
+    for n in runs[0][1]:
+        assert np.array_equal(runs[0][1][n], runs[1][1][n]), n

@@ -108,3 +108,32 @@ def test_product_rng_equals_oracle_rng():
     a, b = SeededRng(77), OracleRng(77)
     assert [a.next() for _ in range(10)] == [b.next() for _ in range(10)]
     assert np.array_equal(a.fill_gauss((7, 9), 0.02), b.fill_gauss((7, 9), 0.02))
+
+
+def test_activation_checkpointing_matches_plain_training():
+    """packages/tests/src/autograd.test.ts:157-189 (checkpoint equivalence): the same steps
+    with every block checkpointed give the same losses and parameters, bit for bit on a
+    deterministic backend, while the outer tape holds one entry per block."""
+    from alpha2_b200.autograd import Tape
+    from alpha2_b200.data import uniform_batches
+    from alpha2_b200.gpt import ModelConfig, gptForward
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    from tests.fake_backend import NumpyBackend, T
+    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=3, nEmbd=32, nHead=2, tied=True, init="plain")
+    batches = uniform_batches(5, 3, 2, 16, 64)
+    runs = []
+    for ck in (False, True):
+        tr = Trainer(NumpyBackend(), mc, TrainConfig(iters=10, batchSize=2, gradClip=0.5, seed=3),
+                     activationCheckpointing=ck)
+        losses = [tr.train_step([(T(t, "i32"), T(g, "i32"))])["loss"] for t, g in batches]
+        runs.append((losses, {n: np.array(v.data.data) for n, v in tr.entries}))
+    assert runs[0][0] == runs[1][0]
+    for n in runs[0][1]:
+        assert np.array_equal(runs[0][1][n], runs[1][1][n]), n
+    B = NumpyBackend()
+    tr = Trainer(B, mc, TrainConfig(iters=10, batchSize=2, seed=3))
+    t0, g0 = batches[0]
+    plain, ck = Tape(), Tape()
+    gptForward(mc, tr.params, B, plain, T(t0, "i32"), T(g0, "i32"), training=True)
+    gptForward(mc, tr.params, B, ck, T(t0, "i32"), T(g0, "i32"), training=True, activationCheckpointing=True)
+    assert ck.size < plain.size and ck.size <= 3 + 4            # embedding, 3 segments, final norm, head
