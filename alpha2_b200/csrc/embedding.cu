@@ -109,22 +109,20 @@ __global__ void __launch_bounds__(RANK_TILE) emb_rank_kernel(const int32_t *__re
 }
 
 // One block: exclusive prefix sum of count[0..vocab) into start[0..vocab]; in place allowed.
-// Every thread owns a run of consecutive entries: it sums its run, the 1024 run sums are
-// scanned with shuffles, then the thread writes its run.
+// Every warp owns a contiguous segment and walks it in 32-element chunks with coalesced
+// accesses: a first pass sums the segment, the 32 segment sums are scanned with shuffles, a
+// second pass writes the running prefix (four chunks of loads in flight at a time).
 __global__ void __launch_bounds__(1024) emb_scan_kernel(const int32_t *count, int32_t *start, int64_t vocab) {
   __shared__ int32_t warp_tot[32];
   const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-  const int64_t per = (vocab + 1 + 1023) / 1024;
-  const int64_t b = (int64_t)threadIdx.x * per, e = (b + per < vocab + 1) ? b + per : vocab + 1;
+  const int64_t n = vocab + 1;                                  // entry `vocab` holds the total
+  const int64_t seg = ((n + 31) / 32 + 31) / 32 * 32;           // per-warp segment, a multiple of 32
+  const int64_t b = (int64_t)wid * seg, e = b + seg < n ? b + seg : n;
   int32_t sum = 0;
-  for (int64_t i = b; i < e; i++) sum += i < vocab ? count[i] : 0;
-  int32_t incl = sum;
+  for (int64_t i = b + lane; i < e; i += 32) sum += i < vocab ? count[i] : 0;
 #pragma unroll
-  for (int o = 1; o < 32; o <<= 1) {
-    const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
-    if (lane >= o) incl += t;
-  }
-  if (lane == 31) warp_tot[wid] = incl;
+  for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane == 0) warp_tot[wid] = sum;
   __syncthreads();
   if (wid == 0) {
     int32_t w = warp_tot[lane], wi = w;
@@ -133,14 +131,29 @@ __global__ void __launch_bounds__(1024) emb_scan_kernel(const int32_t *count, in
       const int32_t t = __shfl_up_sync(0xffffffffu, wi, o);
       if (lane >= o) wi += t;
     }
-    warp_tot[lane] = wi - w;  // exclusive offset of each warp
+    warp_tot[lane] = wi - w;  // exclusive offset of each warp's segment
   }
   __syncthreads();
-  int32_t acc = warp_tot[wid] + incl - sum;
-  for (int64_t i = b; i < e; i++) {
-    const int32_t v = i < vocab ? count[i] : 0;
-    start[i] = acc;
-    acc += v;
+  int32_t carry = warp_tot[wid];
+  for (int64_t c0 = b; c0 < e; c0 += 128) {
+    int32_t v[4];
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      const int64_t i = c0 + u * 32 + lane;
+      v[u] = (i < e && i < vocab) ? count[i] : 0;
+    }
+#pragma unroll
+    for (int u = 0; u < 4; u++) {
+      int32_t incl = v[u];
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int32_t t = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += t;
+      }
+      const int64_t i = c0 + u * 32 + lane;
+      if (i < e) start[i] = carry + incl - v[u];
+      carry += __shfl_sync(0xffffffffu, incl, 31);
+    }
   }
 }
 
