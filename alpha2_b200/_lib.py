@@ -54,7 +54,8 @@ class ProfileEntry(C.Structure):
     _fields_ = [("ms", C.c_double), ("work", C.c_double), ("launches", C.c_int64)]
 
 
-PROFILE_CATEGORIES = ["gemm_tc", "gemm_f32", "attn_fwd", "attn_bwd", "cross_entropy", "adamw", "norm", "embedding"]
+PROFILE_CATEGORIES = ["gemm_tc", "gemm_f32", "attn_fwd", "attn_bwd", "cross_entropy", "adamw", "norm", "embedding",
+                      "elementwise"]
 
 
 class HostRng(C.Structure):
@@ -104,6 +105,7 @@ SIGNATURES = {
     "alpha_flash_attn_fwd": [_B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_flash_attn_bwd": [_B, _B, _B, _B, _B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_rope": [_B, _B, _L, _L, _L, _L, _L, _F, _I, _I],
+    "alpha_rope_qkv": [_B, _B, _L, _L, _L, _L, _F, _I, _I],
     "alpha_cross_entropy_fwd": [_B, _B, _B, _L, _L, _L, _I],
     "alpha_cross_entropy_fwd_noalloc": [_B, _B, _B, _L, _L, _L, _I],
     "alpha_cross_entropy_bwd": [_B, _B, _B, _B, _L, _L, _L, _I],

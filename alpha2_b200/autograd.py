@@ -469,11 +469,28 @@ def linear(ctx, x: Variable, w: Variable) -> Variable:
     xd = x.data
     wd = _compute_weight(w)
 
-    def bw(g, B, rel, needs):
-        ga = B.matmul(g, wd) if needs[0] else None
-        gb = B.matmulTransposedA(g, xd) if needs[1] else None
+    def bw(g, B, rel, needs, acc):
+        ga = _dx_gemm(B, g, wd, acc[0]) if needs[0] else None
+        gb = _dw_gemm(B, g, xd, acc[1]) if needs[1] else None
         return [ga, gb]
-    return _record(ctx, ctx.backend.matmulTransposed(xd, wd), [x, w], bw)
+    return _record(ctx, ctx.backend.matmulTransposed(xd, wd), [x, w], bw, in_place=True)
+
+
+def _dw_gemm(B, g: TensorData, xd: TensorData, acc: TensorData | None):
+    """g^T @ x; added inside the GEMM to a weight gradient that already exists (accumulated
+    micro-steps, shared weights) when the backend can."""
+    if acc is not None and hasattr(B, "matmulInto") and acc.dtype == ("f32" if g.dtype == "bf16" else g.dtype):
+        B.matmulTransposedA(g, xd, into=acc)
+        return ACCUMULATED
+    return B.matmulTransposedA(g, xd)
+
+
+def _dx_gemm(B, g: TensorData, wd: TensorData, acc: TensorData | None):
+    """g @ w; added in the GEMM epilogue to an input gradient that another consumer already left."""
+    if acc is not None and hasattr(B, "matmulInto") and acc.dtype == g.dtype and len(wd.shape) == 2:
+        B.matmulInto(g, wd, acc)
+        return ACCUMULATED
+    return B.matmul(g, wd)
 
 
 def linearGelu(ctx, x: Variable, w: Variable) -> Variable:
@@ -496,11 +513,11 @@ def linearAdd(ctx, x: Variable, w: Variable, residual: Variable) -> Variable:
     xd = x.data
     wd = _compute_weight(w)
 
-    def bw(g, B, rel, needs):
+    def bw(g, B, rel, needs, acc):
         ga = B.matmul(g, wd) if needs[0] else None
-        gb = B.matmulTransposedA(g, xd) if needs[1] else None
+        gb = _dw_gemm(B, g, xd, acc[1]) if needs[1] else None
         return [ga, gb, g]
-    return _record(ctx, ctx.backend.matmulTransposedAdd(xd, wd, residual.data), [x, w, residual], bw)
+    return _record(ctx, ctx.backend.matmulTransposedAdd(xd, wd, residual.data), [x, w, residual], bw, in_place=True)
 
 
 def mlpGelu(ctx, x: Variable, w1: Variable, w2: Variable, residual: Variable) -> Variable:
@@ -513,13 +530,13 @@ def mlpGelu(ctx, x: Variable, w1: Variable, w2: Variable, residual: Variable) ->
     pre, act = B0.matmulTransposedGelu(xd, w1d)
     out = B0.matmulTransposedAdd(act, w2d, residual.data)
 
-    def bw(g, B, rel, needs):
-        dw2 = B.matmulTransposedA(g, act) if needs[2] else None
+    def bw(g, B, rel, needs, acc):
+        dw2 = _dw_gemm(B, g, act, acc[2]) if needs[2] else None
         dpre = B.matmulGeluBackward(g, w2d, pre)
         dx = B.matmul(dpre, w1d) if needs[0] else None
-        dw1 = B.matmulTransposedA(dpre, xd) if needs[1] else None
+        dw1 = _dw_gemm(B, dpre, xd, acc[1]) if needs[1] else None
         return [dx, dw1, dw2, g]
-    return _record(ctx, out, [x, w1, w2, residual], bw)
+    return _record(ctx, out, [x, w1, w2, residual], bw, in_place=True)
 
 
 def _compute_weight(w: Variable) -> TensorData:
@@ -546,20 +563,12 @@ def attentionQkv(ctx, qkv: Variable, Bn: int, T: int, H: int, scale_: float, sof
 
 
 def ropeQk(ctx, qkv: Variable, Bn: int, T: int, H: int, theta: float = 10000.0) -> Variable:
-    """Rotary embedding applied in place to the q and k column blocks of [B*T, 3E]."""
-    B0 = ctx.backend
-    E3 = qkv.data.shape[-1]
-    E = E3 // 3
-    D = E // H
-    out = B0.clone(qkv.data)
-    B0.rope(out, Bn, T, H, D, E3, 0, theta)
-    B0.rope(out, Bn, T, H, D, E3, E, theta)
+    """Rotary embedding of the q and k column blocks of [B*T, 3E] (v passes through); the
+    backward is the transposed rotation of the gradient.  One launch each way."""
+    out = ctx.backend.ropeQkv(qkv.data, Bn, T, H, theta)
 
     def bw(g, B, rel, n):
-        d = B.clone(g)
-        B.rope(d, Bn, T, H, D, E3, 0, theta, inverse=True)
-        B.rope(d, Bn, T, H, D, E3, E, theta, inverse=True)
-        return [d]
+        return [B.ropeQkv(g, Bn, T, H, theta, inverse=True)]
     return _record(ctx, out, [qkv], bw)
 
 

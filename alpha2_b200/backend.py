@@ -460,14 +460,29 @@ class CudaBackend:
         rows = a.size // K
         return self._gemm(L.GEMM_NT, a, b, rows, N, K, K, K, out_shape=a.shape[:-1] + (N,))
 
-    def matmulTransposedA(self, a: TensorData, b: TensorData) -> TensorData:
-        """C = A^T @ B with A stored [K, M], B [K, N] (ops.ts:176-177,224-225)."""
+    def matmulTransposedA(self, a: TensorData, b: TensorData, into: TensorData | None = None) -> TensorData:
+        """C = A^T @ B with A stored [K, M], B [K, N] (ops.ts:176-177,224-225).  ``into``: an
+        existing [M, N] gradient that the product is added to inside the GEMM (one pass instead
+        of a product and a separate addInplace); it is returned."""
         K, M = a.size // a.shape[-1], a.shape[-1]
         K2, N = b.size // b.shape[-1], b.shape[-1]
         if K != K2:
             raise AlphaCudaError(f"matmulTransposedA shape mismatch: {list(a.shape)} x {list(b.shape)}")
         out_dtype = "f32" if a.dtype == "bf16" and self.param_grads_f32 else a.dtype
+        if into is not None:
+            if into.size != M * N or into.dtype != out_dtype:
+                raise AlphaCudaError(f"matmulTransposedA: cannot accumulate into {list(into.shape)} {into.dtype}")
+            return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype, out=into, accumulate=True)
         return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype)
+
+    def matmulInto(self, a: TensorData, b: TensorData, into: TensorData) -> TensorData:
+        """into += A @ B for A [rows, K], B [K, N] with the add in the GEMM epilogue (the
+        gradient of an activation that already has one from another consumer)."""
+        K, N = b.shape
+        rows = a.size // K
+        if into.size != rows * N or into.dtype != a.dtype:
+            raise AlphaCudaError(f"matmulInto: cannot accumulate into {list(into.shape)} {into.dtype}")
+        return self._gemm(L.GEMM_NN, a, b, rows, N, K, K, N, epilogue=L.EPI_ADD, aux=into, out=into)
 
     #: weight gradients of bf16 GEMMs are produced in f32 (they feed f32 AdamW state)
     param_grads_f32 = True
@@ -616,6 +631,17 @@ class CudaBackend:
         check(self.lib.alpha_rope(p, p, batch, T, heads, D, ld, float(theta), 1 if inverse else 0,
                                   self._code(x.dtype)))
         x.invalidate_host()
+
+    def ropeQkv(self, qkv: TensorData, batch: int, T: int, heads: int, theta: float = 10000.0,
+                inverse: bool = False) -> TensorData:
+        """Rotary embedding of the q and k column blocks of a fused activation [batch*T, 3E] into a
+        new tensor (v copied alongside): one pass over the rows."""
+        E3 = qkv.shape[-1]
+        D = E3 // 3 // heads
+        out = self._new(qkv.shape, qkv.dtype)
+        check(self.lib.alpha_rope_qkv(qkv.ptr, out.ptr, batch, T, heads, D, float(theta), 1 if inverse else 0,
+                                      self._code(qkv.dtype)))
+        return out
 
     def crossEntropy(self, logits: TensorData, targets: TensorData) -> TensorData:
         N, V = logits.shape

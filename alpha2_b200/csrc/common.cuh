@@ -21,6 +21,7 @@ extern unsigned long long g_launches;
 int set_error(const char *fmt, ...);
 // Scratch from the caching pool (runtime.cu); returned with pool_free.
 int pool_alloc(size_t bytes, void **out);
+void rope_tables_clear();  // rope.cu: frees the cos/sin tables (shutdown)
 int pool_free(void *p);
 // Device-resident copy of a small host table (pointer/size tables of the multi-tensor
 // kernels).  Tables are cached by content, so a training loop that passes the same
@@ -30,7 +31,7 @@ int table_upload(const void *host, size_t bytes, const void **dev);
 // Per-kernel-family timing (alpha_profile_*): when enabled, the launch sites of the heavy
 // kernels bracket themselves with CUDA events on the compute stream.
 enum ProfCat { PROF_GEMM_TC = 0, PROF_GEMM_F32 = 1, PROF_ATTN_FWD = 2, PROF_ATTN_BWD = 3, PROF_CE = 4,
-               PROF_ADAMW = 5, PROF_NORM = 6, PROF_EMBED = 7, PROF_NCAT = 8 };
+               PROF_ADAMW = 5, PROF_NORM = 6, PROF_EMBED = 7, PROF_ELEMENTWISE = 8, PROF_NCAT = 9 };
 extern bool g_profiling;
 void prof_begin(int cat, double work);
 void prof_end(int cat);

@@ -184,6 +184,7 @@ template <typename T> struct OpResidualDropoutAdd {
 template <typename T, typename Op>
 static int launch_ew(Op op, int64_t n) {
   if (n <= 0) return 0;
+  ProfScope prof(PROF_ELEMENTWISE, (double)n);
   const int block = 256;
   const int grid = grid_for((n + Vec16<T>::N - 1) / Vec16<T>::N, block, 16);
   ew_kernel<T, Op><<<grid, block, 0, g_stream>>>(op, n);
@@ -434,6 +435,7 @@ int alpha_add_inplace(alpha_buf a, alpha_buf b, int64_t n, int a_dtype, int b_dt
         OpBinary<T>{ptr<T>(a), ptr<T>(b), ptr<T>(a), ALPHA_ADD, al16(a) && al16(b)}, n));
   }
   ALPHA_CHECK(a_dtype == ALPHA_F32 && b_dtype == ALPHA_BF16, "alpha_add_inplace: only f32 += bf16 mixes dtypes");
+  ProfScope prof(PROF_ELEMENTWISE, (double)n);
   add_inplace_kernel<float, __nv_bfloat16><<<grid_for(n, 256, 16), 256, 0, g_stream>>>(ptr<float>(a),
                                                                                          ptr<__nv_bfloat16>(b), n);
   ALPHA_LAUNCHED();
@@ -448,6 +450,7 @@ int alpha_scale_inplace(alpha_buf a, float s, int64_t n, int dtype) {
 int alpha_cast(alpha_buf src, int sdt, alpha_buf dst, int ddt, int64_t n) {
   ALPHA_REQUIRE_INIT();
   if (n <= 0) return 0;
+  ProfScope prof(PROF_ELEMENTWISE, (double)n);
   const int grid = grid_for((n + 3) / 4, 256, 16);
   if (sdt == ALPHA_F32 && ddt == ALPHA_BF16)
     cast_kernel<float, __nv_bfloat16><<<grid, 256, 0, g_stream>>>(ptr<float>(src), ptr<__nv_bfloat16>(dst), n);

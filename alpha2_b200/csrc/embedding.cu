@@ -288,6 +288,7 @@ int alpha_embedding_fwd(alpha_buf weight, alpha_buf indices, alpha_buf out, int6
                         int64_t vocab, int dtype) {
   ALPHA_REQUIRE_INIT();
   if (n_idx == 0 || dim == 0) return 0;
+  ProfScope prof(PROF_EMBED, 2.0 * n_idx * dim * dtype_size(dtype));
   const bool a16 = (weight & 15) == 0 && (out & 15) == 0;
   if (dtype == ALPHA_F32) {
     const bool vec = a16 && dim % 4 == 0;
@@ -309,6 +310,7 @@ int alpha_embedding_pos_fwd(alpha_buf wte, alpha_buf wpe, alpha_buf tokens, alph
   ALPHA_REQUIRE_INIT();
   const int64_t n_idx = batch * T;
   if (n_idx == 0 || dim == 0) return 0;
+  ProfScope prof(PROF_EMBED, 3.0 * n_idx * dim * dtype_size(dtype));
   const bool a16 = (wte & 15) == 0 && (wpe & 15) == 0 && (out & 15) == 0;
   if (dtype == ALPHA_F32) {
     embedding_pos_fwd_kernel<float><<<grid_for(n_idx * dim / 4 + 1, 256, 16), 256, 0, g_stream>>>(
@@ -336,6 +338,7 @@ int alpha_embedding_bwd(alpha_buf indices, alpha_buf grad, alpha_buf dw, int64_t
     if (!accumulate) ALPHA_CUDA(cudaMemsetAsync(ptr<void>(dw), 0, (size_t)vocab * dim * 4, g_stream));
     return 0;
   }
+  ProfScope prof(PROF_EMBED, (double)n_idx * dim * dtype_size(grad_dtype));
   void *scratch = nullptr;
   constexpr int HOT_CAP = 1024;
   const size_t n_ints = (size_t)2 * n_idx + vocab + 1 + HOT_CAP + 1;

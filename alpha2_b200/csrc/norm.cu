@@ -545,8 +545,13 @@ __global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, co
 // and are combined across the four warps once at the end, in fixed order.
 constexpr int LR_WARPS = 4, LR_STAGES = 3, LR_THREADS = (LR_WARPS + 1) * 32;
 
+// 32 elements per lane need more registers than three resident blocks leave (and their ring
+// takes a third of the shared memory anyway): two blocks per SM there.
+template <typename T, int NV>
+constexpr int lr_bwd_blocks() { return NV * (16 / (int)sizeof(T)) > 24 ? 2 : 3; }
+
 template <typename T, int NV, bool RMS, bool HAS_ADD>
-__global__ void __launch_bounds__(LR_THREADS, 3)
+__global__ void __launch_bounds__(LR_THREADS, lr_bwd_blocks<T, NV>())
 ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__restrict__ g,
             const T *__restrict__ dx_add, T *__restrict__ dx, float *__restrict__ part, int64_t rows, int dim, float eps,
             uint32_t *err) {
@@ -717,7 +722,7 @@ constexpr int LRF_STAGES = 4;
 template <typename T, int NV, bool RMS>
 __global__ void __launch_bounds__(LR_THREADS, 4)
 ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *__restrict__ b, T *__restrict__ y,
-            int64_t rows, int dim, float eps, uint32_t *err, int dbg) {
+            int64_t rows, int dim, float eps, uint32_t *err) {
   using namespace tc;
   constexpr int V = Vec16<T>::N;
   constexpr int NE = NV * V;
@@ -775,10 +780,9 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
         t.get(&xv[v * V]);
       }
-      if (dbg == 2) fence_proxy_async();
       __syncwarp();
-      if (dbg != 1 && lane == 0) mbar_arrive(empty_bar(s));
-      if (r >= rows) { if (dbg == 1) { __syncwarp(); if (lane == 0) mbar_arrive(empty_bar(s)); } continue; }
+      if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the slot can be refilled
+      if (r >= rows) continue;
       float sum = 0.f;
 #pragma unroll
       for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
@@ -815,7 +819,6 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         t.set(o);
         t.store(yr + (v * 32 + lane) * V);
       }
-      if (dbg == 1) { __syncwarp(); if (lane == 0) mbar_arrive(empty_bar(s)); }
     }
   }
   if (*abort_flag) {  // a bounded wait ran out: let copies in flight land before the block's memory goes away
@@ -835,8 +838,7 @@ static int launch_fwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y
     attr = true;
   }
   ln_fwd_ring<T, NV, RMS><<<grid_for(rows, LR_WARPS, 4), LR_THREADS, smem, g_stream>>>(
-      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word(),
-      getenv("ALPHA_LN_DBG") ? atoi(getenv("ALPHA_LN_DBG")) : 0);
+      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word());
   return 0;
 }
 template <typename T, bool RMS>
@@ -847,6 +849,7 @@ static int launch_fwd_ring(int nv, alpha_buf x, alpha_buf w, alpha_buf b, alpha_
     case 1 * K: return launch_fwd_ring_nv<T, 1 * K, RMS>(x, w, b, y, rows, dim, eps);
     case 2 * K: return launch_fwd_ring_nv<T, 2 * K, RMS>(x, w, b, y, rows, dim, eps);
     case 3 * K: return launch_fwd_ring_nv<T, 3 * K, RMS>(x, w, b, y, rows, dim, eps);
+    case 4 * K: return launch_fwd_ring_nv<T, 4 * K, RMS>(x, w, b, y, rows, dim, eps);
   }
   return set_error("layernorm forward: unsupported vector count %d", nv);
 }
@@ -952,7 +955,7 @@ static int norm_fwd(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t 
   constexpr int V = Vec16<T>::N;
   const bool fast = dim % V == 0 && (x & 15) == 0 && (y & 15) == 0 && dim / V <= 32 * 8;
   constexpr int RK = sizeof(T) == 2 ? 1 : 2;
-  if (!getenv("ALPHA_LN_NORING") && fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
+  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 4 * RK && rows >= 4 * LR_WARPS) {
     if (launch_fwd_ring<T, RMS>((int)(dim / (32 * V)), x, w, b, y, rows, dim, eps)) return 1;
   } else if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0 && (RMS || (b & 15) == 0)) {
     const int nvec = (int)(dim / V);
@@ -1004,11 +1007,12 @@ static int launch_bwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf d
 template <typename T, bool RMS, bool HAS_ADD>
 static int launch_bwd_ring(int nv, alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, float *part,
                            int64_t rows, int64_t dim, float eps, int grid) {
-  constexpr int K = sizeof(T) == 2 ? 1 : 2;  // lanes hold up to 24 elements: 3 bf16 vectors or 6 f32 vectors
+  constexpr int K = sizeof(T) == 2 ? 1 : 2;  // lanes hold up to 32 elements: 4 bf16 vectors or 8 f32 vectors
   switch (nv) {
     case 1 * K: return launch_bwd_ring_nv<T, 1 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
     case 2 * K: return launch_bwd_ring_nv<T, 2 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
     case 3 * K: return launch_bwd_ring_nv<T, 3 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
+    case 4 * K: return launch_bwd_ring_nv<T, 4 * K, RMS, HAS_ADD>(x, w, g, dx_add, dx, part, rows, dim, eps, grid);
   }
   return set_error("layernorm backward: unsupported vector count %d", nv);
 }
@@ -1028,13 +1032,12 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
   constexpr int V = Vec16<T>::N;
   const size_t smem = (size_t)LN_WARPS * 2 * dim * sizeof(float);
   const bool fast = dim % V == 0 && (x & 15) == 0 && (g & 15) == 0 && (dx & 15) == 0 && (dx_add & 15) == 0 &&
-                    dim / V <= 32 * 8 &&
-                    smem <= 48 * 1024;
+                    dim / V <= 32 * 8;
   constexpr int RK = sizeof(T) == 2 ? 1 : 2;  // 16-byte vectors per 8 elements
-  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 3 * RK && rows >= 4 * LR_WARPS) {
-    // ring-fed warp-per-row kernel: 8, 16 or 24 elements per lane
+  if (fast && dim % (32 * V * RK) == 0 && dim / (32 * V) <= 4 * RK && rows >= 4 * LR_WARPS) {
+    // ring-fed warp-per-row kernel: 8, 16, 24 or 32 elements per lane
     const int nv = (int)(dim / (32 * V));
-    const int grid = grid_for(rows, LR_WARPS, 3);
+    const int grid = grid_for(rows, LR_WARPS, nv * V > 24 ? 2 : 3);
     void *part = nullptr;
     if (pool_alloc((size_t)grid * 2 * dim * sizeof(float), &part)) return 1;
     int rc = dx_add ? launch_bwd_ring<T, RMS, true>(nv, x, w, g, dx_add, dx, (float *)part, rows, dim, eps, grid)
@@ -1061,7 +1064,7 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
     ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, LN_RED_GROUPS), 0, g_stream>>>(
         (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
     pool_free(part);
-  } else if (fast) {
+  } else if (fast && smem <= 48 * 1024) {
     const int nv = (int)((dim / V + 31) / 32);
     int grid = grid_for(rows, LN_WARPS, 4);
     void *part = nullptr;

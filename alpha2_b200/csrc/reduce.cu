@@ -187,6 +187,9 @@ int alpha_softmax(alpha_buf a, alpha_buf out, int64_t rows, int64_t cols, int lo
 int alpha_sumsq_multi(const alpha_buf *tensors, const int64_t *counts, const int32_t *dtypes, int n_tensors,
                       alpha_buf out_scalar) {
   ALPHA_REQUIRE_INIT();
+  double n = 0;
+  for (int t = 0; t < n_tensors; t++) n += (double)counts[t];
+  ProfScope prof(PROF_ELEMENTWISE, n);
   return reduce_table(tensors, counts, dtypes, n_tensors, out_scalar, 0);
 }
 

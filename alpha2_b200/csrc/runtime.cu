@@ -214,6 +214,7 @@ int alpha_shutdown(void) {
   alpha_comm_destroy();
   cudaStreamSynchronize(g_stream);
   tables_clear();
+  rope_tables_clear();
   pool_purge(true);
   cudaStreamDestroy(g_stream);
   g_stream = nullptr;

@@ -131,6 +131,31 @@ def layernorm_case(b: Bench, rows=16384, dim=768, backward=False):
     return {"ms": b.time(lambda: B.layerNormBackward(x, w, g, 1e-5)), "work": 3.0 * rows * dim * 2, "kind": "byte"}
 
 
+def rmsnorm_case(b: Bench, rows=16384, dim=1024, backward=False):
+    B = b.B
+    x, g = b.normal((rows, dim), 1.0), b.normal((rows, dim), 1.0)
+    w = B.ones((dim,))
+    if not backward:
+        return {"ms": b.time(lambda: B.rmsNorm(x, w, 1e-5)), "work": 2.0 * rows * dim * 2, "kind": "byte"}
+    return {"ms": b.time(lambda: B.rmsNormBackward(x, w, g, 1e-5)), "work": 3.0 * rows * dim * 2, "kind": "byte"}
+
+
+def swiglu_case(b: Bench, rows=16384, F=2816, backward=False):
+    B = b.B
+    gate, up, g = (b.normal((rows, F), 1.0) for _ in range(3))
+    if not backward:
+        return {"ms": b.time(lambda: B.siluMul(gate, up)), "work": 3.0 * rows * F * 2, "kind": "byte"}
+    return {"ms": b.time(lambda: B.siluMulBackward(gate, up, g)), "work": 5.0 * rows * F * 2, "kind": "byte"}
+
+
+def rope_case(b: Bench, Bn=8, T=2048, H=16, D=64):
+    """Rotation of the q and k column blocks of a fused [B*T, 3E] activation into a new tensor."""
+    B = b.B
+    E = H * D
+    qkv = b.normal((Bn * T, 3 * E), 1.0)
+    return {"ms": b.time(lambda: B.ropeQkv(qkv, Bn, T, H)), "work": 2.0 * Bn * T * 3 * E * 2, "kind": "byte"}
+
+
 def adamw_case(b: Bench, n=124_000_000):
     B = b.B
     p, m, v = B.zeros((n,)), B.zeros((n,)), B.zeros((n,))
@@ -170,6 +195,14 @@ CASES = {
     "softmax_ce": lambda b: ce_case(b),
     "layernorm_fwd": lambda b: layernorm_case(b),
     "layernorm_bwd": lambda b: layernorm_case(b, backward=True),
+    "rmsnorm_fwd_1024": lambda b: rmsnorm_case(b),
+    "rmsnorm_bwd_1024": lambda b: rmsnorm_case(b, backward=True),
+    "swiglu_fwd": lambda b: swiglu_case(b),
+    "swiglu_bwd": lambda b: swiglu_case(b, backward=True),
+    "rope_qk": lambda b: rope_case(b),
+    "gemm_fwd_gate_350m": lambda b: gemm_case(b, "nt", M, 2816, 1024),
+    "gemm_dx_gate_350m": lambda b: gemm_case(b, "nn", M, 1024, 2816),
+    "gemm_dw_gate_350m": lambda b: gemm_case(b, "tn", 2816, 1024, M, "f32"),
     "adamw": lambda b: adamw_case(b),
     "embedding_bwd": lambda b: embedding_bwd_case(b),
 }

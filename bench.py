@@ -44,16 +44,22 @@ WORKLOADS = {
     # BASELINE configuration 3
     "small-gpt": dict(model=dict(vocabSize=4096, blockSize=256, nLayer=6, nEmbd=384, nHead=6, tied=True,
                                  init="plain"), micro_batch=32, dtype="bf16"),
+    # BASELINE configuration 5: RMSNorm, SwiGLU, RoPE, untied head, 4 accumulated micro-batches per step
+    "gpt-350m": dict(model=dict(vocabSize=32768, blockSize=2048, nLayer=24, nEmbd=1024, nHead=16, tied=False,
+                                ffnActivation="swiglu", ffnDim=2816, norm="rms", rope=True, init="plain"),
+                     micro_batch=8, accum=4, dtype="bf16"),
     # a seconds-long case for checking the script itself
     "tiny": dict(model=dict(vocabSize=256, blockSize=64, nLayer=2, nEmbd=64, nHead=4), micro_batch=4, dtype="bf16"),
 }
 
 
 def flops_per_token(m: dict) -> float:
-    """6*P_mm + 12*L*E*T with P_mm = L*(4E^2 + 2EF) + V*E (model FLOPs, no causal discount)."""
+    """6*P_mm + 12*L*E*T with P_mm = L*(4E^2 + 2EF) + V*E (3EF for SwiGLU; model FLOPs, no causal
+    discount)."""
     E, L, V, T = m["nEmbd"], m["nLayer"], m["vocabSize"], m["blockSize"]
-    F = 4 * E
-    return 6.0 * (L * (4 * E * E + 2 * E * F) + V * E) + 12.0 * L * E * T
+    swiglu = m.get("ffnActivation") == "swiglu"
+    F = m.get("ffnDim") or (4 * E)
+    return 6.0 * (L * (4 * E * E + (3 if swiglu else 2) * E * F) + V * E) + 12.0 * L * E * T
 
 
 def measured_peaks() -> dict:
@@ -211,11 +217,12 @@ def main() -> None:
     mb = args.micro_batch or wl["micro_batch"]
     T = model["blockSize"]
     mc = ModelConfig(**model, compute_dtype=wl["dtype"])
-    tr = Trainer(B, mc, TrainConfig(iters=100000, batchSize=mb, warmupIters=100, seed=42), dp=dp)
+    accum = int(wl.get("accum", 1))
+    tr = Trainer(B, mc, TrainConfig(iters=100000, batchSize=mb, warmupIters=100, seed=42, gradAccumSteps=accum), dp=dp)
 
     # synthetic tokens: Zipf(1.1) over the vocabulary, a different seeded stream per rank
     from alpha2_b200.data import zipf_batches
-    n_batches = args.steps + args.warmup
+    n_batches = (args.steps + args.warmup) * accum
     host_batches = zipf_batches(1000 + rank, n_batches, mb, T, model["vocabSize"])
     tok_bytes = mb * T * 4
     pinned = []
@@ -228,13 +235,17 @@ def main() -> None:
             pair.append(p)
         pinned.append(pair)
 
-    def device_tokens(i):
-        out = []
-        for p in pinned[i]:
-            td = TensorData((mb, T), "i32", _DeviceBuffer(tok_bytes))
-            check(lib.alpha_h2d(td.ptr, p, tok_bytes))
-            out.append(td)
-        return tuple(out)
+    def device_tokens(step):
+        """The ``accum`` micro-batches of one optimizer step, copied from pinned host memory."""
+        micro = []
+        for i in range(step * accum, (step + 1) * accum):
+            out = []
+            for p in pinned[i]:
+                td = TensorData((mb, T), "i32", _DeviceBuffer(tok_bytes))
+                check(lib.alpha_h2d(td.ptr, p, tok_bytes))
+                out.append(td)
+            micro.append(tuple(out))
+        return micro
 
     def barrier():
         B.syncGpu()
@@ -267,7 +278,7 @@ def main() -> None:
 
     # ── warm-up (end to end, so pools, tensor maps and NCCL are all primed) ─────────────
     for i in range(args.warmup):
-        tr.train_step([device_tokens(i)], read_back=True)
+        tr.train_step(device_tokens(i), read_back=True)
     B.checkAsyncError()
 
     sampler = ClockSampler(local)
@@ -281,7 +292,7 @@ def main() -> None:
 
     def region_a():
         for i in range(args.steps):
-            last["r"] = tr.train_step([resident[i]], read_back=False)
+            last["r"] = tr.train_step(resident[i], read_back=False)
     ms_a = timed(region_a)
     launches = B.launch_count() - launches0
     final_loss = last["r"]["lossTensor"].item()
@@ -304,7 +315,7 @@ def main() -> None:
         # so the host never stalls the device (the last one is collected inside the region).
         pending = None
         for i in range(args.steps):
-            out = tr.train_step([device_tokens(args.warmup + i)], read_back=False)
+            out = tr.train_step(device_tokens(args.warmup + i), read_back=False)
             nxt = B.readScalarAsync(out["lossTensor"])
             if pending is not None:
                 losses.append(pending.get())
@@ -320,7 +331,7 @@ def main() -> None:
             dist.destroy_process_group()
         return
 
-    tokens_per_step = mb * T * world
+    tokens_per_step = mb * T * accum * world
     value = tokens_per_step * args.steps / (ms_a / 1e3)
     e2e = tokens_per_step * args.steps / (ms_b / 1e3)
     peaks = measured_peaks()
@@ -338,11 +349,11 @@ def main() -> None:
         "warmup": args.warmup, "ms_per_step": ms_a / args.steps, "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": wl["dtype"], "data": "synthetic",
         "config": {"workload": args.workload, "shape": {k: model[k] for k in ("vocabSize", "nLayer", "nEmbd", "nHead", "blockSize")},
-                   "micro_batch_per_gpu": mb, "tokens_per_step": tokens_per_step, "tied_embeddings": bool(model.get("tied")),
+                   "micro_batch_per_gpu": mb, "grad_accum_steps": accum, "tokens_per_step": tokens_per_step, "tied_embeddings": bool(model.get("tied")),
                    "precision": "bf16 activations and weight shadows, fp32 master weights and AdamW state",
                    "parallelism": f"dp{world}", "l2": "inputs larger than L2 (each step streams >10 GB of activations and weights)",
                    "tokens": "Zipf(s=1.1), seeded per rank"},
-        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * tok_bytes, "d2h_bytes_per_step": 4,
+        "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * tok_bytes * accum, "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_b / args.steps},
         "gpu_launches": launches,
         "clocks": clocks,

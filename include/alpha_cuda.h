@@ -67,13 +67,13 @@ int alpha_check_async_error(void);
  * the algorithmic work the launches declared (flop for GEMM/attention, bytes for the
  * HBM-bound families) and the launch count, and clears the records.
  * Families: 0 tensor-core GEMM, 1 fp32 GEMM, 2 attention fwd, 3 attention bwd,
- * 4 cross-entropy, 5 AdamW, 6 norms, 7 embedding. */
+ * 4 cross-entropy, 5 AdamW, 6 norms, 7 embedding, 8 elementwise / RoPE (work = elements). */
 typedef struct {
   double ms;
   double work;
   int64_t launches;
 } alpha_profile_entry_t;
-enum { ALPHA_PROFILE_CATEGORIES = 8 };
+enum { ALPHA_PROFILE_CATEGORIES = 9 };
 int alpha_profile_enable(int on);
 int alpha_profile_read(alpha_profile_entry_t *out, int n_categories);
 
@@ -260,6 +260,11 @@ int alpha_flash_attn_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alp
  * inverse != 0 applies the transposed rotation (the backward). In place when x == out. */
 int alpha_rope(alpha_buf x, alpha_buf out, int64_t batch, int64_t T, int64_t heads, int64_t D,
                int64_t ld, float theta, int inverse, int dtype);
+/* The same rotation on the q and k column blocks of a fused activation qkv [B*T, 3*heads*D],
+ * written with the v block copied alongside to out (same layout; out may equal qkv), one read
+ * and one write of every row. */
+int alpha_rope_qkv(alpha_buf qkv, alpha_buf out, int64_t batch, int64_t T, int64_t heads, int64_t D,
+                   float theta, int inverse, int dtype);
 
 /* ── loss ────────────────────────────────────────────────────────────────────────────
  * Backend.crossEntropy (interfaces.ts:74; cpu_ref.ts:543-563) and crossEntropyBackward

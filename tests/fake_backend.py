@@ -106,10 +106,19 @@ class NumpyBackend:
     def matmul(self, a, b): return self._o(a.data.astype(f64) @ b.data.astype(f64))
     def matmulTransposed(self, a, b): return self._o(a.data.astype(f64) @ b.data.astype(f64).T)
 
-    def matmulTransposedA(self, a, b):
+    def matmulTransposedA(self, a, b, into=None):
         A = a.data.astype(f64).reshape(-1, a.shape[-1])
         Bm = b.data.astype(f64).reshape(-1, b.shape[-1])
+        if into is not None:
+            self.ops += 1
+            into._host = (into.data.astype(f64) + A.T @ Bm).astype(f32)
+            return into
         return self._o(A.T @ Bm)
+
+    def matmulInto(self, a, b, into):
+        self.ops += 1
+        into._host = (into.data.astype(f64) + (a.data.astype(f64) @ b.data.astype(f64)).reshape(into.shape)).astype(f32)
+        return into
 
     def matmulTransposedGelu(self, a, b):
         pre = a.data.astype(f64) @ b.data.astype(f64).T
@@ -197,6 +206,14 @@ class NumpyBackend:
         blk[..., :half], blk[..., half:] = p * c - q * s, q * c + p * s
         a[:, :, col_offset:col_offset + heads * D] = blk.reshape(batch, Tn, heads * D)
         x._host = a.reshape(x.shape).astype(f32)
+
+    def ropeQkv(self, qkv, batch, Tn, heads, theta=10000.0, inverse=False):
+        E3 = qkv.shape[-1]
+        E = E3 // 3
+        out = self.clone(qkv)
+        self.rope(out, batch, Tn, heads, E // heads, E3, 0, theta, inverse)
+        self.rope(out, batch, Tn, heads, E // heads, E3, E, theta, inverse)
+        return out
 
     def crossEntropy(self, logits, targets):
         x = logits.data.astype(f64)

@@ -193,3 +193,30 @@ def test_train_steps_at_full_size_are_reproducible(B):
     assert runs[0][0] == runs[1][0] and runs[0][1] == runs[1][1] and np.array_equal(runs[0][2], runs[1][2])
     # N(0, 0.02) weights with a tied head: the first loss sits a little above ln V = 10.82
     assert abs(runs[0][0][0] - math.log(V)) < 0.5 and all(math.isfinite(v) for v in runs[0][0] + runs[0][1])
+
+
+def test_train_steps_at_the_350m_shape_are_reproducible(B):
+    """The 350M configuration (RMSNorm, SwiGLU 2816, RoPE, untied head, context 2048, micro-batch
+    8 with accumulated micro-steps): two optimizer steps, twice from the same seed, give
+    identical bits; the first loss sits at ln V and every quantity stays finite."""
+    from alpha2_b200.data import zipf_batches
+    from alpha2_b200.gpt import ModelConfig
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    v, t, mb, accum = 32768, 2048, 8, 2
+    mc = ModelConfig(vocabSize=v, blockSize=t, nLayer=24, nEmbd=1024, nHead=16, tied=False, ffnActivation="swiglu",
+                     ffnDim=2816, norm="rms", rope=True, init="plain", compute_dtype="bf16")
+    batches = zipf_batches(78, 2 * accum, mb, t, v)
+    runs = []
+    for _ in range(2):
+        tr = Trainer(B, mc, TrainConfig(iters=1000, batchSize=mb, warmupIters=100, seed=42, gradAccumSteps=accum))
+        res = []
+        for s in range(2):
+            micro = [(B.upload(a, "i32"), B.upload(g, "i32")) for a, g in batches[s * accum:(s + 1) * accum]]
+            res.append(tr.train_step(micro))
+        runs.append(([x["loss"] for x in res], [x["gradNorm"] for x in res],
+                     np.array(tr.params["layer.11.attn.wqkv"].data.data[:4, :8])))
+        del tr
+        B.purgeBufferPools()
+    assert runs[0][0] == runs[1][0] and runs[0][1] == runs[1][1] and np.array_equal(runs[0][2], runs[1][2])
+    assert abs(runs[0][0][0] - math.log(v)) < 0.5 and all(math.isfinite(x) for x in runs[0][0] + runs[0][1])
+    assert runs[0][1][0] > 0

@@ -444,12 +444,35 @@ def test_gemm_bf16_epilogues_and_accumulate(B):
     B.checkAsyncError()
 
 
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+@pytest.mark.parametrize("shape", [(300, 520, 192), (2048, 512, 768)])
+def test_gradients_added_inside_the_gemm(B, dtype, shape):
+    """matmulInto (into += G @ W, output aliasing the addend) and matmulTransposedA(into=)."""
+    M, N, K = shape
+    r = rng(12)
+    g, w, x, acc = (r.standard_normal(s).astype(f32) * c for s, c in
+                    (((M, N), 0.1), ((N, K), 0.1), ((M, K), 0.5), ((M, K), 1.0)))
+    if dtype == "bf16":
+        g, w, x, acc = (bf16_round(t) for t in (g, w, x, acc))
+    G, W, X, ACC = (B.upload(t, dtype) for t in (g, w, x, acc))
+    out = B.matmulInto(G, W, ACC)
+    assert out is ACC
+    assert rel_err(ACC.data, acc + g.astype(np.float64) @ w) < (1e-5 if dtype == "f32" else 1e-2)
+    dw0 = r.standard_normal((N, K)).astype(f32)
+    DW = B.upload(dw0, "f32")
+    assert B.matmulTransposedA(G, X, into=DW) is DW
+    assert rel_err(DW.data, dw0 + g.astype(np.float64).T @ x) < 1e-5
+    B.checkAsyncError()
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("cfg", [(3, 64, 16, 30.0), (2, 100, 64, 30.0), (2, 256, 64, 0.0), (1, 130, 32, 2.0),
                                  (1, 192, 128, 30.0),
                                  (2, 640, 64, 30.0),    # 5 key/query blocks: the 4-stage rings wrap
                                  (1, 300, 64, 2.0),     # tight cap: tanh arguments beyond the polynomial range
-                                 (1, 1024, 64, 0.0)])
+                                 (1, 1024, 64, 0.0),
+                                 (1, 2048, 64, 30.0),   # the 350M configuration's context: 16 blocks per item
+                                 (1, 1990, 64, 0.0)])   # ragged, long, running-maximum path
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
 def test_flash_attention_contract(B, cfg, dtype):
     """Backend.flashAttention / flashAttentionBackward on [B*H, T, D] (interfaces.ts:127-135)."""
@@ -518,6 +541,31 @@ def test_rope_matches_oracle_and_inverts(B):
     assert np.all(got[:, :E] == 0) and np.all(got[:, 2 * E:] == 0)
     B.rope(X, Bn, T, H, D, 3 * E, E, inverse=True)
     assert rel_err(X.data[:, E:2 * E], x.reshape(Bn * T, E)) < 3e-6
+
+
+@pytest.mark.parametrize("geom", [(2, 33, 3, 16), (1, 2048, 2, 64), (2, 40, 2, 6)])
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_rope_qkv_matches_oracle_and_inverts(B, geom, dtype):
+    """q and k blocks of a fused [B*T, 3E] activation rotated, v passed through, out of place;
+    head dim 6 takes the scalar kernel (pairs are not a multiple of 16 bytes)."""
+    from oracle import autograd as oag
+    from oracle.autograd import Ctx, Tape, Variable
+    Bn, T, H, D = geom
+    E = H * D
+    qkv = rng(32).standard_normal((Bn * T, 3 * E)).astype(f32)
+    if dtype == "bf16":
+        qkv = bf16_round(qkv)
+    ref = qkv.copy()
+    for blk in range(2):
+        xb = np.ascontiguousarray(qkv[:, blk * E:(blk + 1) * E]).reshape(Bn, T, E)
+        ref[:, blk * E:(blk + 1) * E] = oag.rope(Ctx(Tape(), O), Variable(xb, True), H).data.reshape(Bn * T, E)
+    X = B.upload(qkv, dtype)
+    Y = B.ropeQkv(X, Bn, T, H)
+    tol = 3e-6 if dtype == "f32" else 6e-3
+    assert rel_err(Y.data, ref) < tol
+    assert np.array_equal(Y.data[:, 2 * E:], qkv[:, 2 * E:]) and np.array_equal(X.data, qkv)
+    back = B.ropeQkv(Y, Bn, T, H, inverse=True)
+    assert rel_err(back.data, qkv) < 2 * tol
 
 
 def test_allocator_reuses_blocks(B):
