@@ -105,6 +105,7 @@ SIGNATURES = {
     "alpha_flash_attn_fwd": [_B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_flash_attn_bwd": [_B, _B, _B, _B, _B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_rope": [_B, _B, _L, _L, _L, _L, _L, _F, _I, _I],
+    "alpha_set_launch_overlap": [_I],
     "alpha_rope_qkv": [_B, _B, _L, _L, _L, _L, _F, _I, _I],
     "alpha_cross_entropy_fwd": [_B, _B, _B, _L, _L, _L, _I],
     "alpha_cross_entropy_fwd_noalloc": [_B, _B, _B, _L, _L, _L, _I],

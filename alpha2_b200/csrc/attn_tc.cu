@@ -91,6 +91,8 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_trigger();
+  grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS = tmem_base, tO = tmem_base + 128;
 
@@ -319,6 +321,8 @@ __global__ void __launch_bounds__(256) attn_tc_delta_kernel(const __nv_bfloat16 
                                                             int64_t rows) {
   const int sub = threadIdx.x & 7;
   const int64_t stride = (int64_t)gridDim.x * 32;
+  grid_dependency_trigger();
+  grid_dependency_wait();
   for (int64_t r0 = (int64_t)blockIdx.x * 32; r0 < rows; r0 += stride) {  // warp-uniform trip count
     const int64_t r = r0 + (threadIdx.x >> 3);
     float s = 0.f;
@@ -549,6 +553,8 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_trigger();
+  grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdV = tmem_base + 384, tdK = tmem_base + 448;
 
@@ -812,6 +818,8 @@ attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_c
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_trigger();
+  grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdQ = tmem_base + 384;
 
@@ -1133,6 +1141,8 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
+  grid_dependency_trigger();
+  grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tO = tmem_base + 256;
 
@@ -1428,12 +1438,12 @@ int attn_tc_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf ls
     const int BH = (int)(p->batch * p->heads);
     const int n_items = (int)((p->T + 127) / 128) * BH;
     const int grid2 = n_items < g_sm_count ? n_items : g_sm_count;
-    attn_tc_fwd2_kernel<<<grid2, AF2_THREADS, AF2_DYN, g_stream>>>(tq, tk, tv, a, n_items, BH);
+    ALPHA_CUDA(launch_overlapped(OVL_ATTN_FWD, attn_tc_fwd2_kernel, dim3(grid2), dim3(AF2_THREADS), AF2_DYN, tq, tk, tv, a, n_items, BH));
     ALPHA_LAUNCHED();
     return 0;
   }
   dim3 grid((unsigned)((p->T + 127) / 128), (unsigned)(p->batch * p->heads));
-  attn_tc_fwd_kernel<<<grid, AT_THREADS, AF_DYN, g_stream>>>(tq, tk, tv, a);
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_FWD, attn_tc_fwd_kernel, grid, dim3(AT_THREADS), AF_DYN, tq, tk, tv, a));
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -1450,9 +1460,9 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   const int64_t rows = p->batch * p->heads * p->T;
   void *delta = nullptr;
   if (pool_alloc((size_t)rows * sizeof(float), &delta)) return 1;
-  attn_tc_delta_kernel<<<grid_for(rows, 32, 16), 256, 0, g_stream>>>(ptr<__nv_bfloat16>(o), ptr<__nv_bfloat16>(d_o),
-                                                                    (float *)delta, p->o_sb, p->o_sh, p->o_st,
-                                                                    (int)p->heads, (int)p->T, rows);
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_delta_kernel, dim3(grid_for(rows, 32, 16)), dim3(256), 0,
+                               (const __nv_bfloat16 *)ptr<__nv_bfloat16>(o), (const __nv_bfloat16 *)ptr<__nv_bfloat16>(d_o),
+                               (float *)delta, p->o_sb, p->o_sh, p->o_st, (int)p->heads, (int)p->T, rows));
   g_launches++;
   AttnBwdArgs a;
   memset(&a, 0, sizeof(a));
@@ -1471,9 +1481,9 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   const int BH = (int)(p->batch * p->heads);
   const int n_items = (int)((p->T + 127) / 128) * BH;
   const int grid = n_items < g_sm_count ? n_items : g_sm_count;
-  attn_tc_bwd_dkv_kernel<<<grid, ABP_THREADS, AK_DYN, g_stream>>>(tq, tk, tv, tdo, a, n_items, BH);
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_dkv_kernel, dim3(grid), dim3(ABP_THREADS), AK_DYN, tq, tk, tv, tdo, a, n_items, BH));
   g_launches++;
-  attn_tc_bwd_dq_kernel<<<grid, ABP_THREADS, AQ_DYN, g_stream>>>(tq, tk, tv, tdo, a, n_items, BH);
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_dq_kernel, dim3(grid), dim3(ABP_THREADS), AQ_DYN, tq, tk, tv, tdo, a, n_items, BH));
   pool_free(delta);
   ALPHA_LAUNCHED();
   return 0;

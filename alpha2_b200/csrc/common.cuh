@@ -70,6 +70,36 @@ struct ProfScope {
     }                                                                                       \
   } while (0)
 
+// Launch that may overlap the tail of its predecessor in the stream (programmatic dependent
+// launch): the kernel's blocks can become resident and run their set-up (barriers, tensor
+// memory, shared-memory tables) while the previous kernel drains.  Such a kernel executes
+// grid_dependency_wait() before its first access to global memory, which returns once the
+// previous kernel has finished and its writes are visible, and grid_dependency_trigger()
+// as early as it likes to give its own successor the same head start.
+extern int g_overlap_launches;  // bit mask of kernel families (OVL_*) launched this way
+enum { OVL_GEMM = 1, OVL_SPLITK = 2, OVL_ATTN_FWD = 4, OVL_ATTN_BWD = 8, OVL_NORM_FWD = 16, OVL_NORM_BWD = 32 };
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
+                                     Args &&...args) {
+  cudaLaunchConfig_t cfg;
+  memset(&cfg, 0, sizeof(cfg));
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = g_stream;
+  cudaLaunchAttribute at;
+  memset(&at, 0, sizeof(at));
+  at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at.val.programmaticStreamSerializationAllowed = (g_overlap_launches & family) ? 1 : 0;
+  cfg.attrs = &at;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 template <typename T>
 __host__ __device__ inline T *ptr(alpha_buf b) {
   return reinterpret_cast<T *>(static_cast<uintptr_t>(b));

@@ -347,6 +347,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
   __syncthreads();
   if (PAIR) cluster_sync_all();  // the peer's barriers exist before anything signals them
   tc_fence_after();
+  // everything above touched only this SM; global memory is first read or written below
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const uint32_t tmem_base = *tmem_slot;
   // The pair's MMA writes both CTAs' tensor memory at one address, so both allocations must
   // start at the same column; each CTA takes all 512 columns of its SM, which puts them at 0.
@@ -557,6 +560,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float *__restr
                                                             int64_t ldc, int splits, int accumulate, int vec4) {
   const int64_t total = M * N;
   const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+  grid_dependency_trigger();
+  grid_dependency_wait();  // the slabs come from the GEMM launched just before
   if (vec4) {
     const int64_t n4 = total / 4;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
@@ -641,7 +646,7 @@ static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CU
     ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     attr = true;
   }
-  gemm_tc_kernel<BN, A_MN, B_MN><<<grid, GEMM_THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
+  ALPHA_CUDA(launch_overlapped(OVL_GEMM, gemm_tc_kernel<BN, A_MN, B_MN>, dim3(grid), dim3(GEMM_THREADS), L::DYN, ta, tb, tc_, tx, g));
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -673,7 +678,8 @@ static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, con
     max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
   }
   const int n = pairs < max_pairs ? pairs : max_pairs;
-  gemm_tc_pair_kernel<A_MN, B_MN, WIDE><<<2 * n, L::THREADS, L::DYN, g_stream>>>(ta, tb, tc_, tx, g);
+  ALPHA_CUDA(launch_overlapped(OVL_GEMM, gemm_tc_pair_kernel<A_MN, B_MN, WIDE>, dim3(2 * n), dim3(L::THREADS), L::DYN, ta, tb,
+                               tc_, tx, g));
   ALPHA_LAUNCHED();
   return 0;
 }
@@ -774,12 +780,14 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   if (rc == 0 && splits > 1) {
     const int vec4 = (N % 4 == 0) ? 1 : 0;   // ws slabs are 512-byte aligned and dense
     const int rgrid = grid_for(M * N / (vec4 ? 4 : 1) + 1, 256, 8);
+    cudaError_t e;
     if (out_dtype == ALPHA_F32)
-      splitk_reduce_kernel<float><<<rgrid, 256, 0, g_stream>>>((const float *)ws, ptr<float>(C), M, N, ldc, splits,
-                                                               accumulate, vec4);
+      e = launch_overlapped(OVL_SPLITK, splitk_reduce_kernel<float>, dim3(rgrid), dim3(256), 0, (const float *)ws, ptr<float>(C), M,
+                            N, ldc, splits, accumulate, vec4);
     else
-      splitk_reduce_kernel<__nv_bfloat16><<<rgrid, 256, 0, g_stream>>>((const float *)ws, ptr<__nv_bfloat16>(C), M, N,
-                                                                       ldc, splits, accumulate, vec4);
+      e = launch_overlapped(OVL_SPLITK, splitk_reduce_kernel<__nv_bfloat16>, dim3(rgrid), dim3(256), 0, (const float *)ws,
+                            ptr<__nv_bfloat16>(C), M, N, ldc, splits, accumulate, vec4);
+    if (e != cudaSuccess) rc = set_error("split-K reduce launch -> %s", cudaGetErrorString(e));
     g_launches++;
   }
   if (ws) pool_free(ws);

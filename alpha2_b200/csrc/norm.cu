@@ -212,6 +212,8 @@ __global__ void __launch_bounds__(32 * LN_RED_GROUPS) ln_reduce_partials(const f
                                                                          float *db, int n_part, int dim,
                                                                          int accumulate) {
   __shared__ float sm[LN_RED_GROUPS][33];
+  grid_dependency_trigger();
+  grid_dependency_wait();
   const int c = blockIdx.x * 32 + threadIdx.x;
   float a0 = 0.f, a1 = 0.f, a2 = 0.f, a3 = 0.f;
   if (c < 2 * dim) {
@@ -569,6 +571,8 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
   volatile uint32_t *abort_flag = (volatile uint32_t *)(lr_smem + LR_STAGES * stage_bytes + 16 * LR_STAGES);
   float *w_sm = reinterpret_cast<float *>(lr_smem + LR_STAGES * stage_bytes + 64);  // the weight row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dependency_trigger();
+  grid_dependency_wait();
   for (int c = threadIdx.x; c < dim; c += LR_THREADS) w_sm[c] = w[c];
   if (threadIdx.x == 0) {
     for (int s = 0; s < LR_STAGES; s++) {
@@ -622,6 +626,9 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
         t.get(&xv[v * V]);
         u.get(&gv[v * V]);
       }
+      // The rows were read through the generic proxy and the slot's next contents arrive through
+      // the async proxy (bulk copy): without this fence the refill may overtake the reads.
+      fence_proxy_async();
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the stage may be refilled
       if (r >= rows) continue;                   // warp-uniform (a short last group)
@@ -737,6 +744,8 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
   float *w_sm = reinterpret_cast<float *>(lr_smem + LRF_STAGES * stage_bytes + 128);
   float *b_sm = w_sm + dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  grid_dependency_trigger();
+  grid_dependency_wait();
   for (int c = threadIdx.x; c < dim; c += LR_THREADS) {
     w_sm[c] = w[c];
     b_sm[c] = RMS ? 0.f : b[c];
@@ -780,6 +789,7 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
         t.get(&xv[v * V]);
       }
+      fence_proxy_async();  // generic-proxy reads before the async-proxy refill of the slot
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the slot can be refilled
       if (r >= rows) continue;
@@ -837,8 +847,10 @@ static int launch_fwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y
     ALPHA_CUDA(cudaFuncSetAttribute(ln_fwd_ring<T, NV, RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
     attr = true;
   }
-  ln_fwd_ring<T, NV, RMS><<<grid_for(rows, LR_WARPS, 4), LR_THREADS, smem, g_stream>>>(
-      ptr<T>(x), ptr<float>(w), RMS ? nullptr : ptr<float>(b), ptr<T>(y), rows, (int)dim, eps, tc::tc_error_word());
+  ALPHA_CUDA(launch_overlapped(OVL_NORM_FWD, ln_fwd_ring<T, NV, RMS>, dim3(grid_for(rows, LR_WARPS, 4)), dim3(LR_THREADS), smem,
+                               (const T *)ptr<T>(x), (const float *)ptr<float>(w),
+                               (const float *)(RMS ? nullptr : ptr<float>(b)), ptr<T>(y), rows, (int)dim, eps,
+                               tc::tc_error_word()));
   return 0;
 }
 template <typename T, bool RMS>
@@ -999,9 +1011,10 @@ static int launch_bwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf d
                                     200 * 1024));
     attr = true;
   }
-  ln_bwd_ring<T, NV, RMS, HAS_ADD><<<grid, LR_THREADS, smem, g_stream>>>(
-      ptr<T>(x), ptr<float>(w), ptr<T>(g), HAS_ADD ? ptr<T>(dx_add) : nullptr, ptr<T>(dx), part, rows, (int)dim, eps,
-      tc::tc_error_word());
+  ALPHA_CUDA(launch_overlapped(OVL_NORM_BWD, ln_bwd_ring<T, NV, RMS, HAS_ADD>, dim3(grid), dim3(LR_THREADS), smem,
+                               (const T *)ptr<T>(x), (const float *)ptr<float>(w), (const T *)ptr<T>(g),
+                               (const T *)(HAS_ADD ? ptr<T>(dx_add) : nullptr), ptr<T>(dx), part, rows, (int)dim, eps,
+                               tc::tc_error_word()));
   return 0;
 }
 template <typename T, bool RMS, bool HAS_ADD>
@@ -1044,9 +1057,11 @@ static int norm_bwd(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alp
                     : launch_bwd_ring<T, RMS, false>(nv, x, w, g, dx_add, dx, (float *)part, rows, dim, eps, grid);
     if (rc) { pool_free(part); return 1; }
     g_launches++;
-    ln_reduce_partials<<<(unsigned)((2 * dim + 31) / 32), dim3(32, LN_RED_GROUPS), 0, g_stream>>>(
-        (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : nullptr, grid, (int)dim, accumulate);
+    cudaError_t e = launch_overlapped(OVL_NORM_BWD, ln_reduce_partials, dim3((unsigned)((2 * dim + 31) / 32)), dim3(32, LN_RED_GROUPS), 0,
+                                      (const float *)part, ptr<float>(dw), db ? ptr<float>(db) : (float *)nullptr, grid,
+                                      (int)dim, accumulate);
     pool_free(part);
+    if (e != cudaSuccess) return set_error("layernorm partial reduce launch -> %s", cudaGetErrorString(e));
   } else if (fast && dim / V <= 2 * LN_CTA && (w & 15) == 0) {
     const int nvec = (int)(dim / V);
     const int grid = nvec <= LN_CTA ? grid_for(rows, 2, 5) : grid_for(rows, 1, 4);

@@ -23,6 +23,7 @@ int g_device = -1;
 int g_sm_count = 148;
 bool g_inited = false;
 unsigned long long g_launches = 0;
+int g_overlap_launches = ~0;
 
 static thread_local char t_err[1024] = "";
 
@@ -220,6 +221,11 @@ int alpha_shutdown(void) {
   g_stream = nullptr;
   g_inited = false;
   g_device = -1;
+  return 0;
+}
+
+int alpha_set_launch_overlap(int families) {
+  g_overlap_launches = families;
   return 0;
 }
 

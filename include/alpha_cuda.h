@@ -61,6 +61,14 @@ int alpha_stream_handle(uint64_t *out);
  * invalid.  Waits inside the kernels never spin without limit. */
 int alpha_check_async_error(void);
 
+/* The tensor-core GEMM, attention and norm kernels are launched so that their blocks may
+ * become resident and set themselves up while the previous kernel of the stream drains
+ * (programmatic dependent launch; each waits for its predecessor before it touches global
+ * memory).  families is a bit mask: 1 GEMM, 2 split-K reduce, 4 attention forward,
+ * 8 attention backward, 16 norm forward, 32 norm backward; -1 = all (the default),
+ * 0 = fully serialised launches (for timing comparisons and fault isolation). */
+int alpha_set_launch_overlap(int families);
+
 /* Per-kernel-family device timing (helios_vk.c:3448 gpuTime; backend.ts:5159-5204 profileOp).
  * While enabled, launches of the heavy kernel families are bracketed by events on the
  * compute stream; alpha_profile_read waits, then returns per family the summed device time,
