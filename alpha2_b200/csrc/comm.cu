@@ -103,6 +103,7 @@ int alpha_comm_allreduce_sum(alpha_buf buf, int64_t n, int dtype) {
   ALPHA_CHECK(dtype == ALPHA_F32 || dtype == ALPHA_BF16, "alpha_comm_allreduce_sum: unsupported dtype %d", dtype);
   ALPHA_CUDA(cudaEventRecord(g_ev_ready, g_stream));
   ALPHA_CUDA(cudaStreamWaitEvent(g_comm_stream, g_ev_ready, 0));
+  g_overlap_hold = 2;  // give the collective's blocks an ordinary kernel boundary to start at
   ALPHA_NCCL(g_nccl.AllReduce(ptr<void>(buf), ptr<void>(buf), (size_t)n, dtype == ALPHA_F32 ? ncclFloat32 : ncclBfloat16,
                               ncclSum, g_comm, g_comm_stream));
   return 0;
@@ -119,6 +120,7 @@ int alpha_comm_allreduce_sum_bucket(const alpha_buf *bufs, const int64_t *counts
   ALPHA_CHECK(dtype == ALPHA_F32 || dtype == ALPHA_BF16, "alpha_comm_allreduce_sum_bucket: unsupported dtype %d", dtype);
   ALPHA_CUDA(cudaEventRecord(g_ev_ready, g_stream));
   ALPHA_CUDA(cudaStreamWaitEvent(g_comm_stream, g_ev_ready, 0));
+  g_overlap_hold = 2;  // give the collective's blocks an ordinary kernel boundary to start at
   ALPHA_NCCL(g_nccl.GroupStart());
   for (int i = 0; i < n_bufs; i++) {
     if (counts[i] == 0) continue;

@@ -77,6 +77,9 @@ struct ProfScope {
 // previous kernel has finished and its writes are visible, and grid_dependency_trigger()
 // as early as it likes to give its own successor the same head start.
 extern int g_overlap_launches;  // bit mask of kernel families (OVL_*) launched this way
+// Number of coming launches to serialise fully: a collective that has just been queued on the
+// side stream needs one ordinary kernel boundary, with idle SMs, to get its blocks resident.
+extern int g_overlap_hold;
 enum { OVL_GEMM = 1, OVL_SPLITK = 2, OVL_ATTN_FWD = 4, OVL_ATTN_BWD = 8, OVL_NORM_FWD = 16, OVL_NORM_BWD = 32 };
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_overlapped(int family, void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
@@ -90,7 +93,8 @@ inline cudaError_t launch_overlapped(int family, void (*kernel)(KArgs...), dim3 
   cudaLaunchAttribute at;
   memset(&at, 0, sizeof(at));
   at.id = cudaLaunchAttributeProgrammaticStreamSerialization;
-  at.val.programmaticStreamSerializationAllowed = (g_overlap_launches & family) ? 1 : 0;
+  at.val.programmaticStreamSerializationAllowed = ((g_overlap_launches & family) && g_overlap_hold == 0) ? 1 : 0;
+  if (g_overlap_hold > 0) g_overlap_hold--;
   cfg.attrs = &at;
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);

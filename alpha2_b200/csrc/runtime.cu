@@ -24,6 +24,7 @@ int g_sm_count = 148;
 bool g_inited = false;
 unsigned long long g_launches = 0;
 int g_overlap_launches = ~0;
+int g_overlap_hold = 0;
 
 static thread_local char t_err[1024] = "";
 
