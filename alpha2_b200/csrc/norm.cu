@@ -546,6 +546,14 @@ __global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, co
 // are warp shuffles only (no block barrier in the loop), dw / db sums stay in registers
 // and are combined across the four warps once at the end, in fixed order.
 constexpr int LR_WARPS = 4, LR_STAGES = 3, LR_THREADS = (LR_WARPS + 1) * 32;
+// Position of per-column constant c (weight, bias) in shared memory: a lane owns V consecutive
+// columns per vector and reads them as float4s, so the float4s of one (vector, quarter) are laid
+// side by side across the 32 lanes (16-byte lane stride: no bank conflicts) instead of V*4 bytes apart.
+template <int V>
+__device__ __forceinline__ int lr_const_pos(int c) {
+  const int j = c % V, lane = (c / V) & 31, v = c / (32 * V);
+  return ((v * (V / 4) + j / 4) * 32 + lane) * 4 + (j & 3);
+}
 
 // 32 elements per lane need more registers than three resident blocks leave (and their ring
 // takes a third of the shared memory anyway): two blocks per SM there.
@@ -573,7 +581,7 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   grid_dependency_trigger();
   grid_dependency_wait();
-  for (int c = threadIdx.x; c < dim; c += LR_THREADS) w_sm[c] = w[c];
+  for (int c = threadIdx.x; c < dim; c += LR_THREADS) w_sm[lr_const_pos<V>(c)] = w[c];
   if (threadIdx.x == 0) {
     for (int s = 0; s < LR_STAGES; s++) {
       mbar_init(full_bar(s), 1);
@@ -655,7 +663,7 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
       for (int v = 0; v < NV; v++)
 #pragma unroll
         for (int j4 = 0; j4 < V; j4 += 4) {
-          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + (v * 32 + lane) * V + j4);
+          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + ((v * (V / 4) + j4 / 4) * 32 + lane) * 4);
           const float wq[4] = {w4.x, w4.y, w4.z, w4.w};
 #pragma unroll
           for (int q = 0; q < 4; q++) {
@@ -747,8 +755,8 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
   grid_dependency_trigger();
   grid_dependency_wait();
   for (int c = threadIdx.x; c < dim; c += LR_THREADS) {
-    w_sm[c] = w[c];
-    b_sm[c] = RMS ? 0.f : b[c];
+    w_sm[lr_const_pos<V>(c)] = w[c];
+    b_sm[lr_const_pos<V>(c)] = RMS ? 0.f : b[c];
   }
   if (threadIdx.x == 0) {
     for (int s = 0; s < LRF_STAGES; s++) {
@@ -817,9 +825,9 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
         float o[V];
 #pragma unroll
         for (int j4 = 0; j4 < V; j4 += 4) {
-          const int c = (v * 32 + lane) * V + j4;
-          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + c);
-          const float4 b4 = *reinterpret_cast<const float4 *>(b_sm + c);
+          const int cp = ((v * (V / 4) + j4 / 4) * 32 + lane) * 4;
+          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + cp);
+          const float4 b4 = *reinterpret_cast<const float4 *>(b_sm + cp);
           o[j4] = (xv[v * V + j4] - mean) * rstd * w4.x + b4.x;
           o[j4 + 1] = (xv[v * V + j4 + 1] - mean) * rstd * w4.y + b4.y;
           o[j4 + 2] = (xv[v * V + j4 + 2] - mean) * rstd * w4.z + b4.z;
