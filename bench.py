@@ -12,7 +12,9 @@ Keys: ``value`` — whole-job tokens/s with every step's tokens already resident
 device-timed with CUDA events on the library's stream, max over ranks; ``e2e`` — the same
 steps driven through the public API with host buffers: per step the tokens/targets are
 copied from pinned host memory and the loss is read back; ``roofline`` — the dominant
-kernel family (tensor-core GEMM) timed with events inside the timed region; ``cpu_baseline``
+kernel family (tensor-core GEMM) timed with events around its launches in a third pass over
+the same steps (events between kernels would stop the launch overlap of the two timed regions,
+which run first, back to back); ``cpu_baseline``
 — the CPU oracle (a port of the reference's cpu_ref path) timed on the host cores on a
 bounded sample; ``clocks`` — nvidia-smi samples taken during the timed regions.
 
@@ -297,15 +299,6 @@ def main() -> None:
     launches = B.launch_count() - launches0
     final_loss = last["r"]["lossTensor"].item()
 
-    # ── region P: the same steps once more with per-kernel-family event timing switched on
-    # (kept out of region A: an event record between two kernels stops their overlap) ────
-    check(lib.alpha_profile_enable(1))
-    ms_p = timed(region_a)
-    check(lib.alpha_profile_enable(0))
-    prof = (L.ProfileEntry * len(L.PROFILE_CATEGORIES))()
-    check(lib.alpha_profile_read(prof, len(L.PROFILE_CATEGORIES)))
-    del resident
-
     # ── region B: end to end through the public API with host buffers ───────────────────
     losses = []
 
@@ -323,6 +316,16 @@ def main() -> None:
         losses.append(pending.get())
     ms_b = timed(region_b)
     clocks = sampler.stop() if rank == 0 else {}
+    # ── region P: the steps of region A once more with per-kernel-family event timing switched
+    # on (kept out of regions A and B: an event record between two kernels stops their overlap;
+    # run last, after the clock sampling has stopped) ────
+    check(lib.alpha_profile_enable(1))
+    ms_p = timed(region_a)
+    check(lib.alpha_profile_enable(0))
+    prof = (L.ProfileEntry * len(L.PROFILE_CATEGORIES))()
+    check(lib.alpha_profile_read(prof, len(L.PROFILE_CATEGORIES)))
+    del resident
+
     B.checkAsyncError()
 
     if rank != 0:
