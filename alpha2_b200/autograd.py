@@ -640,6 +640,17 @@ def checkpoint(ctx, fn, input: Variable) -> Variable:
     tmp = Ctx(Tape(), B, ctx.dropoutRng, None)
     tmp_out = fn(tmp, input)
     out_data = tmp_out.data
+    # The trainable parameters the segment reads.  They are listed after the real input on
+    # the outer entry so that whoever watches the tape (the data-parallel hand-off counts the
+    # entries that feed each parameter) sees that this entry's backward finalises them; the
+    # closure returns one gradient only, so the tape itself never touches the extra inputs.
+    captured: list = []
+    seen = set()
+    for e in tmp.tape.entries:
+        for v in e.inputs:
+            if isinstance(v, Param) and v.id not in seen:
+                seen.add(v.id)
+                captured.append(v)
     tmp.tape.clear(ctx.release, tmp_out)                      # intermediates go, the output stays
 
     def bw(g, backend, release, needs):
@@ -651,4 +662,4 @@ def checkpoint(ctx, fn, input: Variable) -> Variable:
         re_input.grad = None
         re.tape.clear(release)
         return [grad if grad is not None else backend.zeros(input.data.shape, input.data.dtype)]
-    return _record(ctx, out_data, [input], bw)
+    return _record(ctx, out_data, [input] + captured, bw)

@@ -272,6 +272,33 @@ class CudaBackend:
             t._host = None
         return t
 
+    def uploadAsync(self, array: np.ndarray, dtype: str = "i32") -> TensorData:
+        """Enqueue a copy of ``array`` (page-locked memory from ``pinned_array``, i32 or f32)
+        into a new device tensor and return at once.  The caller must not write ``array``
+        again before an event recorded after this call has completed; the tensor keeps no
+        host copy."""
+        if dtype == "bf16":
+            raise AlphaCudaError("uploadAsync: i32 or f32 only")
+        if not array.flags["C_CONTIGUOUS"] or array.dtype != _NP[dtype]:
+            raise AlphaCudaError("uploadAsync: contiguous array of the tensor's own type required")
+        t = self._new(array.shape, dtype)
+        check(self.lib.alpha_h2d(t.ptr, array.ctypes.data, array.nbytes))
+        return t
+
+    def eventCreate(self) -> "C.c_uint64":
+        ev = C.c_uint64()
+        check(self.lib.alpha_event_create(C.byref(ev)))
+        return ev
+
+    def eventRecord(self, ev) -> None:
+        check(self.lib.alpha_event_record(ev.value))
+
+    def eventSync(self, ev) -> None:
+        check(self.lib.alpha_event_sync(ev.value))
+
+    def eventDestroy(self, ev) -> None:
+        check(self.lib.alpha_event_destroy(ev.value))
+
     def pinned_array(self, shape, np_dtype):
         """A numpy array over page-locked host memory (uploads from it are asynchronous) and
         the handle that keeps the allocation alive; free it with ``free_pinned``."""

@@ -339,10 +339,10 @@ template <int D> constexpr size_t dq_smem() {
 
 template <typename T, int D>
 static int fwd_launch(const AttnArgs &a, int64_t batch) {
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(attn_fwd_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)fwd_smem<D>()));
-    attr = true;
+    attr = g_init_epoch;
   }
   dim3 grid((unsigned)((a.T + BQ - 1) / BQ), (unsigned)(batch * a.H));
   attn_fwd_kernel<T, D><<<grid, 256, fwd_smem<D>(), g_stream>>>(a);
@@ -352,11 +352,11 @@ static int fwd_launch(const AttnArgs &a, int64_t batch) {
 
 template <typename T, int D>
 static int bwd_launch(const AttnArgs &a, int64_t batch) {
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(attn_bwd_dkv_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dkv_smem<D>()));
     ALPHA_CUDA(cudaFuncSetAttribute(attn_bwd_dq_kernel<T, D>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)dq_smem<D>()));
-    attr = true;
+    attr = g_init_epoch;
   }
   const int64_t rows = batch * a.H * a.T;
   attn_delta_kernel<T><<<grid_for(rows, 8, 8), 256, 0, g_stream>>>(a, D, rows);

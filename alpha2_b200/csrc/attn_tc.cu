@@ -1427,11 +1427,11 @@ int attn_tc_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf ls
   a.H = (int)p->heads; a.T = (int)p->T;
   a.scale = p->scale; a.cap = p->soft_cap;
   a.err = tc_error_word();
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF_DYN));
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_fwd2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AF2_DYN));
-    attr = true;
+    attr = g_init_epoch;
   }
   if (p->soft_cap > 0.f && p->soft_cap * 1.4426950408889634f <= AF2_MAX_C2) {
     // bounded scores: the persistent kernel without a running maximum
@@ -1472,11 +1472,11 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   a.H = (int)p->heads; a.T = (int)p->T;
   a.scale = p->scale; a.cap = p->soft_cap;
   a.err = tc_error_word();
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AK_DYN));
     ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AQ_DYN));
-    attr = true;
+    attr = g_init_epoch;
   }
   const int BH = (int)(p->batch * p->heads);
   const int n_items = (int)((p->T + 127) / 128) * BH;

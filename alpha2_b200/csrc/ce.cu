@@ -240,16 +240,16 @@ static int ce_launch(alpha_buf logits, alpha_buf targets, alpha_buf dlogits, alp
                      (!(mode & 2) || (dlogits & 15) == 0);
   const int grid = grid_for(N, 1, stage ? 2 : 4);
   if (stage) {
-    static bool attr_set = false;
-    if (!attr_set) {
+    static int attr_set = -1;
+    if (attr_set != g_init_epoch) {
       ALPHA_CUDA(cudaFuncSetAttribute(ce_rows_kernel<T, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-      attr_set = true;
+      attr_set = g_init_epoch;
     }
     if constexpr (sizeof(T) == 2) {
-      static bool attr2_set = false;
-      if (!attr2_set) {
+      static int attr2_set = -1;
+      if (attr2_set != g_init_epoch) {
         ALPHA_CUDA(cudaFuncSetAttribute(ce_rows_bf16_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-        attr2_set = true;
+        attr2_set = g_init_epoch;
       }
       ce_rows_bf16_kernel<<<grid, CE_THREADS, row_bytes, g_stream>>>(
           ptr<__nv_bfloat16>(logits), ptr<int32_t>(targets), ptr<__nv_bfloat16>(dlogits), (float *)row_loss,
@@ -331,6 +331,14 @@ static float *g_ce_noalloc_dev_ptr[CE_NOALLOC_MAX_DEVICES] = {nullptr};
 static int ce_noalloc_scratch(float **out) {
   int dev = -1;
   ALPHA_CUDA(cudaGetDevice(&dev));
+  // The launch goes to the library's stream, which lives on the device alpha_init chose.  A
+  // host thread that never selected that device has device 0 current; resolving the symbol
+  // there would quietly create a context (and load this library's image) on a GPU the
+  // caller never asked for — an allocation this entry point promises not to make.
+  ALPHA_CHECK(dev == g_device,
+              "alpha_cross_entropy_fwd_noalloc: the calling thread's current device is %d but the library runs on "
+              "device %d; call cudaSetDevice(%d) (or alpha_init) in this thread first",
+              dev, g_device, g_device);
   ALPHA_CHECK(dev >= 0 && dev < CE_NOALLOC_MAX_DEVICES, "alpha_cross_entropy_fwd_noalloc: device ordinal %d out of range",
               dev);
   if (g_ce_noalloc_dev_ptr[dev] == nullptr) {

@@ -16,12 +16,17 @@ extern cudaStream_t g_stream;
 extern int g_device;
 extern int g_sm_count;
 extern bool g_inited;
+// Counts alpha_init calls.  Per-device set-up that a launch site does on first use (function
+// attributes, device scratch) is remembered as "done in epoch N", so that it is repeated
+// after alpha_shutdown + alpha_init, which may select another GPU.
+extern int g_init_epoch;
 extern unsigned long long g_launches;
 
 int set_error(const char *fmt, ...);
 // Scratch from the caching pool (runtime.cu); returned with pool_free.
 int pool_alloc(size_t bytes, void **out);
 void rope_tables_clear();  // rope.cu: frees the cos/sin tables (shutdown)
+namespace tc { void tc_error_word_free(); }  // tc_host.cu: frees the bounded-wait error word (shutdown)
 int pool_free(void *p);
 // Device-resident copy of a small host table (pointer/size tables of the multi-tensor
 // kernels).  Tables are cached by content, so a training loop that passes the same

@@ -641,10 +641,10 @@ template <int BN, bool A_MN, bool B_MN>
 static int launch_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_, const CUtensorMap &tx,
                           const GemmTcArgs &g, int grid) {
   using L = GemmSmemLayout<BN, false>;
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_kernel<BN, A_MN, B_MN>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
-    attr = true;
+    attr = g_init_epoch;
   }
   ALPHA_CUDA(launch_overlapped(OVL_GEMM, gemm_tc_kernel<BN, A_MN, B_MN>, dim3(grid), dim3(GEMM_THREADS), L::DYN, ta, tb, tc_, tx, g));
   ALPHA_LAUNCHED();

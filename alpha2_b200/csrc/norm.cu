@@ -850,10 +850,10 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
 template <typename T, int NV, bool RMS>
 static int launch_fwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf b, alpha_buf y, int64_t rows, int64_t dim, float eps) {
   const size_t smem = (size_t)LRF_STAGES * LR_WARPS * dim * sizeof(T) + 128 + 2 * dim * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(ln_fwd_ring<T, NV, RMS>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
-    attr = true;
+    attr = g_init_epoch;
   }
   ALPHA_CUDA(launch_overlapped(OVL_NORM_FWD, ln_fwd_ring<T, NV, RMS>, dim3(grid_for(rows, LR_WARPS, 4)), dim3(LR_THREADS), smem,
                                (const T *)ptr<T>(x), (const float *)ptr<float>(w),
@@ -1013,11 +1013,11 @@ template <typename T, int NV, bool RMS, bool HAS_ADD>
 static int launch_bwd_ring_nv(alpha_buf x, alpha_buf w, alpha_buf g, alpha_buf dx_add, alpha_buf dx, float *part,
                               int64_t rows, int64_t dim, float eps, int grid) {
   const size_t smem = (size_t)LR_STAGES * (HAS_ADD ? 3 : 2) * LR_WARPS * dim * sizeof(T) + 64 + dim * sizeof(float);
-  static bool attr = false;
-  if (!attr) {
+  static int attr = -1;
+  if (attr != g_init_epoch) {
     ALPHA_CUDA(cudaFuncSetAttribute(ln_bwd_ring<T, NV, RMS, HAS_ADD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     200 * 1024));
-    attr = true;
+    attr = g_init_epoch;
   }
   ALPHA_CUDA(launch_overlapped(OVL_NORM_BWD, ln_bwd_ring<T, NV, RMS, HAS_ADD>, dim3(grid), dim3(LR_THREADS), smem,
                                (const T *)ptr<T>(x), (const float *)ptr<float>(w), (const T *)ptr<T>(g),

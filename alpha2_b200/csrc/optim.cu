@@ -23,12 +23,17 @@ struct AdamHyper {
   const float *clip_sumsq;
 };
 
-__device__ __forceinline__ float effective_scale(const AdamHyper &h) {
+// Gradient scale with the clip coefficient folded in.  `*skip` is set when the norm is not
+// finite: the caller must then leave p, m, v and the shadow exactly as they are (the
+// reference does not call the optimizer at all for such a step, trainer.ts:1495-1527,1750;
+// scaling the gradient by zero would not do, 0 * Inf is NaN and decay would still apply).
+__device__ __forceinline__ float effective_scale(const AdamHyper &h, bool *skip) {
   float gs = h.grad_scale;
+  *skip = false;
   if (h.clip_sumsq) {
     const float gnorm = sqrtf(h.clip_sumsq[0]) * fabsf(h.grad_scale);
     if (h.max_norm > 0.f && gnorm > h.max_norm) gs *= h.max_norm / gnorm;
-    if (!isfinite(gnorm)) gs = 0.f;  // non-finite gradients: leave p, m, v untouched by g
+    if (!isfinite(gnorm)) *skip = true;
   }
   return gs;
 }
@@ -100,7 +105,9 @@ struct AdamChunk {
 
 __global__ void __launch_bounds__(256) adamw_chunks_kernel(const AdamChunk *__restrict__ chunks, AdamHyper h) {
   const AdamChunk c = chunks[blockIdx.x];
-  const float gs = effective_scale(h);
+  bool skip;
+  const float gs = effective_scale(h, &skip);
+  if (skip) return;
   if (c.grad_dtype == ALPHA_F32)
     adam_span<float>(c.p, (const float *)c.g, c.m, c.v, c.shadow, c.n, h, gs, c.wd, threadIdx.x, blockDim.x);
   else

@@ -22,6 +22,7 @@ cudaStream_t g_stream = nullptr;
 int g_device = -1;
 int g_sm_count = 148;
 bool g_inited = false;
+int g_init_epoch = 0;
 unsigned long long g_launches = 0;
 int g_overlap_launches = ~0;
 int g_overlap_hold = 0;
@@ -207,6 +208,7 @@ int alpha_init(int device_ordinal) {
   ALPHA_CUDA(cudaStreamCreateWithFlags(&g_stream, cudaStreamNonBlocking));
   g_device = device_ordinal;
   g_launches = 0;
+  g_init_epoch++;
   g_inited = true;
   return 0;
 }
@@ -217,6 +219,7 @@ int alpha_shutdown(void) {
   cudaStreamSynchronize(g_stream);
   tables_clear();
   rope_tables_clear();
+  tc::tc_error_word_free();
   pool_purge(true);
   cudaStreamDestroy(g_stream);
   g_stream = nullptr;

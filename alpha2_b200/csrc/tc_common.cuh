@@ -366,6 +366,7 @@ int encode_tmap_4d_bf16(CUtensorMap *out, const void *base, uint64_t D, uint64_t
 // Device-side error word set by any kernel whose bounded wait ran out (0 = none).
 uint32_t *tc_error_word();
 int tc_check_error(const char *who);
+void tc_error_word_free();
 
 }  // namespace tc
 }  // namespace alpha

@@ -128,6 +128,12 @@ uint32_t *tc_error_word() {
   return g_err_word;
 }
 
+// Shutdown: the word belongs to the device that is being left.
+void tc_error_word_free() {
+  if (g_err_word) cudaFree(g_err_word);
+  g_err_word = nullptr;
+}
+
 int tc_check_error(const char *who) {
   if (!g_err_word) return 0;
   uint32_t v = 0;

@@ -45,12 +45,16 @@ class DataLoader:
     and wrap at N; the target of the last token of the corpus is token 0.  Rank r owns
     cursors r*B .. r*B+B-1.
 
-    Two reusable host buffers alternate between calls (data.ts:48-58); ``pin`` puts them in
-    page-locked memory so that ``to_device`` is a plain asynchronous copy.
+    Two reusable host buffers alternate between calls (data.ts:48-58).  ``pin`` puts them in
+    page-locked memory: ``nextDeviceBatch`` then only enqueues the copies and returns, and an
+    event recorded behind each pair of copies guards the slot — the loader waits on that event
+    before it writes the slot again, so a host that runs several micro-steps or whole steps
+    ahead of the device can never overwrite tokens whose copy has not run yet.  ``slots``
+    (>= 2) is how many batches the host may prepare ahead before that wait can block.
     """
 
     def __init__(self, tokens, rng, batchSize: int, blockSize: int, packed: bool = False, rank: int = 0,
-                 world: int = 1, backend=None, pin: bool = False):
+                 world: int = 1, backend=None, pin: bool = False, slots: int = 2):
         self.tokens = np.ascontiguousarray(tokens, dtype=np.int32)
         self.rng, self.batchSize, self.blockSize, self.packed = rng, int(batchSize), int(blockSize), bool(packed)
         self.rank, self.world = int(rank), int(world)
@@ -62,7 +66,9 @@ class DataLoader:
         self._ring = []
         self._pinned = []
         elems = self.batchSize * self.blockSize
-        for _ in range(2):
+        self._events = []           # per slot: event recorded behind the last upload from it
+        self._in_flight = []        # per slot: True while that event has not been waited on
+        for _ in range(max(2, int(slots))):
             if pin and backend is not None:
                 a, pa = backend.pinned_array((self.batchSize, self.blockSize), np.int32)
                 b, pb = backend.pinned_array((self.batchSize, self.blockSize), np.int32)
@@ -72,7 +78,10 @@ class DataLoader:
                 b = np.zeros((self.batchSize, self.blockSize), np.int32)
             assert a.size == elems
             self._ring.append((a, b))
+            self._events.append(None)
+            self._in_flight.append(False)
         self._idx = 0
+        self._last = 0
 
     @property
     def stepsPerEpoch(self) -> int:
@@ -83,7 +92,12 @@ class DataLoader:
 
     def nextBatch(self):
         """(inputs, targets): int32 [B, T] host arrays, valid until the call after next."""
-        inputs, targets = self._ring[self._idx]
+        slot = self._idx
+        if self._in_flight[slot]:                       # a queued copy still reads this slot
+            self.backend.eventSync(self._events[slot])
+            self._in_flight[slot] = False
+        inputs, targets = self._ring[slot]
+        self._last = slot
         self._idx = (self._idx + 1) % len(self._ring)
         B, T, N, tok = self.batchSize, self.blockSize, len(self.tokens), self.tokens
         if not self.packed:
@@ -118,8 +132,31 @@ class DataLoader:
         return inputs, targets
 
     def nextDeviceBatch(self):
-        """The next batch as device tensors (uploaded on the backend's stream; with pinned
-        buffers the copy is asynchronous and the buffer is not reused before the call after
-        next, by which time the copy has been consumed by a step)."""
+        """The next batch as device tensors, copied on the backend's stream.  The tensors own
+        their device storage and keep no reference to the loader's host buffers (``.data``
+        reads the device copy back).  Pageable buffers are staged by the driver before the
+        copy call returns; pinned ones are guarded by the slot's event (see the class text)."""
         inputs, targets = self.nextBatch()
-        return self.backend.upload(inputs, "i32"), self.backend.upload(targets, "i32")
+        B = self.backend
+        if not self._pinned:
+            return B.upload(inputs.copy(), "i32"), B.upload(targets.copy(), "i32")
+        slot = self._last
+        out = (B.uploadAsync(inputs, "i32"), B.uploadAsync(targets, "i32"))
+        if self._events[slot] is None:
+            self._events[slot] = B.eventCreate()
+        B.eventRecord(self._events[slot])
+        self._in_flight[slot] = True
+        return out
+
+    def close(self) -> None:
+        """Wait for queued copies and give the pinned buffers and events back."""
+        if self.backend is None:
+            return
+        for i, ev in enumerate(self._events):
+            if ev is not None:
+                if self._in_flight[i]:
+                    self.backend.eventSync(ev)
+                self.backend.eventDestroy(ev)
+        for p in self._pinned:
+            self.backend.free_pinned(p)
+        self._events, self._pinned, self._in_flight = [None] * len(self._ring), [], [False] * len(self._ring)

@@ -25,6 +25,7 @@ class AdamW:
         self._step = 0
         self._beta1Pow = 1.0
         self._beta2Pow = 1.0
+        self._prev = None
         self._m: dict[str, TensorData] = {}
         self._v: dict[str, TensorData] = {}
 
@@ -32,10 +33,21 @@ class AdamW:
         self.lr = lr
 
     def _next_bias_corrections(self):
+        self._prev = (self._step, self._beta1Pow, self._beta2Pow)
         self._step += 1
         self._beta1Pow *= self.beta1
         self._beta2Pow *= self.beta2
         return 1 - self._beta1Pow, 1 - self._beta2Pow
+
+    def undoStep(self) -> None:
+        """Take back the last advance of the step count and the running beta powers.  The fused
+        update skips itself on the device when the gradient norm is not finite; a host that
+        learns of that afterwards (it reads the norm with the loss) calls this so that the
+        bias corrections continue as if the optimizer had not been called — which is what the
+        reference does for such a step (trainer.ts:1495-1527,1750)."""
+        if self._prev is not None:
+            self._step, self._beta1Pow, self._beta2Pow = self._prev
+            self._prev = None
 
     def _moments(self, name: str, param: TensorData):
         if name not in self._m:

@@ -179,6 +179,9 @@ class Trainer:
                                       clipSumSq=sumsq if tc.gradClip > 0 else None, maxNorm=tc.gradClip)
             if read_back:
                 gnorm = math.sqrt(float(sumsq.item())) * abs(grad_scale)
+                if not math.isfinite(gnorm):               # the kernel left p, m, v untouched
+                    self.opt.undoStep()
+                    result["skipped"] = True
                 result.update(loss=loss_td.item(), gradNorm=gnorm,
                               clipCoef=(tc.gradClip / gnorm if tc.gradClip > 0 and gnorm > tc.gradClip else 1.0))
             else:

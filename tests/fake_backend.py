@@ -307,6 +307,8 @@ class NumpyBackend:
         gs = gradScale
         if clipSumSq is not None:
             gn = math.sqrt(float(clipSumSq.data.reshape(-1)[0])) * abs(gradScale)
+            if not math.isfinite(gn):
+                return                          # the step is skipped: p, m, v stay as they are
             if maxNorm > 0 and gn > maxNorm:
                 gs *= maxNorm / gn
         for (p, g, m, v, wd, sh) in entries:

@@ -164,3 +164,32 @@ def test_evaluate_and_last_row_logits_on_the_device(dtype, tol):
     out = sample_tokens(mc, P, B, OracleRng(2), ctx[0, :5], steps=6, temperature=0.0)
     assert out.size == 11
     B.checkAsyncError()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("packed", [False, True])
+def test_pinned_loader_feeds_the_device_while_earlier_work_is_still_queued(packed):
+    """Seven batches are requested back to back from a two-slot page-locked ring while tens of
+    milliseconds of kernels are still queued in front of the copies; every device batch must
+    equal the host loader's, and the tensors must not alias the ring."""
+    import time
+    from alpha2_b200.backend import CudaBackend
+    B = CudaBackend(0)
+    tok = _tokens(300000, 50257, seed=3)
+    ld = DataLoader(tok, OracleRng(21), 16, 1024, packed, backend=B, pin=True)
+    ref = DataLoader(tok, OracleRng(21), 16, 1024, packed)
+    x = B.upload(np.random.default_rng(0).standard_normal((2048, 2048)).astype(np.float32))
+    B.syncGpu()
+    t0 = time.perf_counter()
+    for _ in range(24):                                      # fp32 FMA GEMMs: a long queue
+        x2 = B.matmul(x, x)
+    queued = time.perf_counter() - t0
+    got = [ld.nextDeviceBatch() for _ in range(7)]
+    B.syncGpu()
+    busy = time.perf_counter() - t0
+    assert busy > 2 * queued                                 # the requests really ran ahead of the device
+    for i, t in got:
+        wi, wt = ref.nextBatch()
+        assert i._host is None and np.array_equal(i.data, wi) and np.array_equal(t.data, wt)
+    ld.close()
+    B.checkAsyncError()

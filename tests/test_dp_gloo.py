@@ -48,7 +48,7 @@ class GlooBucketDP(GlooDP):
             self.allreduce(g)
 
 
-def _worker(rank, world, port, out_dir, bucketed=False):
+def _worker(rank, world, port, out_dir, bucketed=False, ckpt=False):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -59,7 +59,7 @@ def _worker(rank, world, port, out_dir, bucketed=False):
     mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=2, nEmbd=32, nHead=4, tied=True, init="plain")
     tc = TrainConfig(iters=10, batchSize=2, gradClip=0.5, seed=3)
     dp = GlooBucketDP(world, rank) if bucketed else GlooDP(world, rank)
-    tr = Trainer(NumpyBackend(), mc, tc, dp=dp)
+    tr = Trainer(NumpyBackend(), mc, tc, dp=dp, activationCheckpointing=ckpt)
     batches = uniform_batches(100 + rank, 3, 2, 16, 64)          # a different stream per rank
     res = [tr.train_step([(T(t, "i32"), T(g, "i32"))]) for t, g in batches]
     n_params = len(tr.entries)
@@ -71,13 +71,13 @@ def _worker(rank, world, port, out_dir, bucketed=False):
     dist.destroy_process_group()
 
 
-import pytest
-
-
-@pytest.mark.parametrize("bucketed", [False, True])
-def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path, bucketed):
-    port = 29500 + (os.getpid() + (997 if bucketed else 0)) % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path), bucketed), nprocs=2, join=True)
+@pytest.mark.parametrize("bucketed,ckpt", [(False, False), (True, False), (True, True)])
+def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path, bucketed, ckpt):
+    """``ckpt``: every block runs under activation checkpointing, where the block parameters'
+    gradients are produced on an inner tape during the recompute; they must still all be
+    handed to the exchange (the worker asserts one hand-over per parameter per step)."""
+    port = 29500 + (os.getpid() + (997 if bucketed else 0) + (331 if ckpt else 0)) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), bucketed, ckpt), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     for k in r0.files:
         assert np.array_equal(r0[k], r1[k]), k                   # replicas stay identical

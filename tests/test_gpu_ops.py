@@ -321,6 +321,38 @@ def test_adamw_matches_reference_loop(B):
     assert np.array_equal(va.shadow.data, bf16_round(va.data.data))
 
 
+@pytest.mark.parametrize("bad", [np.inf, np.nan])
+def test_fused_adamw_skips_a_step_with_non_finite_gradients(B, bad):
+    """trainer.ts:1495-1527,1750: a step whose gradient norm is not finite does not call the
+    optimizer.  The fused update learns the norm on the device, so the kernel itself must leave
+    p, m, v and the bf16 shadow bit for bit as they were — for every element, not only those
+    whose own gradient is finite — and the host's step count must be taken back."""
+    from alpha2_b200.optimizers import AdamW
+    r = rng(11)
+    n = 200003
+    p0, g0 = r.standard_normal(n).astype(f32), r.standard_normal(n).astype(f32)
+
+    class V:
+        def __init__(s, d, g, sh): s.data, s.grad, s.shadow = d, g, sh
+    va = V(B.upload(p0), B.upload(g0), B.castDtype(B.upload(p0), "bf16"))
+    opt = AdamW(B, lr=1e-3, weightDecay=0.1)
+    sumsq = B.totalSumOfSquares([va.grad])
+    opt.stepParamEntries([("w", va)], 0.5, fused=True, clipSumSq=sumsq, maxNorm=1.0)      # a normal step first
+    before = [np.array(t.data).copy() for t in (va.data, opt._m["w"], opt._v["w"], va.shadow)]
+    assert not np.array_equal(before[0], p0)
+    g1 = g0.copy(); g1[12345] = bad
+    va.grad = B.upload(g1)
+    sumsq = B.totalSumOfSquares([va.grad])
+    assert not math.isfinite(sumsq.item())
+    state = (opt._step, opt._beta1Pow, opt._beta2Pow)
+    opt.stepParamEntries([("w", va)], 0.5, fused=True, clipSumSq=sumsq, maxNorm=1.0)
+    for t, old in zip((va.data, opt._m["w"], opt._v["w"], va.shadow), before):
+        t.invalidate_host()
+        assert np.array_equal(np.array(t.data), old)
+    opt.undoStep()
+    assert (opt._step, opt._beta1Pow, opt._beta2Pow) == state
+
+
 # ── GEMM ────────────────────────────────────────────────────────────────────
 def lcg(seed, n):
     """Inputs of the reference's own GEMM check (apps/cli/src/commands/bench.ts:402-410)."""

@@ -137,3 +137,26 @@ def test_activation_checkpointing_matches_plain_training():
     gptForward(mc, tr.params, B, plain, T(t0, "i32"), T(g0, "i32"), training=True)
     gptForward(mc, tr.params, B, ck, T(t0, "i32"), T(g0, "i32"), training=True, activationCheckpointing=True)
     assert ck.size < plain.size and ck.size <= 3 + 4            # embedding, 3 segments, final norm, head
+
+
+@pytest.mark.filterwarnings("ignore::RuntimeWarning")
+def test_fused_step_with_non_finite_gradients_changes_nothing():
+    """trainer.ts:1495-1527,1750: no optimizer call when the gradient norm is not finite.  In
+    the fused mode the update is queued before the host knows; parameters, moments and the
+    bias-correction count must come out of such a step as they went in."""
+    mc = ModelConfig(vocabSize=32, blockSize=8, nLayer=1, nEmbd=16, nHead=2)
+    tr = Trainer(NumpyBackend(), mc, TrainConfig(iters=6, batchSize=2, seed=1))
+    bs = otrain.uniform_batches(2, 3, 2, 8, 32)
+    tr.train_step([(T(bs[0][0], "i32"), T(bs[0][1], "i32"))])
+    before = {n: v.data.data.copy() for n, v in tr.entries}
+    m_before = {n: t.data.copy() for n, t in tr.opt._m.items()}
+    state = (tr.opt._step, tr.opt._beta1Pow, tr.opt._beta2Pow)
+    tr.params["wpe"].data.data[0, 0] = np.inf                      # poisons the forward pass
+    res = tr.train_step([(T(bs[1][0], "i32"), T(bs[1][1], "i32"))])
+    assert res.get("skipped") and not np.isfinite(res["gradNorm"])
+    tr.params["wpe"].data.data[0, 0] = before["wpe"][0, 0]
+    for n, v in tr.entries:
+        assert np.array_equal(v.data.data, before[n]), n
+    for n, t in tr.opt._m.items():
+        assert np.array_equal(t.data, m_before[n]), n
+    assert (tr.opt._step, tr.opt._beta1Pow, tr.opt._beta2Pow) == state

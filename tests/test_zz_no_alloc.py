@@ -70,3 +70,26 @@ def test_noalloc_rejects_more_rows_than_the_fixed_scratch(B):
     check(B.lib.alpha_cross_entropy_fwd_noalloc(out.ptr, out.ptr, out.ptr, 0, 4, 4, 0))
     out.invalidate_host()                                  # re-read the device value
     assert out.item() == 0.0
+
+
+def test_noalloc_from_another_host_thread(B):
+    """The scratch address is resolved for the device the library was initialised on, and a
+    thread whose current device is a different one is refused before anything is resolved or
+    launched.  On device 0 a fresh thread's default device is the library's, so the call works
+    and gives the same loss as the calling thread got."""
+    import threading
+    from alpha2_b200._lib import check
+    rng = np.random.default_rng(9)
+    N, V = 50, 300
+    logits = B.upload(rng.standard_normal((N, V)).astype(np.float32), "f32")
+    targets = B.upload(rng.integers(0, V, N).astype(np.int32), "i32")
+    here, there = B.full((), -1.0), B.full((), -2.0)
+    check(B.lib.alpha_cross_entropy_fwd_noalloc(logits.ptr, targets.ptr, here.ptr, N, V, V, 0))
+    box = {}
+
+    def run():
+        box["rc"] = B.lib.alpha_cross_entropy_fwd_noalloc(logits.ptr, targets.ptr, there.ptr, N, V, V, 0)
+    th = threading.Thread(target=run)
+    th.start(); th.join()
+    B.syncGpu()
+    assert box["rc"] == 0 and there.item() == here.item()
