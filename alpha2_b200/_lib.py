@@ -70,6 +70,7 @@ SIGNATURES = {
     "alpha_init": [_I], "alpha_shutdown": [], "alpha_device_info": [C.POINTER(DeviceInfo)],
     "alpha_stream_sync": [], "alpha_launch_count": [C.POINTER(C.c_uint64)],
     "alpha_stream_handle": [C.POINTER(C.c_uint64)], "alpha_check_async_error": [],
+    "alpha_debug_wait_expiry": [_I, _I, C.POINTER(C.c_int)],
     "alpha_profile_enable": [_I], "alpha_profile_read": [C.POINTER(ProfileEntry), _I],
     "alpha_event_create": [C.POINTER(C.c_uint64)], "alpha_event_record": [_B], "alpha_event_sync": [_B],
     "alpha_event_elapsed_ms": [_B, _B, C.POINTER(C.c_float)], "alpha_event_destroy": [_B],
@@ -115,6 +116,7 @@ SIGNATURES = {
     "alpha_adamw_multi": [C.POINTER(AdamWTensor), _I, _F, _F, _F, _F, _F, _F, _F, _B, _F],
     "alpha_comm_unique_id": [_P], "alpha_comm_init_rank": [_I, _I, _P],
     "alpha_comm_allreduce_sum": [_B, _L, _I], "alpha_comm_wait": [], "alpha_comm_destroy": [],
+    "alpha_comm_query": [C.POINTER(C.c_int), C.POINTER(C.c_int)], "alpha_comm_abort": [],
     "alpha_comm_allreduce_sum_bucket": [C.POINTER(C.c_uint64), _PL, _I, _I],
     "alpha_rng_seed": [C.POINTER(HostRng), C.c_uint32],
     "alpha_rng_fill_gauss": [C.POINTER(HostRng), _P, _L, C.c_double],

@@ -29,12 +29,14 @@ struct Nccl {
   ncclResult_t (*GroupStart)() = nullptr;
   ncclResult_t (*GroupEnd)() = nullptr;
   ncclResult_t (*CommDestroy)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommAbort)(ncclComm_t) = nullptr;
+  ncclResult_t (*CommGetAsyncError)(ncclComm_t, ncclResult_t *) = nullptr;
   const char *(*GetErrorString)(ncclResult_t) = nullptr;
 };
 static Nccl g_nccl;
 static ncclComm_t g_comm = nullptr;
 static cudaStream_t g_comm_stream = nullptr;
-static cudaEvent_t g_ev_ready = nullptr, g_ev_done = nullptr;
+static cudaEvent_t g_ev_ready = nullptr, g_ev_done = nullptr, g_ev_probe = nullptr;
 static int g_nranks = 1;
 
 static int load_nccl() {
@@ -54,6 +56,8 @@ static int load_nccl() {
   SYM(GroupStart, "ncclGroupStart")
   SYM(GroupEnd, "ncclGroupEnd")
   SYM(CommDestroy, "ncclCommDestroy")
+  SYM(CommAbort, "ncclCommAbort")
+  SYM(CommGetAsyncError, "ncclCommGetAsyncError")
   SYM(GetErrorString, "ncclGetErrorString")
 #undef SYM
   return 0;
@@ -92,6 +96,7 @@ int alpha_comm_init_rank(int n_ranks, int rank, const void *unique_id_128_bytes)
   ALPHA_CUDA(cudaStreamCreateWithFlags(&g_comm_stream, cudaStreamNonBlocking));
   ALPHA_CUDA(cudaEventCreateWithFlags(&g_ev_ready, cudaEventDisableTiming));
   ALPHA_CUDA(cudaEventCreateWithFlags(&g_ev_done, cudaEventDisableTiming));
+  ALPHA_CUDA(cudaEventCreateWithFlags(&g_ev_probe, cudaEventDisableTiming));
   ALPHA_NCCL(g_nccl.CommInitRank(&g_comm, n_ranks, id, rank));
   return 0;
 }
@@ -143,16 +148,62 @@ int alpha_comm_wait(void) {
   return 0;
 }
 
+// Host-side view of the exchange, without blocking: *pending = 1 while collectives enqueued so
+// far have not completed on the device, *async_error = NCCL's asynchronous error code for the
+// communicator (0 = none; a peer that died or a network fault shows up here, not as a return
+// code of the enqueue).  A host that must not wait for ever polls this against a deadline and
+// calls alpha_comm_abort when the deadline passes or an error appears.
+int alpha_comm_query(int *pending, int *async_error) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(pending != nullptr && async_error != nullptr, "alpha_comm_query: null output");
+  *pending = 0;
+  *async_error = 0;
+  if (g_nranks == 1 || g_comm == nullptr) return 0;
+  ALPHA_CUDA(cudaEventRecord(g_ev_probe, g_comm_stream));
+  cudaError_t q = cudaEventQuery(g_ev_probe);
+  if (q == cudaErrorNotReady) {
+    *pending = 1;
+  } else if (q != cudaSuccess) {
+    return set_error("alpha_comm_query: cudaEventQuery -> %s", cudaGetErrorString(q));
+  }
+  ncclResult_t ae = 0;
+  ALPHA_NCCL(g_nccl.CommGetAsyncError(g_comm, &ae));
+  *async_error = (int)ae;
+  return 0;
+}
+
+static void comm_release_streams() {
+  if (g_comm_stream) { cudaStreamDestroy(g_comm_stream); g_comm_stream = nullptr; }
+  if (g_ev_ready) { cudaEventDestroy(g_ev_ready); g_ev_ready = nullptr; }
+  if (g_ev_done) { cudaEventDestroy(g_ev_done); g_ev_done = nullptr; }
+  if (g_ev_probe) { cudaEventDestroy(g_ev_probe); g_ev_probe = nullptr; }
+  g_nranks = 1;
+}
+
+// Gives up on the communicator: ncclCommAbort makes collectives that are still waiting for a
+// peer return, so the side stream drains and the process can report the failure and leave (or
+// build a new communicator with the ranks that remain).  Gradients touched by an aborted
+// collective are undefined; the step must be discarded.
+int alpha_comm_abort(void) {
+  if (g_comm) {
+    ncclResult_t r = g_nccl.CommAbort(g_comm);
+    g_comm = nullptr;
+    if (g_comm_stream) cudaStreamSynchronize(g_comm_stream);
+    comm_release_streams();
+    if (r != 0) return set_error("alpha_comm_abort: ncclCommAbort -> %s", g_nccl.GetErrorString(r));
+    return 0;
+  }
+  comm_release_streams();
+  return 0;
+}
+
 int alpha_comm_destroy(void) {
   if (g_comm) {
     cudaStreamSynchronize(g_comm_stream);
     g_nccl.CommDestroy(g_comm);
     g_comm = nullptr;
   }
-  if (g_comm_stream) { cudaStreamDestroy(g_comm_stream); g_comm_stream = nullptr; }
-  if (g_ev_ready) { cudaEventDestroy(g_ev_ready); g_ev_ready = nullptr; }
-  if (g_ev_done) { cudaEventDestroy(g_ev_done); g_ev_done = nullptr; }
-  g_nranks = 1;
+  comm_release_streams();
   return 0;
 }
 

@@ -55,7 +55,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 // before the warp-collective instructions that follow a wait (tcgen05.ld / .st, elect.sync)
 // and gives every lane the same answer.  Without it a wait that really had to spin could
 // leave the warp split, and a tcgen05.ld issued by part of a warp returns garbage.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+__device__ __forceinline__ bool mbar_wait_limited(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag,
+                                                  long long limit_cycles) {
   bool ok = mbar_try_wait(bar, parity);
   if (!ok) {
     const long long t0 = clock64();
@@ -65,13 +66,16 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatil
         break;
       }
       if (*abort_flag) break;
-      if (clock64() - t0 > WAIT_LIMIT_CYCLES) {
+      if (clock64() - t0 > limit_cycles) {
         *abort_flag = 1;
         break;
       }
     }
   }
   return __all_sync(0xffffffffu, ok);
+}
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile uint32_t *abort_flag) {
+  return mbar_wait_limited(bar, parity, abort_flag, WAIT_LIMIT_CYCLES);
 }
 
 // 2-D tiled TMA load global -> shared, completion counted on an mbarrier.  x is the

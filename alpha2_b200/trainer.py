@@ -74,14 +74,37 @@ def learningRate(tc: TrainConfig, step: int) -> float:
     return max(lr_min * 0.1, base)
 
 
+class CollectiveError(RuntimeError):
+    """The gradient exchange failed (NCCL reported an asynchronous error) or did not finish
+    within the host's deadline.  The communicator has been aborted; the step is void."""
+
+
+class PeerLeftError(RuntimeError):
+    """Another rank announced that it has left the job; raised before anything is launched."""
+
+
 class DataParallel:
     """One rank of a data-parallel job: NCCL communicator inside the library, gradients
-    all-reduced on its side stream as soon as backward has finalised them."""
+    all-reduced on its side stream as soon as backward has finalised them.
 
-    def __init__(self, backend: CudaBackend, world: int, rank: int, unique_id: bytes):
+    Failure handling, all on the host (the reference is single-device and has none):
+    * ``store`` — any key-value store shared by the ranks with ``set(key, value)`` and
+      ``check([keys]) -> bool`` (``torch.distributed.TCPStore`` fits).  A rank that stops
+      between steps calls ``leave()``; the others see it in ``assert_peers()``, which the
+      trainer calls at the top of every step, before any kernel or collective of that step is
+      enqueued, and raise ``PeerLeftError`` instead of entering a collective that would wait for
+      ever.
+    * ``sync(timeout_s)`` — waits on the host for the collectives enqueued so far, polling the
+      device and NCCL's asynchronous error state; on an error or when the deadline passes it
+      aborts the communicator (``ncclCommAbort`` releases collectives stuck on a missing peer)
+      and raises ``CollectiveError``.  ``wait()`` stays the cheap stream-order form used inside
+      the step.
+    """
+
+    def __init__(self, backend: CudaBackend, world: int, rank: int, unique_id: bytes, store=None):
         import ctypes as C
         from ._lib import check
-        self.backend, self.world, self.rank = backend, world, rank
+        self.backend, self.world, self.rank, self.store = backend, world, rank, store
         buf = C.create_string_buffer(unique_id, 128)
         check(backend.lib.alpha_comm_init_rank(world, rank, buf))
 
@@ -116,6 +139,44 @@ class DataParallel:
         from ._lib import check
         check(self.backend.lib.alpha_comm_wait())
 
+    # ── failure handling ──────────────────────────────────────────────────────
+    def leave(self) -> None:
+        """Announce that this rank will enqueue no further collectives (call between steps)."""
+        if self.store is not None:
+            self.store.set(f"alpha_dp/left/{self.rank}", b"1")
+
+    def peers_gone(self) -> list:
+        if self.store is None:
+            return []
+        return [r for r in range(self.world) if r != self.rank and self.store.check([f"alpha_dp/left/{r}"])]
+
+    def assert_peers(self) -> None:
+        gone = self.peers_gone()
+        if gone:
+            raise PeerLeftError(f"rank {self.rank}: rank(s) {gone} left the job; not entering the next exchange")
+
+    def sync(self, timeout_s: float = 30.0, poll_s: float = 0.0005) -> None:
+        """Wait on the host until every collective enqueued so far has completed."""
+        import ctypes as C
+        import time
+        from ._lib import check
+        lib = self.backend.lib
+        pending, err = C.c_int(0), C.c_int(0)
+        deadline = time.monotonic() + float(timeout_s)
+        while True:
+            check(lib.alpha_comm_query(C.byref(pending), C.byref(err)))
+            if err.value != 0:
+                lib.alpha_comm_abort()
+                raise CollectiveError(f"rank {self.rank}: NCCL reported asynchronous error {err.value}; "
+                                      "communicator aborted")
+            if not pending.value:
+                return
+            if time.monotonic() > deadline:
+                lib.alpha_comm_abort()
+                raise CollectiveError(f"rank {self.rank}: gradient exchange did not finish within {timeout_s} s; "
+                                      "communicator aborted")
+            time.sleep(poll_s)
+
 
 class Trainer:
     def __init__(self, backend: CudaBackend, modelConfig: ModelConfig, trainConfig: TrainConfig,
@@ -144,6 +205,8 @@ class Trainer:
         B, tc = self.B, self.tc
         accum = len(batches)
         world = self.dp.world if self.dp else 1
+        if self.dp is not None and hasattr(self.dp, "assert_peers"):
+            self.dp.assert_peers()                             # before anything of this step is enqueued
         lr = learningRate(tc, self.step_index)
         self.opt.setLr(lr)
         B.resetStepOps()
@@ -196,6 +259,11 @@ class Trainer:
             if math.isfinite(loss_val) and math.isfinite(gnorm):
                 self.opt.stepParamEntries(self.entries, eff)
             result.update(loss=loss_val, gradNorm=gnorm, clipCoef=clip)
+        if read_back and hasattr(B, "checkAsyncError"):
+            # The host has just waited for the step's scalars, so asking the library whether a
+            # tensor-core kernel gave up a bounded wait costs one 4-byte read.  Such a step
+            # produced garbage; the error must not pass silently into the next one.
+            B.checkAsyncError()
         for _, v in self.entries:                              # trainer.ts:1776-1780
             v.grad = None
         self.step_index += 1

@@ -60,6 +60,14 @@ int alpha_stream_handle(uint64_t *out);
  * abandoned one of its bounded waits since the last check; such a kernel's output is
  * invalid.  Waits inside the kernels never spin without limit. */
 int alpha_check_async_error(void);
+/* Test hook for the give-up path of those waits (no reference counterpart): launches, on
+ * `blocks` SMs, a kernel with the GEMM's role structure and tensor-memory allocation in which
+ * the producer waits on a barrier that nothing signals, with a limit of `limit_us`
+ * microseconds (1..100000) instead of the production limit of about a second.  The wait runs
+ * out, every role unwinds, tensor memory is freed and the error word is set; nothing faults
+ * and the kernel returns by itself.  *roles_left_out = number of warps that left through the
+ * give-up path (6 per block).  The next alpha_check_async_error() reports the expiry. */
+int alpha_debug_wait_expiry(int blocks, int limit_us, int *roles_left_out);
 
 /* The tensor-core GEMM, attention and norm kernels are launched so that their blocks may
  * become resident and set themselves up while the previous kernel of the stream drains
@@ -359,6 +367,13 @@ int alpha_comm_allreduce_sum(alpha_buf buf, int64_t n, int dtype);
 int alpha_comm_allreduce_sum_bucket(const alpha_buf *bufs, const int64_t *counts, int n_bufs, int dtype);
 int alpha_comm_wait(void);
 int alpha_comm_destroy(void);
+/* Failure handling of the exchange (host side; no reference counterpart).  alpha_comm_query
+ * never blocks: *pending = 1 while collectives enqueued so far are unfinished, *async_error =
+ * NCCL's asynchronous error code of the communicator (0 = none).  alpha_comm_abort ends the
+ * communicator with ncclCommAbort, which releases collectives that wait for a peer that will
+ * never come; the step in flight must be discarded. */
+int alpha_comm_query(int *pending, int *async_error);
+int alpha_comm_abort(void);
 
 #ifdef __cplusplus
 }

@@ -1,0 +1,135 @@
+"""Data parallel on real hardware: two ranks, one GPU each, the library's own NCCL exchange.
+
+The reference has nothing distributed (docs/scale.md:3), so the oracle for data parallel is the
+identity "N ranks with one batch each == one rank that takes the N batches as N accumulated
+micro-steps" (1/accum and 1/world are folded into the optimizer's gradient scale in the same
+place, trainer.ts:1297,1650-1656).  ``tests/test_dp_gloo.py`` checks that identity for the host
+logic on CPU; this file checks it through everything a multi-GPU run really uses: comm.cu, NCCL,
+the side stream and its events, the two ordinary launches after every queued collective, the
+bucket flush during backward.
+
+Each rank is a child process (``python tests/test_gpu_dp_nccl.py --rank r ...``) that trains for
+three steps and saves its parameters and gradient norms; the parent then runs the same batches
+on one GPU as accumulated micro-steps and compares:
+
+* the replicas are bit-identical to each other,
+* they equal the single-GPU run: fp32 parameters within 2e-6 absolute and the gradient norm
+  within 2e-5 relative (the two runs differ only in the order of one fp32 sum per gradient
+  element); the bf16 case uses the same bounds on its fp32 master weights.
+
+Needs two visible GPUs; skipped otherwise.  NCCL runs with its defaults except NVLS, which is
+switched off because the children exit on their own schedule.
+"""
+import argparse
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+CASES = {
+    # the tiny byte-level GPT in fp32 (reference-faithful init, untied head, head dim 16)
+    "tiny_f32": dict(model=dict(vocabSize=256, blockSize=64, nLayer=2, nEmbd=64, nHead=4), dtype="f32", batch=4,
+                     ckpt=False),
+    # a short stand-in of the GPT-2-124M shape in bf16: full vocabulary and width, tied head, head
+    # dim 64 (tensor-core attention and paired GEMMs), three layers, context 256; ~39M-element
+    # tied embedding gradient => several buckets per step
+    "gpt2_width_bf16": dict(model=dict(vocabSize=50257, blockSize=256, nLayer=3, nEmbd=768, nHead=12, tied=True,
+                                       init="plain"), dtype="bf16", batch=4, ckpt=False),
+    # the same with every block under activation checkpointing (block gradients come from an inner tape)
+    "gpt2_width_bf16_ckpt": dict(model=dict(vocabSize=50257, blockSize=256, nLayer=3, nEmbd=768, nHead=12, tied=True,
+                                            init="plain"), dtype="bf16", batch=4, ckpt=True),
+}
+STEPS = 3
+TRAIN = dict(iters=20, lr=3e-4, gradClip=1.0, seed=42)
+
+
+def _batches(case: dict, rank: int):
+    from alpha2_b200.data import zipf_batches
+    m = case["model"]
+    return zipf_batches(100 + rank, STEPS, case["batch"], m["blockSize"], m["vocabSize"])
+
+
+def _trainer(B, case: dict, dp=None):
+    from alpha2_b200.gpt import ModelConfig
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    return Trainer(B, ModelConfig(**case["model"], compute_dtype=case["dtype"]),
+                   TrainConfig(batchSize=case["batch"], **TRAIN), dp=dp, activationCheckpointing=case["ckpt"])
+
+
+def _worker(args) -> None:
+    from alpha2_b200.backend import CudaBackend
+    from alpha2_b200.trainer import DataParallel
+    case = CASES[args.case]
+    B = CudaBackend(args.rank)
+    dp = DataParallel(B, args.world, args.rank, bytes.fromhex(args.uid))
+    tr = _trainer(B, case, dp)
+    res = [tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))]) for t, g in _batches(case, args.rank)]
+    B.checkAsyncError()
+    np.savez(os.path.join(args.out, f"{args.case}_rank{args.rank}.npz"),
+             gn=np.array([r["gradNorm"] for r in res]), loss=np.array([r["loss"] for r in res]),
+             **{n: np.array(v.data.data) for n, v in tr.entries})
+    B.lib.alpha_comm_destroy()
+
+
+def _gpu_count() -> int:
+    try:
+        out = subprocess.run(["nvidia-smi", "-L"], capture_output=True, text=True, timeout=30).stdout
+        return sum(1 for line in out.splitlines() if line.startswith("GPU "))
+    except Exception:
+        return 0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("case", list(CASES))
+def test_two_nccl_ranks_equal_one_gpu_with_two_microsteps(tmp_path, case):
+    if _gpu_count() < 2:
+        pytest.skip("needs two visible GPUs")
+    from alpha2_b200.backend import CudaBackend
+    from alpha2_b200.trainer import DataParallel
+    world = 2
+    uid = DataParallel.new_unique_id().hex()
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    procs = [subprocess.Popen([sys.executable, os.path.abspath(__file__), "--rank", str(r), "--world", str(world),
+                               "--uid", uid, "--case", case, "--out", str(tmp_path)], env=env)
+             for r in range(world)]
+    for p in procs:
+        assert p.wait(timeout=600) == 0
+    r0, r1 = (np.load(tmp_path / f"{case}_rank{r}.npz") for r in range(world))
+    for k in r0.files:
+        if k != "loss":                                       # each rank reports the loss of its own batch
+            assert np.array_equal(r0[k], r1[k]), k
+    B = CudaBackend(0)
+    spec = CASES[case]
+    tr = _trainer(B, spec)
+    b0, b1 = _batches(spec, 0), _batches(spec, 1)
+    gns, losses = [], []
+    for i in range(STEPS):
+        pair = [(B.upload(t, "i32"), B.upload(g, "i32")) for t, g in (b0[i], b1[i])]
+        r = tr.train_step(pair)
+        gns.append(r["gradNorm"]); losses.append(r["loss"])
+    B.checkAsyncError()
+    np.testing.assert_allclose(r0["gn"], gns, rtol=2e-5)
+    np.testing.assert_allclose((r0["loss"] + r1["loss"]) / 2, losses, rtol=2e-5)
+    worst = 0.0
+    for n, v in tr.entries:
+        d = float(np.max(np.abs(r0[n] - v.data.data)))
+        worst = max(worst, d)
+        assert d <= 2e-6, (n, d)
+    print(f"{case}: 2 NCCL ranks == 1 GPU x 2 micro-steps; worst parameter difference {worst:.2e}, "
+          f"gradient norms {r0['gn'].tolist()} vs {gns}")
+
+
+if __name__ == "__main__":
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--rank", type=int, required=True)
+    ap.add_argument("--world", type=int, required=True)
+    ap.add_argument("--uid", required=True)
+    ap.add_argument("--case", required=True)
+    ap.add_argument("--out", required=True)
+    _worker(ap.parse_args())

@@ -56,6 +56,56 @@ def test_gemm_checksums_at_full_size(B, layout, M, Nn, K):
     assert np.max(np.abs(got.sum(0) - cols)) < 1e-4 * scale * M
 
 
+@pytest.mark.parametrize("layout", ["nt", "nn", "tn"])
+def test_lm_head_gemm_checksums_at_full_size(B, layout):
+    """The three GEMMs of the language-model head at 16384 rows and the GPT-2 vocabulary, whose
+    50257 is a multiple of no tile: logits = x W^T (NT, N = 50257, row pitch 50304 as the head
+    stores them), dx = dlogits W (NN, K = 50257), dW = dlogits^T x (TN, M = 50257).  Same two
+    checksums as above, which together touch every tile, the ragged last ones included; the
+    pad columns of the logits buffer must stay untouched."""
+    from alpha2_b200 import _lib as L
+    from alpha2_b200._lib import check
+    LD = 50304
+    r = np.random.default_rng({"nt": 1, "nn": 2, "tn": 3}[layout])
+    gen = lambda shape: bf16_round(r.standard_normal(shape, dtype=f32) * f32(0.05))
+    if layout == "nt":
+        M, Nn, K = N, V, E
+        a, b = gen((N, E)), gen((V, E))
+        A, Bm, lda, ldb, ldc = B.upload(a, "bf16"), B.upload(b, "bf16"), E, E, LD
+    elif layout == "nn":
+        M, Nn, K = N, E, V
+        a, b = gen((N, V)), gen((V, E))
+        pad = np.zeros((N, LD), f32); pad[:, :V] = a; pad[:, V:] = 7.0      # pad columns must not be read
+        A, Bm, lda, ldb, ldc = B.upload(pad, "bf16"), B.upload(b, "bf16"), LD, E, E
+        del pad
+    else:
+        M, Nn, K = V, E, N
+        a, b = gen((N, V)), gen((N, E))
+        pad = np.zeros((N, LD), f32); pad[:, :V] = a; pad[:, V:] = 7.0
+        A, Bm, lda, ldb, ldc = B.upload(pad, "bf16"), B.upload(b, "bf16"), LD, E, E
+        del pad
+    Cm = B.full((M, ldc), -3.0, "f32")
+    code = {"nt": L.GEMM_NT, "nn": L.GEMM_NN, "tn": L.GEMM_TN}[layout]
+    check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cm.ptr, M, Nn, K, lda, ldb, ldc, L.BF16, L.F32, L.EPI_NONE, 0, 0, 0))
+    Cm.invalidate_host()
+    got = Cm.data
+    if ldc != Nn:
+        assert np.all(got[:, Nn:] == -3.0)
+        got = got[:, :Nn]
+    d = lambda x, y: np.matmul(x, y, dtype=np.float64)
+    b64 = b.astype(np.float64)
+    if layout == "nt":
+        rows, cols = d(a, b64.sum(0)), d(a.sum(0, dtype=np.float64), b64.T)
+    elif layout == "nn":
+        rows, cols = d(a, b64.sum(1)), d(a.sum(0, dtype=np.float64), b64)
+    else:
+        rows, cols = d(a.T, b64.sum(1)), d(a.sum(1, dtype=np.float64), b64)
+    scale = math.sqrt(K) * 0.05 * 0.05
+    assert np.max(np.abs(got.sum(1, dtype=np.float64) - rows)) < 1e-4 * scale * Nn
+    assert np.max(np.abs(got.sum(0, dtype=np.float64) - cols)) < 1e-4 * scale * M
+    B.checkAsyncError()
+
+
 def _qkv(seed):
     r = np.random.default_rng(seed)
     return bf16_round(r.standard_normal((N, 3 * E))), bf16_round(r.standard_normal((N, E)))
