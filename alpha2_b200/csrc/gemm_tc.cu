@@ -657,8 +657,9 @@ template <bool A_MN, bool B_MN, bool WIDE = false>
 static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, const CUtensorMap &tc_,
                                const CUtensorMap &tx, const GemmTcArgs &g, int pairs) {
   using L = GemmSmemLayout<256, true, WIDE>;
-  static int max_pairs = 0;
-  if (!max_pairs) {
+  static int max_pairs = 0, epoch = -1;
+  if (epoch != g_init_epoch) {   // function attributes and cluster capacity belong to the device
+    epoch = g_init_epoch;
     ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_pair_kernel<A_MN, B_MN, WIDE>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
     cudaLaunchConfig_t cfg;
     memset(&cfg, 0, sizeof(cfg));
@@ -737,6 +738,16 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
   g.kb_per_split = (g.kblocks + splits - 1) / splits;
   splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;  // drop empty splits
   g.splits = splits;
+  // C += A*B with nothing else in the epilogue is the residual-add epilogue with C as its own
+  // addend: the old tile arrives by TMA in the staging buffer the new one leaves from, instead
+  // of every lane reading and writing its own row.
+  const size_t oes0 = dtype_size(out_dtype);
+  if (splits == 1 && accumulate && epilogue == ALPHA_EPI_NONE && (C & 15) == 0 && (ldc * oes0) % 16 == 0) {
+    epilogue = ALPHA_EPI_ADD;
+    aux = C;
+    ld_aux = ldc;
+    accumulate = 0;
+  }
   void *ws = nullptr;
   if (splits > 1) {
     if (pool_alloc((size_t)splits * M * N * sizeof(float), &ws)) return 1;

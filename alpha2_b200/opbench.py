@@ -1,6 +1,6 @@
-"""Op microbenchmark over the C ABI (BASELINE configuration 2: the train-step ops alone).
+"""Op microbenchmark over the C ABI (the train-step ops alone, at the GPT-2-124M step's shapes).
 
-    python -m alpha2_b200.opbench [--op NAME ...] [--iters 10] [--json]
+    python -m alpha2_b200.opbench [--op NAME ...] [--iters 10] [--json] [--cublas]
 
 Ops and shapes (bf16 inputs, fp32 accumulation): GEMM forward / dX / dW at
 [16384x768]x[768x{2304,3072}], [16384x3072]x[3072x768] and the lm head [16384x768]x[768x50257]
@@ -13,6 +13,11 @@ launches; a 256 MiB buffer is overwritten between launches so that each one star
 cold L2.  Printed per op: mean device time, achieved TFLOP/s or GB/s from the algorithmic
 work, and the fraction of the measured peak (MEASURED_PEAKS.json: burst figures, since the
 kernel runs alone).
+
+``--cublas`` adds a yardstick column for the GEMM rows: ``torch.matmul`` (cuBLAS) on the same
+shape, layout and leading dimensions, timed the same way (CUDA events, cold L2).  It is there
+only to say what a library GEMM reaches on that shape on that GPU; nothing in the library or
+the train step calls it.
 """
 from __future__ import annotations
 
@@ -40,7 +45,8 @@ def _peaks():
 
 
 class Bench:
-    def __init__(self, iters: int):
+    def __init__(self, iters: int, cublas: bool = False):
+        self.cublas = cublas
         self.B = CudaBackend(0)
         self.lib = self.B.lib
         self.iters = iters
@@ -93,7 +99,42 @@ def gemm_case(b: Bench, layout: str, M: int, N: int, K: int, out_dtype: str = "b
         check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cc.ptr, M, N, K, lda, ldb, ldc, L.BF16, L.DTYPE_CODE[out_dtype],
                                epilogue, aux.ptr if aux is not None else 0, ldc, 0))
     ms = b.time(fn)
-    return {"ms": ms, "work": 2.0 * M * N * K, "kind": "flop"}
+    r = {"ms": ms, "work": 2.0 * M * N * K, "kind": "flop"}
+    if b.cublas and epilogue == L.EPI_NONE:
+        r["cublas_ms"] = cublas_gemm_ms(b, layout, M, N, K, lda, ldb, out_dtype)
+    return r
+
+
+def cublas_gemm_ms(b: Bench, layout: str, M: int, N: int, K: int, lda: int, ldb: int, out_dtype: str) -> float:
+    """torch.matmul on strided views with the same leading dimensions; fp32 output where the
+    library's GEMM writes fp32 (weight gradients) if this torch offers it, else bf16."""
+    import torch
+    dev = torch.device("cuda", 0)
+    rows_a, rows_b = (K if layout == "tn" else M), (N if layout == "nt" else K)
+    a = (torch.randn(rows_a, lda, device=dev) * 0.02).to(torch.bfloat16)
+    bm = (torch.randn(rows_b, ldb, device=dev) * 0.02).to(torch.bfloat16)
+    A = a[:, :M].t() if layout == "tn" else a[:, :K]
+    Bm = bm[:, :K].t() if layout == "nt" else bm[:, :N]
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+    fn = lambda: torch.matmul(A, Bm)
+    if out_dtype == "f32":
+        try:
+            torch.mm(A, Bm, out_dtype=torch.float32)
+            fn = lambda: torch.mm(A, Bm, out_dtype=torch.float32)
+        except Exception:
+            pass
+    for _ in range(3):
+        fn()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total = 0.0
+    for _ in range(b.iters):
+        flush.fill_(1)
+        e0.record()
+        fn()
+        e1.record()
+        e1.synchronize()
+        total += e0.elapsed_time(e1)
+    return total / b.iters
 
 
 def attn_case(b: Bench, Bn=16, H=12, T=1024, D=64, backward=False, dtype="bf16", cap=30.0):
@@ -192,6 +233,10 @@ CASES = {
     "gemm_dw_head": lambda b: gemm_case(b, "tn", 50257, 768, M, "f32"),
     "attn_fwd": lambda b: attn_case(b),
     "attn_bwd": lambda b: attn_case(b, backward=True),
+    "attn_fwd_b8": lambda b: attn_case(b, Bn=8),
+    "attn_bwd_b8": lambda b: attn_case(b, Bn=8, backward=True),
+    "attn_fwd_nocap_b8": lambda b: attn_case(b, Bn=8, cap=0.0),
+    "attn_bwd_nocap_b8": lambda b: attn_case(b, Bn=8, backward=True, cap=0.0),
     "softmax_ce": lambda b: ce_case(b),
     "layernorm_fwd": lambda b: layernorm_case(b),
     "layernorm_bwd": lambda b: layernorm_case(b, backward=True),
@@ -213,15 +258,19 @@ def main():
     ap.add_argument("--op", action="append", choices=sorted(CASES), help="default: all")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", action="store_true")
+    ap.add_argument("--cublas", action="store_true", help="time torch.matmul beside every plain GEMM row")
     args = ap.parse_args()
     tf_peak, gb_peak, src = _peaks()
-    b = Bench(args.iters)
+    b = Bench(args.iters, args.cublas)
     rows = []
     for name in (args.op or list(CASES)):
         r = CASES[name](b)
         if r["kind"] == "flop":
             ach = r["work"] / (r["ms"] * 1e-3) / 1e12
             rows.append({"op": name, "ms": r["ms"], "achieved": ach, "unit": "TFLOP/s", "frac": ach / tf_peak})
+            if "cublas_ms" in r:
+                rows[-1]["cublas_ms"] = r["cublas_ms"]
+                rows[-1]["cublas_tflops"] = r["work"] / (r["cublas_ms"] * 1e-3) / 1e12
         else:
             ach = r["work"] / (r["ms"] * 1e-3) / 1e9
             rows.append({"op": name, "ms": r["ms"], "achieved": ach, "unit": "GB/s", "frac": ach / gb_peak})
@@ -230,7 +279,10 @@ def main():
     else:
         print(f"# peaks: {src} (bf16 {tf_peak} TFLOP/s burst, HBM {gb_peak} GB/s)")
         for r in rows:
-            print(f"{r['op']:20s} {r['ms']:9.4f} ms  {r['achieved']:9.1f} {r['unit']:8s} {100 * r['frac']:5.1f}% of peak")
+            extra = ""
+            if "cublas_ms" in r:
+                extra = f"   | cuBLAS {r['cublas_ms']:8.4f} ms {r['cublas_tflops']:8.1f} TFLOP/s  (ours/cuBLAS {r['achieved'] / r['cublas_tflops']:.2f})"
+            print(f"{r['op']:20s} {r['ms']:9.4f} ms  {r['achieved']:9.1f} {r['unit']:8s} {100 * r['frac']:5.1f}% of peak{extra}")
 
 
 if __name__ == "__main__":

@@ -119,16 +119,21 @@ class DataParallel:
 
     #: gradients are handed to NCCL in groups of about this many bytes (one collective launch each)
     bucket_bytes = 32 << 20
+    #: False turns every exchange into a no-op (each rank then trains on its own gradients):
+    #: a measuring aid for "how much of the exchange is hidden behind backward", nothing else
+    enabled = True
 
     def allreduce(self, grad: TensorData) -> None:
         from ._lib import check
+        if not self.enabled:
+            return
         check(self.backend.lib.alpha_comm_allreduce_sum(grad.ptr, grad.size, self.backend._code(grad.dtype)))
 
     def allreduce_bucket(self, grads: list) -> None:
         """Sum-allreduce several gradient tensors of one dtype as a single NCCL group."""
         import ctypes as C
         from ._lib import check
-        if not grads:
+        if not grads or not self.enabled:
             return
         n = len(grads)
         ptrs = (C.c_uint64 * n)(*[g.ptr for g in grads])
@@ -137,7 +142,8 @@ class DataParallel:
 
     def wait(self) -> None:
         from ._lib import check
-        check(self.backend.lib.alpha_comm_wait())
+        if self.enabled:
+            check(self.backend.lib.alpha_comm_wait())
 
     # ── failure handling ──────────────────────────────────────────────────────
     def leave(self) -> None:

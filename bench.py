@@ -10,8 +10,10 @@ one JSON line.
 
 Keys: ``value`` — whole-job tokens/s with every step's tokens already resident in HBM,
 device-timed with CUDA events on the library's stream, max over ranks; ``e2e`` — the same
-steps driven through the public API with host buffers: per step the tokens/targets are
-copied from pinned host memory and the loss is read back; ``roofline`` — the dominant
+steps driven through the public API with host buffers: per step the product's DataLoader
+draws the batch on the host into page-locked memory, tokens and targets are copied to the
+device and the loss is read back; ``comm`` (N > 1) — step time with and without the gradient
+exchange, i.e. how much of it is exposed; ``roofline`` — the dominant
 kernel family (tensor-core GEMM) timed with events around its launches in a third pass over
 the same steps (events between kernels would stop the launch overlap of the two timed regions,
 which run first, back to back); ``cpu_baseline``
@@ -40,13 +42,13 @@ if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
 WORKLOADS = {
-    # BASELINE configuration 4 — the shape the headline metric is quoted on
+    # GPT-2-small shape (124M), micro-batch 16 per GPU — the shape the headline metric is quoted on
     "gpt2-124m": dict(model=dict(vocabSize=50257, blockSize=1024, nLayer=12, nEmbd=768, nHead=12, tied=True,
                                  init="plain"), micro_batch=16, dtype="bf16"),
-    # BASELINE configuration 3
+    # small GPT: vocab 4096, 6 layers, width 384, context 256, batch 32
     "small-gpt": dict(model=dict(vocabSize=4096, blockSize=256, nLayer=6, nEmbd=384, nHead=6, tied=True,
                                  init="plain"), micro_batch=32, dtype="bf16"),
-    # BASELINE configuration 5: RMSNorm, SwiGLU, RoPE, untied head, 4 accumulated micro-batches per step
+    # GPT 350M shape: RMSNorm, SwiGLU, RoPE, untied head, 4 accumulated micro-batches of 8 per step
     "gpt-350m": dict(model=dict(vocabSize=32768, blockSize=2048, nLayer=24, nEmbd=1024, nHead=16, tied=False,
                                 ffnActivation="swiglu", ffnDim=2816, norm="rms", rope=True, init="plain"),
                      micro_batch=8, accum=4, dtype="bf16"),
@@ -139,6 +141,21 @@ def oracle_step_rate(model: dict, sample_T: int, steps: int, warmup: int) -> dic
     return {"tokens_per_s": steps * sample_T / dt, "seconds": dt, "ms_per_step": 1e3 * dt / steps}
 
 
+def profiled_traffic():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of the dominant kernel, taken
+    from the ncu summary committed under profiles/ (the MLP up-projection forward GEMM,
+    16384 x 3072 x 768).  (None, None) when the summary is missing."""
+    import re
+    name = "gemm_tc_pair_kernel_fc1_fwd_16384x3072x768.md"
+    try:
+        text = open(os.path.join(ROOT, "profiles", name)).read()
+        rd = float(re.search(r"dram__bytes_read\.sum\s*\|\s*([0-9.]+)\s*MB", text).group(1))
+        wr = float(re.search(r"dram__bytes_write\.sum\s*\|\s*([0-9.]+)\s*MB", text).group(1))
+        return (rd + wr) * 1e6, f"profiles/{name}"
+    except Exception:
+        return None, None
+
+
 def host_threads() -> int:
     try:
         return len(os.sched_getaffinity(0))
@@ -152,12 +169,18 @@ def run_reference(args, wl) -> None:
         return
     model = wl["model"]
     total = max(1, args.steps + args.warmup)
-    # ~76 ms per token per step for the 124M shape on 8 cores: keep the whole run near 2 minutes
-    per_tok = 0.076 * flops_per_token(model) / flops_per_token(WORKLOADS["gpt2-124m"]["model"])
-    budget_tokens = 120.0 / total / max(per_tok, 1e-9)
-    T = model["blockSize"]
-    while T > 32 and T > budget_tokens:
+    # One sequence per step, as long as the in-run cpu_baseline's (256 tokens) when the whole
+    # --steps/--warmup run then stays near four minutes: ~18 ms per token per step for the 124M
+    # shape on 16 host threads, scaled by the model's FLOPs per token.
+    per_tok = 0.018 * flops_per_token(model) / flops_per_token(WORKLOADS["gpt2-124m"]["model"])
+    T = min(256, model["blockSize"])
+    while T > 32 and total * T * per_tok > 240.0:
         T //= 2
+    try:                                         # torchrun exports OMP_NUM_THREADS=1; the CPU arm may use every core
+        from threadpoolctl import threadpool_limits
+        threadpool_limits(limits=host_threads())
+    except Exception:
+        pass
     r = oracle_step_rate(model, T, args.steps, args.warmup)
     sample = f"1 sequence x {T} tokens per step, full {model['nLayer']}-layer model, fp32 storage / f64 accumulate"
     line = {
@@ -184,6 +207,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gpt2-124m", choices=sorted(WORKLOADS))
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--repeats", type=int, default=3, help="timed repetitions of the resident-token region (median reported)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
     if args.impl == "reference":
@@ -299,7 +323,24 @@ def main() -> None:
     launches = B.launch_count() - launches0
     final_loss = last["r"]["lossTensor"].item()
 
+    # more runs of the same region: the figure reported is the median (single regions of a few
+    # hundred milliseconds move by a percent or so with the clock)
+    runs_a = [ms_a]
+    for _ in range(max(0, args.repeats - 1)):
+        runs_a.append(timed(region_a))
+    ms_a = statistics.median(runs_a)
+
     # ── region B: end to end through the public API with host buffers ───────────────────
+    # Batches come from the product's DataLoader over a synthetic token stream in page-locked
+    # memory (two slots, guarded by events): per step it draws the windows on the host, copies
+    # tokens and targets to the device asynchronously and the step consumes them.
+    from alpha2_b200.data import DataLoader
+    from alpha2_b200.rng import SeededRng
+    corpus = np.concatenate([t.reshape(-1) for t, _ in host_batches[:64]])
+    loader = DataLoader(corpus, SeededRng(7 + rank), mb, T, backend=B, pin=True)
+
+    def loader_tokens():
+        return [loader.nextDeviceBatch() for _ in range(accum)]
     losses = []
 
     def region_b():
@@ -308,13 +349,15 @@ def main() -> None:
         # so the host never stalls the device (the last one is collected inside the region).
         pending = None
         for i in range(args.steps):
-            out = tr.train_step(device_tokens(args.warmup + i), read_back=False)
+            out = tr.train_step(loader_tokens(), read_back=False)
             nxt = B.readScalarAsync(out["lossTensor"])
             if pending is not None:
                 losses.append(pending.get())
             pending = nxt
         losses.append(pending.get())
+    region_b_warm = tr.train_step(loader_tokens(), read_back=True)     # first use of the loader's buffers, untimed
     ms_b = timed(region_b)
+    loader.close()
     clocks = sampler.stop() if rank == 0 else {}
     # ── region P: the steps of region A once more with per-kernel-family event timing switched
     # on (kept out of regions A and B: an event record between two kernels stops their overlap;
@@ -324,6 +367,16 @@ def main() -> None:
     check(lib.alpha_profile_enable(0))
     prof = (L.ProfileEntry * len(L.PROFILE_CATEGORIES))()
     check(lib.alpha_profile_read(prof, len(L.PROFILE_CATEGORIES)))
+    # ── region C (multi-GPU only, last: the replicas drift apart in it): the steps of region A
+    # with the gradient exchange switched off, so that "step time minus compute-only step time"
+    # says how much of the exchange is exposed ──
+    ms_c = None
+    if dp is not None:
+        ms_c_ref = timed(region_a)                 # with the exchange, directly before
+        dp.enabled = False
+        ms_c = timed(region_a)
+        dp.enabled = True
+
     del resident
 
     B.checkAsyncError()
@@ -347,6 +400,7 @@ def main() -> None:
         if e.launches:
             profile[name] = {"ms_per_step": e.ms / args.steps, "launches_per_step": e.launches / args.steps,
                              "work_per_step": e.work / args.steps}
+    traffic, traffic_src = (profiled_traffic() if args.workload == "gpt2-124m" else (None, None))
     line = {
         "metric": "train tokens/s", "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": ms_a / args.steps, "higher_is_better": True, "scaling": "weak",
@@ -355,7 +409,11 @@ def main() -> None:
                    "micro_batch_per_gpu": mb, "grad_accum_steps": accum, "tokens_per_step": tokens_per_step, "tied_embeddings": bool(model.get("tied")),
                    "precision": "bf16 activations and weight shadows, fp32 master weights and AdamW state",
                    "parallelism": f"dp{world}", "l2": "inputs larger than L2 (each step streams >10 GB of activations and weights)",
-                   "tokens": "Zipf(s=1.1), seeded per rank"},
+                   "tokens": "Zipf(s=1.1), seeded per rank",
+                   "attention": "causal, scores soft-capped at 30*tanh(s/30) as in the reference model (gpt.ts:244)"
+                   if model.get("softCap", None) in (None, 30.0) else f"causal, softCap {model.get('softCap')}",
+                   "timed_region": f"{args.steps} steps, median of {len(runs_a)} repetitions"},
+        "ms_per_step_runs": [m / args.steps for m in runs_a],
         "e2e": {"value": e2e, "unit": "tokens/s", "h2d_bytes_per_step": 2 * tok_bytes * accum, "d2h_bytes_per_step": 4,
                 "ms_per_step": ms_b / args.steps},
         "gpu_launches": launches,
@@ -365,13 +423,15 @@ def main() -> None:
         "roofline": {"bound": "tensor", "kernel": "gemm_tc_pair_kernel (bf16 tcgen05 GEMM, CTA pairs, all layouts)",
                      "achieved": achieved,
                      "peak": peak_tf, "unit": "TFLOP/s", "frac": (achieved / peak_tf) if achieved else None,
-                     # DRAM bytes of one profiled launch (the 16384 x 3072 x 768 forward GEMM: 30.0 MB read +
-                     # 41.6 MB written, against 130.6 MB algorithmic: part of the output stays in L2)
-                     "traffic": 71.6e6 if args.workload == "gpt2-124m" else None,
-                     "traffic_launch": "fc1 forward 16384x3072x768, one ncu capture" if args.workload == "gpt2-124m" else None,
+                     # DRAM bytes of one profiled launch, read from the committed ncu summary of that launch
+                     "traffic": traffic, "traffic_launch": traffic_src,
                      "peak_source": f"{peaks['source']} cuBLAS bf16, sustained",
                      "launches_per_step": gemm.launches / args.steps, "ms_per_step": gemm.ms / args.steps},
         "profile": profile, "profile_pass_ms_per_step": ms_p / args.steps,
+        "comm": ({"compute_only_ms_per_step": ms_c / args.steps,
+                  "exposed_ms_per_step": (ms_c_ref - ms_c) / args.steps,
+                  "note": "the timed region run once more with the exchange, minus the same steps with the "
+                          "gradient exchange switched off directly after it"} if ms_c is not None else None),
         "final_loss": final_loss,
     }
     if world == 1 and not args.no_cpu_baseline:

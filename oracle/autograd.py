@@ -9,7 +9,7 @@ transpose+matmul for ``matmulTransposed`` (ops.ts:200-234), the composed ``softC
 (:329-340), host-loop GELU backward (:404-418, :451-466), layerNorm backward (:523-569),
 embedding scatter-add (:495-505) and cross-entropy backward (:713-727).
 
-Extensions that BASELINE's configurations ask for but the reference lacks (RMSNorm, RoPE,
+Extensions that the benchmarked model shapes need but the reference lacks (RMSNorm, RoPE,
 tied head) are written in the same discipline (f64 arithmetic, f32 stores per op) and
 marked EXTENSION.
 """

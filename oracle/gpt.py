@@ -8,7 +8,7 @@ backend (cpu_ref has no flashAttention hook).  ``flash_attention_dense`` restate
 contract of the optional hook (``packages/core/src/interfaces.ts:127-135``) for op-level
 tests, including the raw-reshape head layout of gpt.ts:250-254.
 
-EXTENSIONS (asked for by BASELINE's configurations, absent from the reference):
+EXTENSIONS (needed by the benchmarked model shapes, absent from the reference):
 ``tied`` (lm head shares wte; follows the reference's own written plan in
 docs/GPT2-PLAN.md:68-88), ``norm="rms"``, ``rope``, and ``init="plain"`` (every linear and
 embedding weight N(0, 0.02) without the residual-scaled std).

@@ -168,7 +168,7 @@ class Trainer:
 
 
 def uniform_batches(seed: int, n_steps: int, batch: int, T: int, vocab: int):
-    """Synthetic data of configuration 1: each row is a window of T+1 tokens drawn uniform
+    """Synthetic data of the tiny byte-level GPT: each row is a window of T+1 tokens drawn uniform
     in [0, vocab); inputs are w[:-1], targets w[1:].  (The reference draws windows from a
     tokenised text file, packages/train/src/data.ts:18-119; no text corpus is used here.)"""
     g = np.random.default_rng(seed)
@@ -180,7 +180,7 @@ def uniform_batches(seed: int, n_steps: int, batch: int, T: int, vocab: int):
 
 
 def zipf_batches(seed: int, n_steps: int, batch: int, T: int, vocab: int, s: float = 1.1):
-    """Synthetic data of configurations 3-5: token ids Zipf(s) over the vocabulary
+    """Synthetic data of the larger model shapes: token ids Zipf(s) over the vocabulary
     (p(k) ~ 1/(k+1)^s), same windowing as uniform_batches."""
     g = np.random.default_rng(seed)
     p = 1.0 / np.power(np.arange(1, vocab + 1, dtype=f64), s)

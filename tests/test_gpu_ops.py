@@ -497,6 +497,52 @@ def test_gradients_added_inside_the_gemm(B, dtype, shape):
     B.checkAsyncError()
 
 
+K_BALANCED = [
+    # (layout, M, N, K, out): few output tiles, long K -> K is split
+    ("tn", 2304, 768, 16384, "f32"), ("tn", 768, 768, 16384, "f32"), ("tn", 768, 3072, 8192, "f32"),
+    ("tn", 1000, 520, 8200, "f32"),            # ragged M, N (rows and columns beyond the matrix in the last tiles), ragged K
+    ("nt", 512, 512, 16384, "bf16"),           # bf16 output through the scalar reduce path
+    ("nn", 300, 264, 12288, "f32"),
+    ("tn", 128, 768, 16384, "f32"),            # M <= 128: single-CTA kernel, 128 x 256 tiles
+    ("tn", 768, 128, 16384, "f32"),            # N <= 128: 128 x 128 tiles
+]
+
+
+@pytest.mark.parametrize("layout,M,N,K,out", K_BALANCED)
+@pytest.mark.parametrize("accumulate", [0, 1])
+def test_gemm_split_over_k_adds_partials_in_a_fixed_order(B, layout, M, N, K, out, accumulate):
+    """The weight-gradient GEMMs split K across the device: partial products meet in an fp32
+    workspace and are added in split order.  Result against the f64 product; five launches must
+    agree bit for bit; accumulate adds to what C held; a different split shape in between must
+    not disturb anything."""
+    from alpha2_b200 import _lib as L
+    from alpha2_b200._lib import check
+    r = rng(M + 3 * N + K)
+    sa, sb = shapes_for(layout, M, N, K)
+    a = bf16_round(r.standard_normal(sa) * 0.05)
+    b = bf16_round(r.standard_normal(sb) * 0.05)
+    c0 = bf16_round(r.standard_normal((M, N))) if accumulate else np.zeros((M, N), f32)
+    A, Bm = B.upload(a, "bf16"), B.upload(b, "bf16")
+    code = {"nt": L.GEMM_NT, "nn": L.GEMM_NN, "tn": L.GEMM_TN}[layout]
+    ref = c0.astype(np.float64) + gemm_ref(layout, a, b)
+    outs = []
+    other = B.upload(bf16_round(r.standard_normal((4096, 256)) * 0.05), "bf16")
+    for rep in range(5):
+        Cm = B.upload(c0, out)
+        check(B.lib.alpha_gemm(code, A.ptr, Bm.ptr, Cm.ptr, M, N, K, sa[1], sb[1], N, L.BF16, L.DTYPE_CODE[out],
+                               L.EPI_NONE, 0, 0, accumulate))
+        Cm.invalidate_host()
+        outs.append(np.array(Cm.data))
+        if rep == 1:
+            B.matmulTransposedA(other, other)                # [256, 256] from K = 4096: one shared tile
+    scale = float(np.sqrt(K)) * 0.05 * 0.05
+    tol = (scale * 1e-5 * 16 + 1e-12) if out == "f32" else (2 ** -7 * (float(np.abs(ref).max()) + scale))
+    assert float(np.abs(outs[0] - ref).max()) < tol
+    for o in outs[1:]:
+        assert np.array_equal(o, outs[0])
+    B.checkAsyncError()
+
+
 # ── attention ───────────────────────────────────────────────────────────────
 @pytest.mark.parametrize("cfg", [(3, 64, 16, 30.0), (2, 100, 64, 30.0), (2, 256, 64, 0.0), (1, 130, 32, 2.0),
                                  (1, 192, 128, 30.0),

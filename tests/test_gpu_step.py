@@ -1,5 +1,6 @@
 """Train-step parity on the GPU: the CUDA backend against the oracle on identical seeded
-weights and tokens (BASELINE configurations 1 and 3; reduced-size stand-ins for 4 and 5).
+weights and tokens (the tiny byte-level GPT and the small GPT, plus reduced-size stand-ins of
+the GPT-2-124M and 350M shapes; the full shapes are in tests/test_gpu_step_golden.py).
 
 Tolerances (north star): fp32 path — loss within 1e-4 relative per step; every parameter
 tensor within 1e-4 relative (L2) plus an absolute floor of a few learning-rate quanta
@@ -70,13 +71,14 @@ C1_TRAIN = dict(iters=20, batchSize=4, lr=3e-4, beta1=0.9, beta2=0.95, eps=1e-8,
 
 @pytest.mark.parametrize("route,fused", [("fused", True), ("standard", False), ("flash", False)])
 def test_config1_fp32_20_steps(B, route, fused):
-    """Configuration 1, reference-faithful (untied head, soft cap 30, residual-scaled init)."""
+    """The tiny byte-level GPT (vocab 256, 2 layers, width 64, 4 heads, context 64, batch 4),
+    reference-faithful: untied head, soft cap 30, residual-scaled init."""
     batches = otrain.uniform_batches(123, 20, 4, 64, 256)
     run_parity(B, C1, C1_TRAIN, batches, route, fused, 20, 1e-4, 1e-4)
 
 
 def test_config1_literal_tied_head(B):
-    """Configuration 1 as BASELINE words it: N(0, 0.02) everywhere, tied embeddings."""
+    """The tiny byte-level GPT with N(0, 0.02) everywhere and tied embeddings."""
     batches = otrain.uniform_batches(124, 20, 4, 64, 256)
     run_parity(B, {**C1, "tied": True, "init": "plain"}, C1_TRAIN, batches, "fused", True, 20, 1e-4, 1e-4)
 
@@ -118,8 +120,9 @@ C3_TRAIN = dict(iters=100, batchSize=32, lr=3e-4, seed=42)
 
 
 def test_config3_fp32(B):
-    """Configuration 3 in fp32 against the oracle (batch reduced to 4 rows so that the CPU
-    oracle finishes in seconds; the full batch runs in bench.py)."""
+    """The small GPT (vocab 4096, 6 layers, width 384, context 256) in fp32 against the oracle
+    run at test time: batch reduced to 4 rows so that the CPU oracle finishes in seconds.  Batch
+    32 for 100 steps is compared with a committed oracle trajectory in test_gpu_step_golden.py."""
     batches = otrain.zipf_batches(5, 3, 4, 256, 4096)
     run_parity(B, C3, C3_TRAIN, batches, "fused", True, 3, 1e-4, 1e-4)
 
