@@ -19,6 +19,7 @@
 // Two CTAs fit on an SM (96 KB shared memory, 256 TMEM columns each), so one CTA's softmax
 // overlaps the other's MMAs.  Single CTAs (no cluster).  Every wait is bounded.
 // Model work: forward 4*B*H*T^2*D flop (causal tiles are skipped, so about half is executed).
+#include <stdlib.h>
 #include <string.h>
 
 #include <mutex>
@@ -292,19 +293,23 @@ attn_tc_fwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
 }
 
 // ── backward ────────────────────────────────────────────────────────────────
-// Two kernels, each output tile owned by one CTA (no atomics: gradients are reproducible):
-//   dK/dV kernel: CTA = (batch, head, 128 keys), loops over the query blocks at or after it;
-//   dQ    kernel: CTA = (batch, head, 128 queries), loops over the key blocks at or before it.
-// Per (query block, key block) pair both recompute S = Q K^T and dP = dO V^T on the tensor
-// cores into TMEM; sixteen math warps (32 query rows x 32 key columns each) turn them into
-// P = exp2(x2 - lse2) and dS = P*(dP - D)*(1 - tanh^2)*scale, round to bf16 and store them as
-// [query rows][key columns] 128B-swizzled tiles.  That one layout serves both remaining
-// products: read K-major it is the A operand of dQ += dS K, read M-major it is the A operand
-// of dV += P^T dO and dK += dS^T Q (the tensor core transposes through the descriptor).
-// Q, dO, K, V tiles are likewise used both K-major (score products) and N-major (gradient
-// products) from the same bytes.  The streamed operand pair comes through a 4-stage TMA ring.
+// One pass over the causal (query block, key block) tiles; every output element has one owner
+// and nothing is added with atomics, so gradients are bit-reproducible:
+//   main kernel: CTA = (batch, head, 128 keys), loops over the query blocks at or after it.
+//     Per tile it computes S = Q K^T and dP = dO V^T on the tensor cores into TMEM; sixteen math
+//     warps (32 query rows x 32 key columns each) turn them into P = exp2(x2 - lse2) and
+//     dS = P*(dP - D)*(1 - tanh^2)*scale, round to bf16 and store them as
+//     [query rows][key columns] 128B-swizzled tiles; three products follow: dV += P^T dO and
+//     dK += dS^T Q (accumulated in TMEM over the item, the tiles read M-major: the tensor core
+//     transposes through the descriptor) and the tile's contribution to dQ, dS K (dS read
+//     K-major, K read N-major), which goes out as fp32 to a workspace slab per (query block,
+//     key block) — 5 products and one pass of the score arithmetic per tile;
+//   reduce kernel: dQ[query block] = the slabs of its key blocks added in key-block order.
+// Q, dO, K, V tiles are used both K-major (score products) and N-major (gradient products)
+// from the same bytes.  (Q, dO) pairs stream through a 3-stage TMA ring.
 struct AttnBwdArgs {
   void *dq, *dk, *dv;
+  float *dq_part;   // fp32 dQ contributions, [batch*head][pair(qb, kb) = qb(qb+1)/2 + kb][128 rows][64]
   const float *lse, *delta;
   int64_t q_sb, q_sh, q_st;
   int H, T;
@@ -490,54 +495,64 @@ __device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0,
 }
 
 // shared-memory map of the dK/dV kernel
-constexpr int AK_STAGES = 4;                               // ring of (Q, dO) tiles
-constexpr int AK_K = 0;
-constexpr int AK_V = AT_TILE;
-constexpr int AK_Q = 2 * AT_TILE;
+constexpr int AK_STAGES = 3;                               // ring of (Q, dO) tiles
+constexpr int AK_K = 0;                                    // 2 buffers (items alternate)
+constexpr int AK_V = 2 * AT_TILE;
+constexpr int AK_Q = 3 * AT_TILE;
 constexpr int AK_DO = AK_Q + AK_STAGES * AT_TILE;
 constexpr int AK_P = AK_DO + AK_STAGES * AT_TILE;          // 2 tiles (key halves)
 constexpr int AK_DS = AK_P + 2 * AT_TILE;                  // 2 tiles
-constexpr int AK_BAR = AK_DS + 2 * AT_TILE;
+constexpr int AK_STG = AK_DS + 2 * AT_TILE;                // dQ staging: 4 epilogue warps x (32 rows x 128 bytes)
+constexpr int AK_BAR = AK_STG + 4 * 4096;
 constexpr int AK_DYN = AK_BAR + 256 + 1024;
 constexpr int ABP_THREADS = AB_THREADS + 128;              // + four epilogue warps
 
-// Pipeline of the dK/dV kernel.  One CTA per SM walks (batch*head, key block) items, longest
+// Pipeline of the backward kernel.  One CTA per SM walks (batch*head, key block) items, longest
 // first; inside an item the tile index `it` walks the query blocks of the key block:
-//   tensor core, on "tile it-1 stored" : dP(it)  ->  dV,dK += (P,dS)(it-1)  ->  S(it+1)
+//   tensor core, on "tile it-1 stored" : dP(it) -> dQ(it-1), dV,dK += (P,dS)(it-1) -> S(it+1)
 //   math warps                          : phase A(it) from S(it) | wait dP(it) and the end of
-//                                         dV,dK(it-1) | phase B(it) stores P,dS | signal
-//   epilogue warps (one per lane quadrant): when an item's last products are done they write
+//                                         the products of tile it-1 | phase B(it) stores P,dS
+//   epilogue warps (one per lane quadrant): every tile they move its dQ contribution TMEM ->
+//                                         swizzled shared memory -> TMA store to the workspace;
+//                                         when an item's last products are done they write
 //                                         dV, dK while everybody else is on the next item
 // S has two TMEM buffers, so the scores of the next tile are ready before the math warps ask
-// for them.  K and V of the next item are fetched as soon as the current item's last dP has
-// been issued (the gradient products do not read them).  All barrier phases are running
-// counters over items (n) and tiles (t).
+// for them; the dQ contribution of a tile is written over that tile's (long consumed) scores
+// and the buffer takes new scores once the epilogue warps have read it out.  K has two
+// buffers: the item's last dQ product still reads it when the next item begins, so the next K
+// is fetched with the item's last (Q, dO) pair; V is free after the item's last dP.  All
+// barrier phases are running counters over items (n) and tiles (t).
 __global__ void __launch_bounds__(ABP_THREADS, 1)
-attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
+attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                        const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                       AttnBwdArgs a, int n_items, int BH) {
+                       const __grid_constant__ CUtensorMap tmap_part, AttnBwdArgs a, int n_items, int BH) {
   extern __shared__ uint8_t at_smem_raw[];
   uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t sb = smem_u32(smem);
   const uint32_t bar = sb + AK_BAR;
-  const uint32_t kv_full = bar, kv_empty = bar + 8, s_full0 = bar + 16, dp_full = bar + 32, pds_ready = bar + 40,
-                 acc_done = bar + 48, acc_final = bar + 56, acc_free = bar + 64, q_full0 = bar + 72,
+  const uint32_t v_full = bar, v_empty = bar + 8, s_full0 = bar + 16, dp_full = bar + 32, pds_ready = bar + 40,
+                 acc_done = bar + 48, acc_final = bar + 56, acc_free = bar + 64, dq_full0 = bar + 72,
+                 dq_free0 = bar + 88, k_full0 = bar + 104, k_empty0 = bar + 120, q_full0 = bar + 136,
                  q_empty0 = q_full0 + 8 * AK_STAGES;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 72 + 16 * AK_STAGES);
+  uint32_t *tmem_slot = (uint32_t *)(smem + AK_BAR + 136 + 16 * AK_STAGES);
   volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n_qb = (a.T + 127) / 128;
   constexpr uint32_t TMEM_COLS = 512;
 
   if (threadIdx.x == 0) {
-    mbar_init(kv_full, 1);
-    mbar_init(kv_empty, 1);
+    mbar_init(v_full, 1);
+    mbar_init(v_empty, 1);
+    mbar_init(k_full0, 1); mbar_init(k_full0 + 8, 1);
+    mbar_init(k_empty0, 1); mbar_init(k_empty0 + 8, 1);
     mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
     mbar_init(dp_full, 1);
     mbar_init(pds_ready, AB_MATH_WARPS);
     mbar_init(acc_done, 1);
     mbar_init(acc_final, 1);
     mbar_init(acc_free, 4);
+    mbar_init(dq_full0, 1); mbar_init(dq_full0 + 8, 1);
+    mbar_init(dq_free0, 4); mbar_init(dq_free0 + 8, 4);
     for (int s = 0; s < AK_STAGES; s++) {
       mbar_init(q_full0 + 8 * s, 1);
       mbar_init(q_empty0 + 8 * s, 1);
@@ -557,6 +572,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
   const uint32_t tmem_base = *tmem_slot;
   const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdV = tmem_base + 384, tdK = tmem_base + 448;
+  const int n_pairs = n_qb * (n_qb + 1) / 2;
 
   // item -> (batch*head, key block): key block 0 has the most query blocks to visit
   auto decode = [&](int item, int &bh, int &kb) {
@@ -572,11 +588,20 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       int bh, kb;
       decode(item, bh, kb);
       const int b = bh / a.H, h = bh - b * a.H, n_it = n_qb - kb;
-      if (!mbar_wait(kv_empty, (n & 1) ^ 1, abort_flag)) break;
+      // K has two buffers (items alternate): the item's last dQ product still reads it while the
+      // next item starts, so the next K is fetched ahead, with this item's last tile (below); the
+      // very first K is fetched here.  V is free after the item's last dP and has one buffer.
+      if (n == 0) {
+        if (elect_one()) {
+          mbar_expect_tx(k_full0, AT_TILE);
+          tma_load_4d(sb + AK_K, &tmap_k, k_full0, 0, kb * 128, h, b);
+        }
+        __syncwarp();
+      }
+      if (!mbar_wait(v_empty, (n & 1) ^ 1, abort_flag)) break;
       if (elect_one()) {
-        mbar_expect_tx(kv_full, 2 * AT_TILE);
-        tma_load_4d(sb + AK_K, &tmap_k, kv_full, 0, kb * 128, h, b);
-        tma_load_4d(sb + AK_V, &tmap_v, kv_full, 0, kb * 128, h, b);
+        mbar_expect_tx(v_full, AT_TILE);
+        tma_load_4d(sb + AK_V, &tmap_v, v_full, 0, kb * 128, h, b);
       }
       __syncwarp();
       for (int it = 0; it < n_it; it++, t++) {
@@ -589,25 +614,46 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           tma_load_4d(sb + AK_DO + st * AT_TILE, &tmap_do, q_full0 + 8 * st, 0, q0, h, b);
         }
         __syncwarp();
+        if (it == n_it - 1) {   // all of this item's tiles are on their way: now the next item's K
+          const int nxt = snake_item(n + 1);
+          if (nxt < n_items) {
+            int bh2, kb2;
+            decode(nxt, bh2, kb2);
+            const int b2 = bh2 / a.H, h2 = bh2 - b2 * a.H, kbuf = (n + 1) & 1;
+            // the buffer's previous tenant was item n - 1
+            if (!mbar_wait(k_empty0 + 8 * kbuf, (((n + 1) >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+            if (elect_one()) {
+              mbar_expect_tx(k_full0 + 8 * kbuf, AT_TILE);
+              tma_load_4d(sb + AK_K + kbuf * AT_TILE, &tmap_k, k_full0 + 8 * kbuf, 0, kb2 * 128, h2, b2);
+            }
+            __syncwarp();
+          }
+        }
       }
     }
   } else if (warp == 1) {
     // MMA issuer: warp-uniform control flow and descriptors, one elected lane issues
     constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);   // [q x k] = A[q,d] B[k,d]^T
     constexpr uint32_t idesc_g = make_idesc_bf16(128, 64, true, true);      // [k x d] = A[q,k]^T B[q,d]
-    const uint64_t d_k = make_smem_desc(sb + AK_K, 16, 1024), d_v = make_smem_desc(sb + AK_V, 16, 1024);
+    const uint64_t d_k0 = make_smem_desc(sb + AK_K, 16, 1024), d_v = make_smem_desc(sb + AK_V, 16, 1024);
     const uint64_t d_q_k = make_smem_desc(sb + AK_Q, 16, 1024), d_do_k = make_smem_desc(sb + AK_DO, 16, 1024);
     const uint64_t d_q_n = make_smem_desc(sb + AK_Q, AT_TILE, 1024), d_do_n = make_smem_desc(sb + AK_DO, AT_TILE, 1024);
     const uint64_t d_p = make_smem_desc(sb + AK_P, AT_TILE, 1024), d_ds = make_smem_desc(sb + AK_DS, AT_TILE, 1024);
+    // dQ(tile) = dS K, [q x d] = A[q,k] B[k,d]: dS read K-major, K read N-major
+    constexpr uint32_t idesc_dq = make_idesc_bf16(128, 64, false, true);
+    const uint64_t d_ds_k = make_smem_desc(sb + AK_DS, 16, 1024), d_k_n0 = make_smem_desc(sb + AK_K, AT_TILE, 1024);
     int t = 0, n = 0;
     bool ok = true;
     for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, kb;
       decode(item, bh, kb);
       const int n_it = n_qb - kb;
+      const uint64_t d_k = d_k0 + (uint64_t)(((n & 1) * AT_TILE) >> 4), d_k_n = d_k_n0 + (uint64_t)(((n & 1) * AT_TILE) >> 4);
       auto issue_s = [&](int it) -> bool {   // S(it) = Q(it) K^T into buffer (t + it) & 1 (waits for the tile's loads)
         const int tt = t + it, st = tt % AK_STAGES;
         if (!mbar_wait(q_full0 + 8 * st, (tt / AK_STAGES) & 1, abort_flag)) return false;
+        // the buffer last held the dQ contribution of tile tt - 2; it must have been read out
+        if (tt >= 2 && !mbar_wait(dq_free0 + 8 * (tt & 1), ((tt - 2) >> 1) & 1, abort_flag)) return false;
         tc_fence_after();
         const uint64_t qd = d_q_k + (uint64_t)((st * AT_TILE) >> 4);
         const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1);
@@ -626,11 +672,11 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
 #pragma unroll
           for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, dd + kk * 2, d_v + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
           mma_commit(dp_full);
-          if (last) mma_commit(kv_empty);    // K and V are not read after the item's last dP
+          if (last) mma_commit(v_empty);       // V is not read after the item's last dP
         }
         __syncwarp();
       };
-      ok = mbar_wait(kv_full, n & 1, abort_flag);
+      ok = mbar_wait(k_full0 + 8 * (n & 1), (n >> 1) & 1, abort_flag) && mbar_wait(v_full, n & 1, abort_flag);
       if (ok) ok = issue_s(0);
       if (ok) issue_dp(0);
       if (ok && n_it > 1) ok = issue_s(1);
@@ -647,6 +693,15 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
         const uint32_t first = it > 0 ? 1u : 0u, freed = q_empty0 + 8 * st;
         const bool last = it == n_it - 1;
         if (elect_one()) {
+          {
+            // this tile's dQ contribution goes where its scores were: phase A has long consumed them
+            const uint32_t tdq = tS0 + (tt & 1) * 128;
+#pragma unroll
+            for (int kk = 0; kk < 8; kk++)  // 16 keys per step; dS tile (kk >> 2), 32 bytes per step inside it
+              mma_bf16_ss(tdq, d_ds_k + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), d_k_n + kk * 128,
+                          idesc_dq, kk > 0 ? 1u : 0u);
+            mma_commit(dq_full0 + 8 * (tt & 1));
+          }
 #pragma unroll
           for (int kk = 0; kk < 8; kk++)  // 16 query rows per step
             mma_bf16_ss(tdV, d_p + kk * 128, don + kk * 128, idesc_g, kk > 0 ? 1u : first);
@@ -654,7 +709,10 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
           for (int kk = 0; kk < 8; kk++) mma_bf16_ss(tdK, d_ds + kk * 128, qn + kk * 128, idesc_g, kk > 0 ? 1u : first);
           mma_commit(freed);
           mma_commit(acc_done);
-          if (last) mma_commit(acc_final);
+          if (last) {
+            mma_commit(acc_final);
+            mma_commit(k_empty0 + 8 * (n & 1));  // the last dQ product was the last reader of K
+          }
         }
         __syncwarp();
         if (it + 2 < n_it) ok = issue_s(it + 2);
@@ -716,11 +774,53 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
     const int quad = warp & 3;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    int n = 0;
-    for (int item = snake_item(0); item < n_items; item = snake_item(++n)) {
+    int n = 0, t = 0;
+    bool ok = true;
+    uint8_t *stg = smem + AK_STG + quad * 4096;
+    const uint32_t stg_u32 = sb + AK_STG + quad * 4096;
+    if (lane == 0) tma_prefetch_desc(&tmap_part);
+    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
       int bh, kb;
       decode(item, bh, kb);
       const int b = bh / a.H, h = bh - b * a.H;
+      {
+        // every tile: this quadrant's 32 query rows of the tile's dQ contribution, fp32, to the
+        // workspace slab of (query block, key block); the TMEM columns go back to the scores at once
+        const int n_it = n_qb - kb;
+        for (int it = 0; it < n_it; it++) {
+          const int tt = t + it, qb = kb + it;
+          if (!mbar_wait(dq_full0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t tdq = tS0 + (tt & 1) * 128 + lane_off;
+          // workspace row of this warp's first query row: slab (bh, pair(qb, kb)), 128 rows each
+          const int part_row0 = (bh * n_pairs + (qb * (qb + 1) / 2 + kb)) * 128 + quad * 32;
+#pragma unroll 1
+          for (int c = 0; c < 2; c++) {         // columns 0-31, 32-63: one 128B-swizzled box of 32 rows each
+            uint32_t r[32];
+            tmem_ld_32x32(tdq + c * 32, r);
+            tmem_ld_wait();
+            if (c == 1) {   // both halves have been read: the columns may take new scores
+              tc_fence_before();
+              __syncwarp();
+              if (lane == 0) mbar_arrive(dq_free0 + 8 * (tt & 1));
+            }
+            if (lane == 0) bulk_wait_read<0>();   // the previous box has left the staging buffer
+            __syncwarp();
+            uint8_t *bp = stg + lane * 128;
+#pragma unroll
+            for (int q = 0; q < 8; q++)
+              *reinterpret_cast<uint4 *>(bp + ((q ^ (lane & 7)) << 4)) = make_uint4(r[4 * q], r[4 * q + 1], r[4 * q + 2], r[4 * q + 3]);
+            fence_proxy_async();
+            __syncwarp();
+            if (lane == 0) {
+              tma_store_2d(&tmap_part, stg_u32, c * 32, part_row0);
+              bulk_commit();
+            }
+          }
+        }
+        t += n_it;
+        if (!ok) break;
+      }
       if (!mbar_wait(acc_final, n & 1, abort_flag)) break;
       tc_fence_after();
       const int kj = kb * 128 + row;  // accumulator lanes are keys
@@ -747,6 +847,7 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_free);
     }
+    if (lane == 0) bulk_wait<0>();   // this warp's last dQ boxes have landed
   }
 
   if (*abort_flag) {
@@ -763,253 +864,43 @@ attn_tc_bwd_dkv_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_
   }
 }
 
-// shared-memory map of the dQ kernel
-constexpr int AQ_STAGES = 4;                               // ring of (K, V) tiles
-constexpr int AQ_Q = 0;
-constexpr int AQ_DO = AT_TILE;
-constexpr int AQ_K = 2 * AT_TILE;
-constexpr int AQ_V = AQ_K + AQ_STAGES * AT_TILE;
-constexpr int AQ_DS = AQ_V + AQ_STAGES * AT_TILE;          // 2 tiles (key halves)
-constexpr int AQ_BAR = AQ_DS + 2 * AT_TILE;
-constexpr int AQ_DYN = AQ_BAR + 256 + 1024;
-
-// Same pipeline as the dK/dV kernel with the roles of the operands exchanged: items are
-// (batch*head, query block), the tile index j walks the key blocks of the query block,
-// (K, V) tiles come through the ring, Q and dO are the per-item operands, and the only
-// gradient product is dQ += dS K.
-__global__ void __launch_bounds__(ABP_THREADS, 1)
-attn_tc_bwd_dq_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
-                      const __grid_constant__ CUtensorMap tmap_v, const __grid_constant__ CUtensorMap tmap_do,
-                      AttnBwdArgs a, int n_items, int BH) {
-  extern __shared__ uint8_t at_smem_raw[];
-  uint8_t *smem = (uint8_t *)(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t sb = smem_u32(smem);
-  const uint32_t bar = sb + AQ_BAR;
-  const uint32_t q_full = bar, q_empty = bar + 8, s_full0 = bar + 16, dp_full = bar + 32, ds_ready = bar + 40,
-                 acc_done = bar + 48, acc_final = bar + 56, acc_free = bar + 64, kv_full0 = bar + 72,
-                 kv_empty0 = kv_full0 + 8 * AQ_STAGES;
-  uint32_t *tmem_slot = (uint32_t *)(smem + AQ_BAR + 72 + 16 * AQ_STAGES);
-  volatile uint32_t *abort_flag = (volatile uint32_t *)(tmem_slot + 1);
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n_qb = (a.T + 127) / 128;
-  constexpr uint32_t TMEM_COLS = 512;
-
-  if (threadIdx.x == 0) {
-    mbar_init(q_full, 1);
-    mbar_init(q_empty, 1);
-    mbar_init(s_full0, 1); mbar_init(s_full0 + 8, 1);
-    mbar_init(dp_full, 1);
-    mbar_init(ds_ready, AB_MATH_WARPS);
-    mbar_init(acc_done, 1);
-    mbar_init(acc_final, 1);
-    mbar_init(acc_free, 4);
-    for (int s = 0; s < AQ_STAGES; s++) {
-      mbar_init(kv_full0 + 8 * s, 1);
-      mbar_init(kv_empty0 + 8 * s, 1);
-    }
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), TMEM_COLS);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
+// dQ[bh, query block qb] = sum over key blocks kb <= qb of the fp32 contributions the
+// backward kernel left in the workspace, added in key-block order (the same order on every
+// run), rounded to bf16 once.  Sixteen threads per query row (four floats each); the loads of
+// four key blocks are in flight together.  HBM-bound: reads (qb + 1) * 32 KB, writes 16 KB per
+// (bh, qb).
+__global__ void __launch_bounds__(256) attn_tc_dq_reduce_kernel(const float *__restrict__ part, __nv_bfloat16 *dq,
+                                                                int64_t q_sb, int64_t q_sh, int64_t q_st, int H, int T,
+                                                                int n_qb) {
+  const int n_pairs = n_qb * (n_qb + 1) / 2;
+  const int bh = blockIdx.y, qb = n_qb - 1 - (int)(blockIdx.x >> 3);   // long sums first
+  const int row = (int)(blockIdx.x & 7) * 16 + (int)(threadIdx.x >> 4), c4 = (int)(threadIdx.x & 15);
+  const int qi = qb * 128 + row;
   grid_dependency_trigger();
-  grid_dependency_wait();  // set-up above is SM-local; global memory is touched from here on
-  const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tS0 = tmem_base, tdP = tmem_base + 256, tdQ = tmem_base + 384;
-
-  // item -> (batch*head, query block): the last query block has the most key blocks to visit
-  auto decode = [&](int item, int &bh, int &qb) {
-    qb = n_qb - 1 - item / BH;
-    bh = item - (item / BH) * BH;
-  };
-
-  if (warp == 0) {
-    int t = 0, n = 0;
-    bool ok = true;
-    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
-      int bh, qb;
-      decode(item, bh, qb);
-      const int b = bh / a.H, h = bh - b * a.H, nb = qb + 1;
-      if (!mbar_wait(q_empty, (n & 1) ^ 1, abort_flag)) break;
-      if (elect_one()) {
-        mbar_expect_tx(q_full, 2 * AT_TILE);
-        tma_load_4d(sb + AQ_Q, &tmap_q, q_full, 0, qb * 128, h, b);
-        tma_load_4d(sb + AQ_DO, &tmap_do, q_full, 0, qb * 128, h, b);
-      }
-      __syncwarp();
-      for (int j = 0; j < nb; j++, t++) {
-        const int st = t % AQ_STAGES;
-        if (!mbar_wait(kv_empty0 + 8 * st, ((t / AQ_STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-        if (elect_one()) {
-          mbar_expect_tx(kv_full0 + 8 * st, 2 * AT_TILE);
-          tma_load_4d(sb + AQ_K + st * AT_TILE, &tmap_k, kv_full0 + 8 * st, 0, j * 128, h, b);
-          tma_load_4d(sb + AQ_V + st * AT_TILE, &tmap_v, kv_full0 + 8 * st, 0, j * 128, h, b);
-        }
-        __syncwarp();
-      }
-    }
-  } else if (warp == 1) {
-    constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
-    constexpr uint32_t idesc_q = make_idesc_bf16(128, 64, false, true);     // [q x d] = A[q,k] B[k,d]
-    const uint64_t d_q = make_smem_desc(sb + AQ_Q, 16, 1024), d_do = make_smem_desc(sb + AQ_DO, 16, 1024);
-    const uint64_t d_k_k = make_smem_desc(sb + AQ_K, 16, 1024), d_v_k = make_smem_desc(sb + AQ_V, 16, 1024);
-    const uint64_t d_k_n = make_smem_desc(sb + AQ_K, AT_TILE, 1024);
-    const uint64_t d_ds = make_smem_desc(sb + AQ_DS, 16, 1024);
-    int t = 0, n = 0;
-    bool ok = true;
-    for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
-      int bh, qb;
-      decode(item, bh, qb);
-      const int nb = qb + 1;
-      auto issue_s = [&](int j) -> bool {   // S(j) = Q K(j)^T into buffer (t + j) & 1 (waits for the tile's loads)
-        const int tt = t + j, st = tt % AQ_STAGES;
-        if (!mbar_wait(kv_full0 + 8 * st, (tt / AQ_STAGES) & 1, abort_flag)) return false;
-        tc_fence_after();
-        const uint64_t kd = d_k_k + (uint64_t)((st * AT_TILE) >> 4);
-        const uint32_t ts = tS0 + (tt & 1) * 128, done = s_full0 + 8 * (tt & 1);
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(ts, d_q + kk * 2, kd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-          mma_commit(done);
-        }
-        __syncwarp();
-        return true;
-      };
-      auto issue_dp = [&](int j) {          // dP(j) = dO V(j)^T
-        const uint64_t vd = d_v_k + (uint64_t)((((t + j) % AQ_STAGES) * AT_TILE) >> 4);
-        const bool last = j == nb - 1;
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 4; kk++) mma_bf16_ss(tdP, d_do + kk * 2, vd + kk * 2, idesc_s, kk > 0 ? 1u : 0u);
-          mma_commit(dp_full);
-          if (last) mma_commit(q_empty);     // Q and dO are not read after the item's last dP
-        }
-        __syncwarp();
-      };
-      ok = mbar_wait(q_full, n & 1, abort_flag);
-      if (ok) ok = issue_s(0);
-      if (ok) issue_dp(0);
-      if (ok && nb > 1) ok = issue_s(1);
-      for (int j = 0; j < nb && ok; j++) {
-        const int tt = t + j;
-        if (!mbar_wait(ds_ready, tt & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        if (j + 1 < nb) issue_dp(j + 1);
-        if (j == 0 && n > 0 && !mbar_wait(acc_free, (n - 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        const int st = tt % AQ_STAGES;
-        const uint64_t kn = d_k_n + (uint64_t)((st * AT_TILE) >> 4);
-        const uint32_t first = j > 0 ? 1u : 0u, freed = kv_empty0 + 8 * st;
-        const bool last = j == nb - 1;
-        if (elect_one()) {
-#pragma unroll
-          for (int kk = 0; kk < 8; kk++)  // 16 keys per step; dS tile (kk >> 2), 32 bytes per step inside it
-            mma_bf16_ss(tdQ, d_ds + (uint64_t)(((kk >> 2) * AT_TILE + (kk & 3) * 32) >> 4), kn + kk * 128, idesc_q,
-                        kk > 0 ? 1u : first);
-          mma_commit(freed);
-          mma_commit(acc_done);
-          if (last) mma_commit(acc_final);
-        }
-        __syncwarp();
-        if (j + 2 < nb) ok = issue_s(j + 2);
-      }
-      t += nb;
-    }
-  } else if (warp < 2 + AB_MATH_WARPS) {
-    const int quad = warp & 3, colq = (warp - 2) >> 2;  // lane quadrant, 32-column quarter
-    const int col0 = colq * AB_NC;
-    const int row = quad * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const float LOG2E = 1.4426950408889634f;
-    const bool capped = a.cap > 0.f;
-    BwdRowConsts k;
-    k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
-    k.c2 = a.cap * LOG2E;
-    k.scale = a.scale;
-    uint8_t *ds_row = smem + AQ_DS + (colq >> 1) * AT_TILE + row * 128;
-    int t = 0;
-    bool ok = true;
-    for (int rnd = 0, item = snake_item(0); item < n_items && ok; item = snake_item(++rnd)) {
-      int bh, qb;
-      decode(item, bh, qb);
-      const int nb = qb + 1;
-      const int qi = qb * 128 + row;
-      const bool valid = qi < a.T;
-      k.lse2 = valid ? a.lse[(int64_t)bh * a.T + qi] * LOG2E : INFINITY;
-      k.delta = valid ? a.delta[(int64_t)bh * a.T + qi] : 0.f;
-      for (int j = 0; j < nb; j++) {
-        const int tt = t + j;
-        uint32_t pk[AB_NC / 2], fk[AB_NC / 2];
-        if (!mbar_wait(s_full0 + 8 * (tt & 1), (tt >> 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        bwd_phase_a_any(tS0 + (tt & 1) * 128 + lane_off + col0, row, col0, j == qb, capped, k, pk, fk);
-        if (!mbar_wait(dp_full, tt & 1, abort_flag)) { ok = false; break; }
-        // dQ += dS K of the previous tile must have finished reading the dS tiles
-        if (tt > 0 && !mbar_wait(acc_done, (tt - 1) & 1, abort_flag)) { ok = false; break; }
-        tc_fence_after();
-        bwd_phase_b<false>(tdP + lane_off + col0, row, (colq & 1) * 4, k, pk, fk, nullptr, ds_row);
-        fence_proxy_async();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(ds_ready);
-      }
-      t += nb;
-    }
-  } else {
-    // epilogue warps: quadrant q writes rows 32q .. 32q+31 of dQ of every finished item
-    const int quad = warp & 3;
-    const int row = quad * 32 + lane;
-    const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    int n = 0;
-    for (int item = snake_item(0); item < n_items; item = snake_item(++n)) {
-      int bh, qb;
-      decode(item, bh, qb);
-      const int b = bh / a.H, h = bh - b * a.H;
-      if (!mbar_wait(acc_final, n & 1, abort_flag)) break;
-      tc_fence_after();
-      const int qi = qb * 128 + row;
-      __nv_bfloat16 *dst = (__nv_bfloat16 *)a.dq + (int64_t)b * a.q_sb + (int64_t)h * a.q_sh + (int64_t)qi * a.q_st;
-#pragma unroll 1
-      for (int c = 0; c < 2; c++) {
-        uint32_t r[32];
-        tmem_ld_32x32(tdQ + lane_off + c * 32, r);
-        tmem_ld_wait();
-        if (qi < a.T) {
-#pragma unroll
-          for (int q = 0; q < 4; q++) {
-            float f[8];
-#pragma unroll
-            for (int i = 0; i < 8; i++) f[i] = __uint_as_float(r[q * 8 + i]);
-            Vec16<__nv_bfloat16> v;
-            v.set(f);
-            v.store(dst + c * 32 + q * 8);
-          }
-        }
-      }
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(acc_free);
-    }
+  grid_dependency_wait();
+  if (qi >= T) return;
+  const float4 *src = reinterpret_cast<const float4 *>(part + (((int64_t)bh * n_pairs + qb * (qb + 1) / 2) * 128 + row) * 64) + c4;
+  constexpr int64_t SLAB4 = 128 * 64 / 4;   // float4 per (qb, kb) slab
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  int kb = 0;
+  for (; kb + 4 <= qb + 1; kb += 4) {
+    const float4 v0 = __ldcs(src + (kb + 0) * SLAB4), v1 = __ldcs(src + (kb + 1) * SLAB4),
+                 v2 = __ldcs(src + (kb + 2) * SLAB4), v3 = __ldcs(src + (kb + 3) * SLAB4);
+    acc.x += v0.x; acc.y += v0.y; acc.z += v0.z; acc.w += v0.w;
+    acc.x += v1.x; acc.y += v1.y; acc.z += v1.z; acc.w += v1.w;
+    acc.x += v2.x; acc.y += v2.y; acc.z += v2.z; acc.w += v2.w;
+    acc.x += v3.x; acc.y += v3.y; acc.z += v3.z; acc.w += v3.w;
   }
-
-  if (*abort_flag) {
-    const long long t0 = clock64();
-    while (clock64() - t0 < 2000000ll) {
-    }
-    if (threadIdx.x == 0 && a.err) atomicExch(a.err, 0xA9000000u | (uint32_t)(blockIdx.x & 0xFFFF));
+  for (; kb <= qb; kb++) {
+    const float4 v = __ldcs(src + kb * SLAB4);
+    acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
   }
-  tc_fence_before();
-  __syncthreads();
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, TMEM_COLS);
-  }
+  const int b = bh / H, h = bh - b * H;
+  __nv_bfloat16 *dst = dq + (int64_t)b * q_sb + (int64_t)h * q_sh + (int64_t)qi * q_st + c4 * 4;
+  uint2 o;
+  *reinterpret_cast<__nv_bfloat162 *>(&o.x) = __floats2bfloat162_rn(acc.x, acc.y);
+  *reinterpret_cast<__nv_bfloat162 *>(&o.y) = __floats2bfloat162_rn(acc.z, acc.w);
+  *reinterpret_cast<uint2 *>(dst) = o;
 }
 
 // ── forward, bounded scores (soft cap), persistent ─────────────────────────────────────
@@ -1474,16 +1365,31 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   a.err = tc_error_word();
   static int attr = -1;
   if (attr != g_init_epoch) {
-    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dkv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AK_DYN));
-    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_dq_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AQ_DYN));
+    ALPHA_CUDA(cudaFuncSetAttribute(attn_tc_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, AK_DYN));
     attr = g_init_epoch;
   }
   const int BH = (int)(p->batch * p->heads);
-  const int n_items = (int)((p->T + 127) / 128) * BH;
+  const int n_qb = (int)((p->T + 127) / 128);
+  const int n_items = n_qb * BH;
   const int grid = n_items < g_sm_count ? n_items : g_sm_count;
-  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_dkv_kernel, dim3(grid), dim3(ABP_THREADS), AK_DYN, tq, tk, tv, tdo, a, n_items, BH));
+  // One pass over the (query block, key block) tiles: the kernel that owns dK and dV of a key
+  // block also multiplies each tile's dS by K; those dQ contributions (fp32, 32 KB per tile) go
+  // to a workspace and a second, HBM-bound kernel adds them per query block in key-block order.
+  void *part = nullptr;
+  const size_t part_bytes = (size_t)BH * (n_qb * (n_qb + 1) / 2) * 128 * 64 * sizeof(float);
+  if (pool_alloc(part_bytes, &part)) { pool_free(delta); return 1; }
+  a.dq_part = (float *)part;
+  CUtensorMap tpart;
+  if (encode_tmap_2d_out(&tpart, part, ALPHA_F32, 64, (uint64_t)BH * (n_qb * (n_qb + 1) / 2) * 128, 64, 32)) {
+    pool_free(part); pool_free(delta);
+    return 1;
+  }
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_kernel, dim3(grid), dim3(ABP_THREADS), AK_DYN, tq, tk, tv, tdo, tpart, a, n_items, BH));
   g_launches++;
-  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_dq_kernel, dim3(grid), dim3(ABP_THREADS), AQ_DYN, tq, tk, tv, tdo, a, n_items, BH));
+  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_dq_reduce_kernel, dim3((unsigned)(n_qb * 8), (unsigned)BH), dim3(256), 0,
+                               (const float *)part, ptr<__nv_bfloat16>(dq), p->q_sb, p->q_sh, p->q_st, (int)p->heads,
+                               (int)p->T, n_qb));
+  pool_free(part);
   pool_free(delta);
   ALPHA_LAUNCHED();
   return 0;

@@ -144,6 +144,13 @@ __device__ __forceinline__ void tma_load_4d(uint32_t dst, const CUtensorMap *map
 }
 // 1-D bulk copy global -> shared (both addresses 16-byte aligned, size a multiple of 16),
 // completion counted on an mbarrier.
+// Asks for the box at these coordinates to be brought into L2 (no shared-memory destination, no
+// completion to wait for): a later tma_load_4d of the same box then finds it there.
+__device__ __forceinline__ void tma_prefetch_l2_4d(const CUtensorMap *map, int32_t c0, int32_t c1, int32_t c2, int32_t c3) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];"
+               ::"l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
+               : "memory");
+}
 __device__ __forceinline__ void bulk_load_1d(uint32_t dst, const void *src, uint32_t bytes, uint32_t bar) {
   asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                ::"r"(dst), "l"(src), "r"(bytes), "r"(bar)
