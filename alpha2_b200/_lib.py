@@ -71,6 +71,7 @@ SIGNATURES = {
     "alpha_stream_sync": [], "alpha_launch_count": [C.POINTER(C.c_uint64)],
     "alpha_stream_handle": [C.POINTER(C.c_uint64)], "alpha_check_async_error": [],
     "alpha_debug_wait_expiry": [_I, _I, C.POINTER(C.c_int)],
+    "alpha_range_push": [C.c_char_p], "alpha_range_pop": [],
     "alpha_profile_enable": [_I], "alpha_profile_read": [C.POINTER(ProfileEntry), _I],
     "alpha_event_create": [C.POINTER(C.c_uint64)], "alpha_event_record": [_B], "alpha_event_sync": [_B],
     "alpha_event_elapsed_ms": [_B, _B, C.POINTER(C.c_float)], "alpha_event_destroy": [_B],

@@ -208,6 +208,13 @@ class CudaBackend:
     def syncGpu(self) -> None:
         check(self.lib.alpha_stream_sync())
 
+    def rangePush(self, name: str) -> None:
+        """Open a named NVTX range on the host timeline (see alpha_range_push)."""
+        self.lib.alpha_range_push(name.encode())
+
+    def rangePop(self) -> None:
+        self.lib.alpha_range_pop()
+
     def checkAsyncError(self) -> None:
         check(self.lib.alpha_check_async_error())
 

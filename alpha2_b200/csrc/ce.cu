@@ -139,19 +139,18 @@ ce_rows_bf16_kernel(const __nv_bfloat16 *__restrict__ logits, const int32_t *__r
     // the target's logit is read before dlogits (which may alias logits) is written
     float lt = 0.f;
     if (threadIdx.x == 0 && tgt >= 0 && tgt < V) lt = __bfloat162float(row[tgt]);
-    float mx = -INFINITY;
+    // the row maximum is taken on packed bf16 pairs (one instruction per two logits; exact:
+    // the maximum of bf16 values is one of them) and widened once at the end
+    __nv_bfloat162 mx2 = __float2bfloat162_rn(-INFINITY);
     for (int i = threadIdx.x; i < nvec; i += CE_THREADS) {
       const uint4 v = row_v[i];
       row_s[i] = v;
-      uint64_t p[4];
-      bf16x8_to_pairs(v, p);
-#pragma unroll
-      for (int q = 0; q < 4; q++) {
-        float a, b;
-        tc::f2_unpack(p[q], a, b);
-        mx = tc::fmax3(mx, a, b);
-      }
+      mx2 = __hmax2(mx2, __hmax2(__hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&v.x),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&v.y)),
+                                 __hmax2(*reinterpret_cast<const __nv_bfloat162 *>(&v.z),
+                                         *reinterpret_cast<const __nv_bfloat162 *>(&v.w))));
     }
+    float mx = fmaxf(__low2float(mx2), __high2float(mx2));
     for (int c = nvec * 8 + threadIdx.x; c < V; c += CE_THREADS) {
       const __nv_bfloat16 t = row[c];
       reinterpret_cast<__nv_bfloat16 *>(smem_raw)[c] = t;

@@ -40,11 +40,19 @@ enum ProfCat { PROF_GEMM_TC = 0, PROF_GEMM_F32 = 1, PROF_ATTN_FWD = 2, PROF_ATTN
 extern bool g_profiling;
 void prof_begin(int cat, double work);
 void prof_end(int cat);
+void range_begin(int cat);  // NVTX range named after the kernel family (no-op without a tool attached)
+void range_end();
 struct ProfScope {
   int cat;
   bool on;
-  ProfScope(int c, double work) : cat(c), on(g_profiling) { if (on) prof_begin(c, work); }
-  ~ProfScope() { if (on) prof_end(cat); }
+  ProfScope(int c, double work) : cat(c), on(g_profiling) {
+    range_begin(c);
+    if (on) prof_begin(c, work);
+  }
+  ~ProfScope() {
+    if (on) prof_end(cat);
+    range_end();
+  }
 };
 
 #define ALPHA_REQUIRE_INIT()                                                 \

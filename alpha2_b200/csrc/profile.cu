@@ -3,6 +3,13 @@
 // packages/helios/src/backend.ts:5159-5204 profileOp); here the launch sites of the heavy
 // kernel families record CUDA events on the compute stream while profiling is switched on,
 // and alpha_profile_read sums their elapsed times and the algorithmic work they declared.
+//
+// NVTX: the same launch sites, and the host's step phases (alpha_range_push / alpha_range_pop,
+// the counterpart of the reference's per-phase timers, packages/train/src/trainer.ts:1189-1264),
+// open NVTX ranges, so that a timeline tool shows which family and phase a kernel belongs to.
+// NVTX v3 is header-only and does nothing (a null function-pointer check) when no tool is attached.
+#include <nvtx3/nvToolsExt.h>
+
 #include <vector>
 
 #include "common.cuh"
@@ -32,6 +39,11 @@ static cudaEvent_t get_event() {
   return e;
 }
 
+static const char *const PROF_NAMES[PROF_NCAT] = {"gemm_tc", "gemm_f32", "attn_fwd", "attn_bwd", "cross_entropy",
+                                                  "adamw",   "norm",     "embedding", "elementwise"};
+void range_begin(int cat) { nvtxRangePushA(cat >= 0 && cat < PROF_NCAT ? PROF_NAMES[cat] : "alpha"); }
+void range_end() { nvtxRangePop(); }
+
 void prof_begin(int cat, double work) {
   cudaEvent_t e = get_event();
   cudaEventRecord(e, g_stream);
@@ -50,6 +62,16 @@ void prof_end(int cat) {
 using namespace alpha;
 
 extern "C" {
+
+int alpha_range_push(const char *name) {
+  nvtxRangePushA(name ? name : "alpha");
+  return 0;
+}
+
+int alpha_range_pop(void) {
+  nvtxRangePop();
+  return 0;
+}
 
 int alpha_profile_enable(int on) {
   ALPHA_REQUIRE_INIT();

@@ -218,10 +218,16 @@ class Trainer:
         B.resetStepOps()
         loss_acc = None
         loss_td = None
+        mark = getattr(B, "rangePush", None)        # phase ranges for timeline tools (trainer.ts:1189-1264 times the same phases)
+        unmark = getattr(B, "rangePop", None)
         for mi, (tokens, targets) in enumerate(batches):
+            if mark:
+                mark("forward")
             out = gptForward(self.mc, self.params, B, self.tape, tokens, targets, training=True,
                              attention=self.attention, release=self.releaseFn,
                              activationCheckpointing=self.activationCheckpointing)
+            if mark:
+                unmark()
             loss = out["loss"]
             if accum > 1:                                      # trainer.ts:1210-1226
                 scaled = B.scale(loss.data, 1 / accum)
@@ -232,13 +238,19 @@ class Trainer:
             else:
                 loss_td = B.clone(loss.data) if self.releaseFn else loss.data
             last = mi == accum - 1
+            if mark:
+                mark("backward")
             self._backward(loss, allreduce=last and self.dp is not None)
             self.tape.clear(self.releaseFn)
+            if mark:
+                unmark()
         if accum > 1:
             loss_td = loss_acc
         if self.dp is not None:
             self.dp.wait()
 
+        if mark:
+            mark("optimizer")
         grad_scale = 1.0 / (accum * world)
         grads = [v.grad for _, v in self.entries if v.grad is not None]
         sumsq = B.totalSumOfSquares(grads)
@@ -265,6 +277,8 @@ class Trainer:
             if math.isfinite(loss_val) and math.isfinite(gnorm):
                 self.opt.stepParamEntries(self.entries, eff)
             result.update(loss=loss_val, gradNorm=gnorm, clipCoef=clip)
+        if mark:
+            unmark()
         if read_back and hasattr(B, "checkAsyncError"):
             # The host has just waited for the step's scalars, so asking the library whether a
             # tensor-core kernel gave up a bounded wait costs one 4-byte read.  Such a step

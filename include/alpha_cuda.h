@@ -92,6 +92,12 @@ typedef struct {
 enum { ALPHA_PROFILE_CATEGORIES = 9 };
 int alpha_profile_enable(int on);
 int alpha_profile_read(alpha_profile_entry_t *out, int n_categories);
+/* NVTX ranges for timeline tools: every launch site of the families above opens a range named
+ * after its family; a host brackets its own phases (forward, backward, optimizer — the
+ * reference times the same phases with host clocks, packages/train/src/trainer.ts:1189-1264)
+ * with these two.  Without a tool attached they cost a null-pointer check. */
+int alpha_range_push(const char *name);
+int alpha_range_pop(void);
 
 /* Events: helios_vk.c gpuTime / waitTimeline / getCompleted (:4403-4432). */
 int alpha_event_create(uint64_t *ev);

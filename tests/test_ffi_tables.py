@@ -23,9 +23,9 @@ def _parse_ts(text: str) -> dict:
     return out
 
 
-def _ctypes_to_ffi(t) -> str:
+def _ctypes_to_ffi(t, result: bool = False) -> str:
     if t in (C.c_void_p, C.c_char_p) or (isinstance(t, type) and issubclass(t, C._Pointer)):
-        return "cstring" if t is C.c_char_p else "ptr"
+        return "cstring" if (t is C.c_char_p and result) else "ptr"     # a string argument is a plain pointer
     return {C.c_int: "i32", C.c_int32: "i32", C.c_uint32: "u32", C.c_int64: "i64", C.c_uint64: "u64",
             C.c_size_t: "u64", C.c_float: "f32", C.c_double: "f64"}[t]
 
@@ -44,7 +44,7 @@ def test_generated_ts_table_is_current_and_matches_the_header():
 def test_ctypes_table_matches_the_header():
     hdr = gen_ffi.parse_header()
     table = {n: ("i32", a) for n, a in L.SIGNATURES.items()}
-    table.update({n: (_ctypes_to_ffi(r), a) for n, (a, r) in L._OTHER_RESTYPE.items()})
+    table.update({n: (_ctypes_to_ffi(r, result=True), a) for n, (a, r) in L._OTHER_RESTYPE.items()})
     assert set(table) == set(hdr), sorted(set(table) ^ set(hdr))
     for name, (ret, types, names) in hdr.items():
         got_ret, got_args = table[name]
