@@ -13,8 +13,10 @@ library and compare.  Every case is a model at its full stated shape:
 * ``gpt2_124m_3steps`` — vocab 50257, 12 layers, width 768, 12 heads, context 1024, learned
   positions, GELU MLP 3072, tied head; one sequence of 1024 tokens per step, 3 steps.
 * ``gpt_350m_accum2_2steps`` — vocab 32768, 24 layers, width 1024, 16 heads, context 2048,
-  RMSNorm, SwiGLU 2816, RoPE, untied head; one sequence of 2048 tokens per micro-step, two
-  accumulated micro-steps per optimizer step, 2 steps.
+  RMSNorm, SwiGLU 2816, RoPE, untied head; one sequence of 1024 tokens per micro-step (the
+  oracle keeps every layer's dense [heads, T, T] score tensors for its backward pass: at 2048
+  tokens that is more host memory than the 62 GB this was generated with), two accumulated
+  micro-steps per optimizer step, 2 steps.
 
 A fixture holds, per step: loss, gradient norm, learning rate, clip coefficient; at the
 snapshot steps, for every parameter tensor: its L2 norm (f64) and a strided sample of at most
@@ -49,7 +51,7 @@ CASES = {
         model=dict(vocabSize=32768, blockSize=2048, nLayer=24, nEmbd=1024, nHead=16, tied=False,
                    ffnActivation="swiglu", ffnDim=2816, norm="rms", rope=True, init="plain"),
         train=dict(iters=100, batchSize=1, lr=3e-4, seed=42), data_seed=7, batch=1, accum=2, steps=2,
-        snapshots=(1, 2)),
+        snapshots=(1, 2), seq_len=1024),
 }
 
 
@@ -63,8 +65,8 @@ def case_batches(case: dict):
     """The case's micro-batches, in order: ``steps * accum`` pairs of int32 [batch, T]."""
     from oracle import train as otrain
     m = case["model"]
-    return otrain.zipf_batches(case["data_seed"], case["steps"] * case["accum"], case["batch"], m["blockSize"],
-                               m["vocabSize"])
+    return otrain.zipf_batches(case["data_seed"], case["steps"] * case["accum"], case["batch"],
+                               case.get("seq_len", m["blockSize"]), m["vocabSize"])
 
 
 def snapshot(P: dict) -> dict:

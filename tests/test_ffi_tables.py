@@ -59,3 +59,50 @@ def test_integration_md_excerpts_match_the_header():
     for name, (ret, args) in doc.items():
         assert name in hdr, name
         assert (ret, args) == (hdr[name][0], hdr[name][1]), name
+
+
+def _calls(text: str):
+    """(name, number of top-level arguments) of every `C.alpha_*( ... )` call in a TypeScript text."""
+    out = []
+    for m in re.finditer(r"\bC\.(alpha_[a-z0-9_]+)\(", text):
+        i, depth, args, cur = m.end(), 1, 0, ""
+        while depth:
+            ch = text[i]
+            if ch in "([{":
+                depth += 1
+            elif ch in ")]}":
+                depth -= 1
+                if depth == 0:
+                    break
+            elif ch == "," and depth == 1:
+                args += 1
+                cur = ""
+                i += 1
+                continue
+            cur += ch
+            i += 1
+        out.append((m.group(1), args + (1 if cur.strip() else 0)))
+    return out
+
+
+# every method of the reference's Backend interface (packages/core/src/interfaces.ts:38-151)
+BACKEND_METHODS = """zeros ones full randn fromArray add sub mul div matmul sum mean neg exp log sqrt pow scale clamp
+embedding layerNorm gelu relu silu softmax logSoftmax crossEntropy reshape transpose slice cat argmax topk gather clone
+equal allClose causalMask maskedFill geluBackward reluBackward siluBackward siluMul siluMulBackward clampBackward
+layerNormBackward crossEntropyBackward embeddingBackward softCap softCapBackward residualDropoutAdd matmulTransposed
+matmulTransposedA addInplace scaleInplace sliceQkv scatterSlice dropoutMask flashAttention flashAttentionBackward
+broadcast castDtype sumOfSquares totalSumOfSquares checkFinite adamwStep""".split()
+# what the trainer and the CLI probe by duck typing (trainer.ts:623-641,757-841,998-1044; train.ts:284-318)
+PROBED = "releaseGpuTensor flush syncGpu purgeBufferPools gpuMemStats resetStepOps gpuOpsThisStep getDeviceInfo smokeTest setMinGpuSize coopMatmulPaused getMatmulCoopStats".split()
+
+
+def test_typescript_backend_calls_the_abi_with_the_declared_arity_and_covers_the_interface():
+    hdr = gen_ffi.parse_header()
+    text = open(os.path.join(ROOT, "ts", "backend.ts")).read()
+    calls = _calls(text)
+    assert len(calls) > 50
+    for name, n in calls:
+        assert name in hdr, name
+        assert n == len(hdr[name][1]), (name, n, hdr[name][2])
+    for meth in BACKEND_METHODS + PROBED:
+        assert re.search(r"\n  (?:readonly |get |private )?%s\b" % meth, text), meth
