@@ -219,42 +219,55 @@ __global__ void __launch_bounds__(256) emb_rowsum_kernel(const T *__restrict__ g
 
 // Rows named many times (frequent tokens): a whole block per row.  The row's occurrence list is
 // cut into blockDim.y contiguous segments, segment s is summed in order by the threads
-// (threadIdx.x = 4-column group), and the segment sums are added in segment order — a fixed
-// summation tree, so the result is reproducible (it is not the strictly sequential order of
-// the reference loop, which is why fp32 parity runs do not use this kernel).
-constexpr int HOT_COLS = 192;   // column groups per pass (768 columns)
-constexpr int HOT_SEGS = 5;
+// (threadIdx.x = 8-column group, one 16-byte load per occurrence for bf16), and the segment sums
+// are added in segment order — a fixed summation tree, so the result is reproducible (it is not
+// the strictly sequential order of the reference loop, which is why fp32 parity runs do not use
+// this kernel).  Ten segments: the most frequent token of a Zipf stream takes a seventh of the
+// batch, and the length of the longest sequential sum is what this kernel's time is made of.
+constexpr int HOT_COLS = 96;    // column groups per pass (768 columns)
+constexpr int HOT_SEGS = 10;
+constexpr int HOT_W = 8;        // columns per thread
 template <typename T>
 __global__ void __launch_bounds__(HOT_COLS * HOT_SEGS) emb_hot_rows_kernel(
     const T *__restrict__ g, const int32_t *__restrict__ start, const int32_t *__restrict__ order,
     float *__restrict__ dw, int64_t dim, int accumulate, const int32_t *__restrict__ hot_rows,
     const int32_t *__restrict__ hot_count, int hot_cap) {
-  __shared__ float part[HOT_SEGS][HOT_COLS][4];
+  __shared__ float part[HOT_SEGS][HOT_COLS][HOT_W];
   const int n_hot = *hot_count < hot_cap ? *hot_count : hot_cap;
   const int cg = threadIdx.x, seg = threadIdx.y;
+  const bool vec_ok = sizeof(T) == 2 && dim % HOT_W == 0 && (reinterpret_cast<uintptr_t>(g) & 15) == 0;
   for (int hidx = blockIdx.x; hidx < n_hot; hidx += gridDim.x) {
     const int64_t v = hot_rows[hidx];
     const int32_t s = start[v], e = start[v + 1];
     const int32_t len = (e - s + HOT_SEGS - 1) / HOT_SEGS;
     const int32_t ks = s + seg * len, ke = ks + len < e ? ks + len : e;
-    for (int64_t c0 = 0; c0 < dim; c0 += HOT_COLS * 4) {
-      const int64_t c = c0 + cg * 4;
-      const int nc = c < dim ? (int)(dim - c < 4 ? dim - c : 4) : 0;
-      float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int64_t c0 = 0; c0 < dim; c0 += HOT_COLS * HOT_W) {
+      const int64_t c = c0 + cg * HOT_W;
+      const int nc = c < dim ? (int)(dim - c < HOT_W ? dim - c : HOT_W) : 0;
+      float acc[HOT_W];
+#pragma unroll
+      for (int j = 0; j < HOT_W; j++) acc[j] = 0.f;
       if (nc > 0) {
         int32_t k = ks;
+        // loads are independent of the running sums: eight occurrences of loads, then add in order
         for (; k + 8 <= ke; k += 8) {
-          float t[8][4];
+          float t[8][HOT_W];
 #pragma unroll
           for (int u = 0; u < 8; u++) {
             const T *src = g + (int64_t)order[k + u] * dim + c;
+            if (vec_ok) {
+              Vec16<T> x;
+              x.load(src);
+              x.get(t[u]);
+            } else {
 #pragma unroll
-            for (int j = 0; j < 4; j++) t[u][j] = j < nc ? to_f32(src[j]) : 0.f;
+              for (int j = 0; j < HOT_W; j++) t[u][j] = j < nc ? to_f32(src[j]) : 0.f;
+            }
           }
 #pragma unroll
           for (int u = 0; u < 8; u++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) acc[j] += t[u][j];
+            for (int j = 0; j < HOT_W; j++) acc[j] += t[u][j];
         }
         for (; k < ke; k++) {
           const T *src = g + (int64_t)order[k] * dim + c;
@@ -262,7 +275,7 @@ __global__ void __launch_bounds__(HOT_COLS * HOT_SEGS) emb_hot_rows_kernel(
         }
       }
 #pragma unroll
-      for (int j = 0; j < 4; j++) part[seg][cg][j] = acc[j];
+      for (int j = 0; j < HOT_W; j++) part[seg][cg][j] = acc[j];
       __syncthreads();
       if (seg == 0 && nc > 0) {
         float *dst = dw + v * dim + c;

@@ -188,15 +188,15 @@ def test_embedding_gather_is_bit_exact_and_scatter_is_ordered(B, dtype):
     for i, v in enumerate(flat_idx):
         ref[v] = ref[v] + flat_g[i]
     if dtype == "bf16":
-        # bf16 gradients: a row named more than 64 times is summed as a fixed tree — five
+        # bf16 gradients: a row named more than 64 times is summed as a fixed tree — ten
         # contiguous segments of its occurrence list, each summed in order, added in order
         counts = np.bincount(flat_idx, minlength=V)
         assert counts.max() > 64                                                     # the case is exercised
         for v in np.nonzero(counts > 64)[0]:
             occ = np.nonzero(flat_idx == v)[0]
-            seg = -(-len(occ) // 5)
+            seg = -(-len(occ) // 10)
             tot = np.zeros(E, f32)
-            for q in range(5):
+            for q in range(10):
                 part = np.zeros(E, f32)
                 for i in occ[q * seg:(q + 1) * seg]:
                     part = part + flat_g[i]

@@ -7,8 +7,8 @@ same seeded batches:
 
 * small GPT (vocab 4096, 6 layers, width 384, context 256) at batch 32 for 100 steps,
 * the GPT-2-124M shape (12 layers, width 768, vocab 50257, context 1024, tied head), 3 steps,
-* the 350M shape (24 layers, width 1024, context 2048, RMSNorm, SwiGLU, RoPE, untied head) with
-  two accumulated micro-steps, 2 steps,
+* the 350M shape (24 layers, width 1024, context 2048, RMSNorm, SwiGLU, RoPE, untied head) on
+  sequences of 1024 tokens with two accumulated micro-steps, 2 steps,
 
 each in fp32 and in bf16 (fp32 master weights and AdamW state).  Tolerances: fp32 — loss within
 1e-4 relative at every step, gradient norm within 2e-3 relative, every parameter tensor's sample
