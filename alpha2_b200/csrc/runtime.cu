@@ -112,9 +112,13 @@ int pool_free(void *p) {
 }
 
 // ── content-addressed table cache ───────────────────────────────────────────
+struct TableEntry {
+  void *first;                        // device copy
+  std::vector<unsigned char> host;    // the bytes it was made from: a hit is a byte-for-byte match
+};
 struct TableCache {
   std::mutex mu;
-  std::unordered_map<uint64_t, std::pair<void *, size_t>> entries;
+  std::unordered_map<uint64_t, TableEntry> entries;
 };
 static TableCache g_tables;
 
@@ -131,9 +135,15 @@ int table_upload(const void *host, size_t bytes, const void **dev) {
   h ^= bytes * 0x9e3779b97f4a7c15ull;
   std::lock_guard<std::mutex> lk(g_tables.mu);
   auto it = g_tables.entries.find(h);
-  if (it != g_tables.entries.end() && it->second.second == bytes) {
-    *dev = it->second.first;
-    return 0;
+  if (it != g_tables.entries.end()) {
+    if (it->second.host.size() == bytes && memcmp(it->second.host.data(), host, bytes) == 0) {
+      *dev = it->second.first;
+      return 0;
+    }
+    // same hash, other contents: a kernel given the cached table would read wrong pointers
+    cudaStreamSynchronize(g_stream);
+    cudaFree(it->second.first);
+    g_tables.entries.erase(it);
   }
   if (g_tables.entries.size() >= 256) {  // a changing workload: start over
     cudaStreamSynchronize(g_stream);
@@ -152,7 +162,7 @@ int table_upload(const void *host, size_t bytes, const void **dev) {
     cudaFree(d);
     return set_error("table_upload: copy -> %s", cudaGetErrorString(e));
   }
-  g_tables.entries[h] = {d, bytes};
+  g_tables.entries[h] = TableEntry{d, std::vector<unsigned char>(b, b + bytes)};
   *dev = d;
   return 0;
 }
