@@ -423,6 +423,13 @@ class CudaBackend:
         check(self.lib.alpha_cast(a.ptr, self._code(a.dtype), out.ptr, self._code(dtype), a.size))
         return out
 
+    def castInto(self, src: TensorData, dst: TensorData) -> None:
+        """dst[...] = src converted to dst's element type (same element count), in place."""
+        if src.size != dst.size:
+            raise AlphaCudaError(f"castInto: size mismatch {list(src.shape)} vs {list(dst.shape)}")
+        check(self.lib.alpha_cast(src.ptr, self._code(src.dtype), dst.ptr, self._code(dst.dtype), src.size))
+        dst.invalidate_host()
+
     def broadcast(self, a: TensorData, targetShape) -> TensorData:
         shape = tuple(int(d) for d in targetShape)
         nd = len(shape)

@@ -101,10 +101,19 @@ class DataParallel:
       the step.
     """
 
-    def __init__(self, backend: CudaBackend, world: int, rank: int, unique_id: bytes, store=None):
+    def __init__(self, backend: CudaBackend, world: int, rank: int, unique_id: bytes, store=None,
+                 wire: str = "f32"):
         import ctypes as C
         from ._lib import check
+        if wire not in ("f32", "bf16"):
+            raise ValueError("wire must be 'f32' or 'bf16'")
         self.backend, self.world, self.rank, self.store = backend, world, rank, store
+        #: element type on the wire.  "f32": the fp32 gradient buffers themselves are reduced, so
+        #: data-parallel and single-GPU runs differ only in the order of one fp32 sum per element.
+        #: "bf16": every fp32 gradient is rounded to bf16 into a side buffer, the side buffers
+        #: are reduced (half the bytes over NVLink, bf16 sums across ranks) and converted back
+        #: before the norm — two extra passes over the gradients and 8 bits less of them.
+        self.wire = wire
         buf = C.create_string_buffer(unique_id, 128)
         check(backend.lib.alpha_comm_init_rank(world, rank, buf))
 
@@ -201,6 +210,7 @@ class Trainer:
         self.attention, self.fused, self.dp = attention, fused, dp
         self.activationCheckpointing = activationCheckpointing      # trainer.ts:559,1203
         self.step_index = 0
+        self._wire_pairs: list = []
         self.releaseFn = backend.releaseGpuTensor if release else None
 
     # ── one optimizer step ────────────────────────────────────────────────────
@@ -248,6 +258,11 @@ class Trainer:
             loss_td = loss_acc
         if self.dp is not None:
             self.dp.wait()
+            for g, w in self._wire_pairs:                      # bf16 wire: the reduced copies back into the gradients
+                B.castInto(w, g)
+                if self.releaseFn is not None:
+                    self.releaseFn(w)
+            self._wire_pairs.clear()
 
         if mark:
             mark("optimizer")
@@ -311,6 +326,16 @@ class Trainer:
         limit = getattr(dp, "bucket_bytes", 32 << 20)
         bucket: list = []
         fill = [0]
+        bf16_wire = getattr(dp, "wire", "f32") == "bf16"
+        B = self.B
+
+        def on_wire(g):
+            """The tensor that goes to the collective for gradient g."""
+            if bf16_wire and g.dtype == "f32":
+                t = B.castDtype(g, "bf16")
+                self._wire_pairs.append((g, t))
+                return t
+            return g
 
         def flush():
             if bucket:
@@ -327,13 +352,14 @@ class Trainer:
                 if isinstance(v, Param) and v.id in pending:
                     pending[v.id] -= 1
                     if pending[v.id] == 0 and v.grad is not None:
+                        w = on_wire(v.grad)
                         if bucketed:
-                            bucket.append(v.grad)
-                            fill[0] += v.grad.size * (2 if v.grad.dtype == "bf16" else 4)
+                            bucket.append(w)
+                            fill[0] += w.size * (2 if w.dtype == "bf16" else 4)
                             if fill[0] >= limit:
                                 flush()
                         else:
-                            dp.allreduce(v.grad)
+                            dp.allreduce(w)
                         del pending[v.id]
         self.tape.backward(loss, self.B, self.releaseFn, onEntryDone=on_entry_done)
         flush()

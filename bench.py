@@ -207,6 +207,7 @@ def main() -> None:
     ap.add_argument("--workload", default="gpt2-124m", choices=sorted(WORKLOADS))
     ap.add_argument("--micro-batch", type=int, default=0)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--wire", default="f32", choices=["f32", "bf16"], help="element type of the gradient exchange (N > 1)")
     ap.add_argument("--repeats", type=int, default=3, help="timed repetitions of the resident-token region (median reported)")
     args = ap.parse_args()
     wl = WORKLOADS[args.workload]
@@ -237,7 +238,7 @@ def main() -> None:
     if world > 1:
         ids = [DataParallel.new_unique_id() if rank == 0 else None]
         dist.broadcast_object_list(ids, src=0)
-        dp = DataParallel(B, world, rank, ids[0])
+        dp = DataParallel(B, world, rank, ids[0], wire=args.wire)
 
     model = wl["model"]
     mb = args.micro_batch or wl["micro_batch"]
@@ -408,7 +409,7 @@ def main() -> None:
         "config": {"workload": args.workload, "shape": {k: model[k] for k in ("vocabSize", "nLayer", "nEmbd", "nHead", "blockSize")},
                    "micro_batch_per_gpu": mb, "grad_accum_steps": accum, "tokens_per_step": tokens_per_step, "tied_embeddings": bool(model.get("tied")),
                    "precision": "bf16 activations and weight shadows, fp32 master weights and AdamW state",
-                   "parallelism": f"dp{world}", "l2": "inputs larger than L2 (each step streams >10 GB of activations and weights)",
+                   "parallelism": f"dp{world}", "gradient_exchange": (f"NCCL all-reduce, {args.wire} on the wire" if world > 1 else "none"), "l2": "inputs larger than L2 (each step streams >10 GB of activations and weights)",
                    "tokens": "Zipf(s=1.1), seeded per rank",
                    "attention": "causal, scores soft-capped at 30*tanh(s/30) as in the reference model (gpt.ts:244)"
                    if model.get("softCap", None) in (None, 30.0) else f"causal, softCap {model.get('softCap')}",

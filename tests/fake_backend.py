@@ -72,6 +72,10 @@ class NumpyBackend:
     def clone(self, a): return self._o(a.data.copy(), a.dtype)
     def castDtype(self, a, dtype): return self._o(a.data.copy(), "f32")
 
+    def castInto(self, src, dst):
+        self.ops += 1
+        dst._host = np.asarray(src.data, dtype=f32).reshape(dst.shape).copy()
+
     # elementwise
     def add(self, a, b): return self._o(a.data.astype(f64) + b.data)
     def sub(self, a, b): return self._o(a.data.astype(f64) - b.data)

@@ -48,7 +48,7 @@ class GlooBucketDP(GlooDP):
             self.allreduce(g)
 
 
-def _worker(rank, world, port, out_dir, bucketed=False, ckpt=False):
+def _worker(rank, world, port, out_dir, bucketed=False, ckpt=False, wire="f32"):
     sys.path.insert(0, ROOT)
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -59,6 +59,7 @@ def _worker(rank, world, port, out_dir, bucketed=False, ckpt=False):
     mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=2, nEmbd=32, nHead=4, tied=True, init="plain")
     tc = TrainConfig(iters=10, batchSize=2, gradClip=0.5, seed=3)
     dp = GlooBucketDP(world, rank) if bucketed else GlooDP(world, rank)
+    dp.wire = wire
     tr = Trainer(NumpyBackend(), mc, tc, dp=dp, activationCheckpointing=ckpt)
     batches = uniform_batches(100 + rank, 3, 2, 16, 64)          # a different stream per rank
     res = [tr.train_step([(T(t, "i32"), T(g, "i32"))]) for t, g in batches]
@@ -71,13 +72,17 @@ def _worker(rank, world, port, out_dir, bucketed=False, ckpt=False):
     dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("bucketed,ckpt", [(False, False), (True, False), (True, True)])
-def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path, bucketed, ckpt):
+@pytest.mark.parametrize("bucketed,ckpt,wire", [(False, False, "f32"), (True, False, "f32"), (True, True, "f32"),
+                                                 (True, False, "bf16")])
+def test_two_ranks_equal_one_process_with_two_microsteps(tmp_path, bucketed, ckpt, wire):
     """``ckpt``: every block runs under activation checkpointing, where the block parameters'
     gradients are produced on an inner tape during the recompute; they must still all be
-    handed to the exchange (the worker asserts one hand-over per parameter per step)."""
-    port = 29500 + (os.getpid() + (997 if bucketed else 0) + (331 if ckpt else 0)) % 2000
-    mp.spawn(_worker, args=(2, port, str(tmp_path), bucketed, ckpt), nprocs=2, join=True)
+    handed to the exchange (the worker asserts one hand-over per parameter per step).
+    ``wire="bf16"``: gradients travel as side copies that are converted back before the norm (the
+    numpy stand-in keeps them in fp32, so this checks the plumbing; the rounding is checked on
+    the GPU)."""
+    port = 29500 + (os.getpid() + (997 if bucketed else 0) + (331 if ckpt else 0) + (173 if wire == "bf16" else 0)) % 2000
+    mp.spawn(_worker, args=(2, port, str(tmp_path), bucketed, ckpt, wire), nprocs=2, join=True)
     r0, r1 = np.load(tmp_path / "rank0.npz"), np.load(tmp_path / "rank1.npz")
     for k in r0.files:
         assert np.array_equal(r0[k], r1[k]), k                   # replicas stay identical

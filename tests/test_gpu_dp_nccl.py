@@ -15,7 +15,9 @@ on one GPU as accumulated micro-steps and compares:
 * the replicas are bit-identical to each other,
 * they equal the single-GPU run: fp32 parameters within 2e-6 absolute and the gradient norm
   within 2e-5 relative (the two runs differ only in the order of one fp32 sum per gradient
-  element); the bf16 case uses the same bounds on its fp32 master weights.
+  element); the bf16 case uses the same bounds on its fp32 master weights.  With the bf16 wire
+  format (gradients rounded to bf16 for the exchange) the bounds are those of that rounding:
+  gradient norm within 5e-3, parameters within 2.5 learning rates per step.
 
 Needs two visible GPUs; skipped otherwise.  NCCL runs with its defaults except NVLS, which is
 switched off because the children exit on their own schedule.
@@ -44,6 +46,10 @@ CASES = {
     # the same with every block under activation checkpointing (block gradients come from an inner tape)
     "gpt2_width_bf16_ckpt": dict(model=dict(vocabSize=50257, blockSize=256, nLayer=3, nEmbd=768, nHead=12, tied=True,
                                             init="plain"), dtype="bf16", batch=4, ckpt=True),
+    # the same stand-in with the gradients rounded to bf16 for the exchange
+    "gpt2_width_bf16_wire_bf16": dict(model=dict(vocabSize=50257, blockSize=256, nLayer=3, nEmbd=768, nHead=12,
+                                                 tied=True, init="plain"), dtype="bf16", batch=4, ckpt=False,
+                                      wire="bf16"),
 }
 STEPS = 3
 TRAIN = dict(iters=20, lr=3e-4, gradClip=1.0, seed=42)
@@ -67,7 +73,7 @@ def _worker(args) -> None:
     from alpha2_b200.trainer import DataParallel
     case = CASES[args.case]
     B = CudaBackend(args.rank)
-    dp = DataParallel(B, args.world, args.rank, bytes.fromhex(args.uid))
+    dp = DataParallel(B, args.world, args.rank, bytes.fromhex(args.uid), wire=case.get("wire", "f32"))
     tr = _trainer(B, case, dp)
     res = [tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))]) for t, g in _batches(case, args.rank)]
     B.checkAsyncError()
@@ -114,13 +120,17 @@ def test_two_nccl_ranks_equal_one_gpu_with_two_microsteps(tmp_path, case):
         r = tr.train_step(pair)
         gns.append(r["gradNorm"]); losses.append(r["loss"])
     B.checkAsyncError()
-    np.testing.assert_allclose(r0["gn"], gns, rtol=2e-5)
-    np.testing.assert_allclose((r0["loss"] + r1["loss"]) / 2, losses, rtol=2e-5)
+    # bf16 on the wire: every gradient element carries a relative rounding error of up to 2^-9
+    # before the sum, so the norm agrees to a few 1e-3 and AdamW may move an element whose
+    # gradient is near zero by up to ~2 lr per step in the other direction
+    bf16_wire = spec.get("wire") == "bf16"
+    np.testing.assert_allclose(r0["gn"], gns, rtol=5e-3 if bf16_wire else 2e-5)
+    np.testing.assert_allclose((r0["loss"] + r1["loss"]) / 2, losses, rtol=1e-3 if bf16_wire else 2e-5)
     worst = 0.0
     for n, v in tr.entries:
         d = float(np.max(np.abs(r0[n] - v.data.data)))
         worst = max(worst, d)
-        assert d <= 2e-6, (n, d)
+        assert d <= (2.5 * TRAIN["lr"] * STEPS if bf16_wire else 2e-6), (n, d)
     print(f"{case}: 2 NCCL ranks == 1 GPU x 2 micro-steps; worst parameter difference {worst:.2e}, "
           f"gradient norms {r0['gn'].tolist()} vs {gns}")
 
