@@ -259,7 +259,9 @@ def test_cross_entropy(B, V, dtype):
     tg = r.integers(0, V, N).astype(np.int32)
     Lg, Tg = B.upload(logits, dtype), B.upload(tg, "i32")
     ref_loss = float(O.crossEntropy(logits, tg))
-    assert abs(B.crossEntropy(Lg, Tg).item() - ref_loss) < 2e-6 * ref_loss + (2e-3 if dtype == "bf16" else 0) * 0
+    # the loss is an fp32 sum over logits that are exact in either storage type (the bf16 case
+    # feeds the oracle the rounded logits), so one bound serves both: 2e-6 relative
+    assert abs(B.crossEntropy(Lg, Tg).item() - ref_loss) < 2e-6 * ref_loss
     probs = O.softmax(logits).astype(np.float64)
     probs[np.arange(N), tg] -= 1
     ref_grad = probs * 0.5 / N
