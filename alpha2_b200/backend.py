@@ -829,15 +829,37 @@ class CudaBackend:
         check(self.lib.alpha_flash_attn_fwd(base, base + E * es, base + 2 * E * es, out.ptr, lse.ptr, C.byref(p)))
         return out, lse
 
-    def attentionQkvBackward(self, qkv, out, dout, lse, Bn: int, T: int, H: int, scale: float, softCap: float):
-        """Returns dqkv [B*T, 3E]: dq, dk, dv written straight into their column blocks."""
+    def attentionQkvBackward(self, qkv, out, dout, lse, Bn: int, T: int, H: int, scale: float, softCap: float,
+                             delta: TensorData | None = None):
+        """Returns dqkv [B*T, 3E]: dq, dk, dv written straight into their column blocks.
+        ``delta``: the row-dots dO.O [B, H, T] when the caller has them already (matmulRowdot);
+        the forward output is then not read."""
         p, E, D = self._qkv_params(qkv, Bn, T, H, scale, softCap)
         es = L.DTYPE_SIZE[qkv.dtype]
         dqkv = self._new(qkv.shape, qkv.dtype)
         b, d = qkv.ptr, dqkv.ptr
+        if delta is not None:
+            check(self.lib.alpha_flash_attn_bwd_delta(b, b + E * es, b + 2 * E * es, dout.ptr, lse.ptr, delta.ptr,
+                                                      d, d + E * es, d + 2 * E * es, C.byref(p)))
+            return dqkv
         check(self.lib.alpha_flash_attn_bwd(b, b + E * es, b + 2 * E * es, out.ptr, dout.ptr, lse.ptr,
                                             d, d + E * es, d + 2 * E * es, C.byref(p)))
         return dqkv
+
+    def rowdotSupported(self, g: TensorData, o: TensorData, H: int) -> bool:
+        """Whether matmulRowdot / attentionQkvBackward(delta=) apply: bf16, head dim 64."""
+        return g.dtype == "bf16" and o.dtype == "bf16" and o.shape[-1] == 64 * H
+
+    def matmulRowdot(self, g: TensorData, w: TensorData, o: TensorData, T: int, H: int):
+        """(G @ W, delta): the gradient of the attention output, dO = G @ W for G [rows, N], W [N, E],
+        together with delta[b, h, t] = sum_d dO * O over each head's 64 columns, from one GEMM
+        launch (the row-dot is taken in the epilogue, on dO as rounded to bf16)."""
+        N, E = w.shape
+        rows = g.size // N
+        dO = self._new(o.shape, o.dtype)
+        delta = self._new((rows // T, H, T), "f32")
+        check(self.lib.alpha_gemm_nn_rowdot(g.ptr, w.ptr, dO.ptr, rows, E, N, N, E, E, o.ptr, E, delta.ptr, T, H))
+        return dO, delta
 
     # ── optimizer (interfaces.ts:149-150) ────────────────────────────────────
     def adamwStep(self, params, grads, m, v, lr, beta1, beta2, eps, weightDecay, bc1, bc2, gradScale=1.0,

@@ -1339,8 +1339,10 @@ int attn_tc_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf ls
   return 0;
 }
 
+// `delta_in` != 0: the row-dots dO.O, [batch, heads, T] f32, already computed by the caller
+// (alpha_gemm_nn_rowdot); `o` is then not read.
 int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_o, alpha_buf lse, alpha_buf dq,
-                alpha_buf dk, alpha_buf dv, const alpha_attn_params_t *p) {
+                alpha_buf dk, alpha_buf dv, const alpha_attn_params_t *p, alpha_buf delta_in) {
   if (p->batch * p->heads * p->T == 0) return 0;
   ProfScope prof(PROF_ATTN_BWD, 8.0 * p->batch * p->heads * (double)p->T * p->T * p->D);
   CUtensorMap tq, tk, tv, tdo;
@@ -1350,11 +1352,15 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   if (get_tmap4(&tdo, ptr<void>(d_o), p, p->o_st, p->o_sh, p->o_sb, 128)) return 1;
   const int64_t rows = p->batch * p->heads * p->T;
   void *delta = nullptr;
-  if (pool_alloc((size_t)rows * sizeof(float), &delta)) return 1;
-  ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_delta_kernel, dim3(grid_for(rows, 32, 16)), dim3(256), 0,
-                               (const __nv_bfloat16 *)ptr<__nv_bfloat16>(o), (const __nv_bfloat16 *)ptr<__nv_bfloat16>(d_o),
-                               (float *)delta, p->o_sb, p->o_sh, p->o_st, (int)p->heads, (int)p->T, rows));
-  g_launches++;
+  if (delta_in) {
+    delta = ptr<void>(delta_in);
+  } else {
+    if (pool_alloc((size_t)rows * sizeof(float), &delta)) return 1;
+    ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_delta_kernel, dim3(grid_for(rows, 32, 16)), dim3(256), 0,
+                                 (const __nv_bfloat16 *)ptr<__nv_bfloat16>(o), (const __nv_bfloat16 *)ptr<__nv_bfloat16>(d_o),
+                                 (float *)delta, p->o_sb, p->o_sh, p->o_st, (int)p->heads, (int)p->T, rows));
+    g_launches++;
+  }
   AttnBwdArgs a;
   memset(&a, 0, sizeof(a));
   a.dq = ptr<void>(dq); a.dk = ptr<void>(dk); a.dv = ptr<void>(dv);
@@ -1377,11 +1383,12 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
   // to a workspace and a second, HBM-bound kernel adds them per query block in key-block order.
   void *part = nullptr;
   const size_t part_bytes = (size_t)BH * (n_qb * (n_qb + 1) / 2) * 128 * 64 * sizeof(float);
-  if (pool_alloc(part_bytes, &part)) { pool_free(delta); return 1; }
+  if (pool_alloc(part_bytes, &part)) { if (!delta_in) pool_free(delta); return 1; }
   a.dq_part = (float *)part;
   CUtensorMap tpart;
   if (encode_tmap_2d_out(&tpart, part, ALPHA_F32, 64, (uint64_t)BH * (n_qb * (n_qb + 1) / 2) * 128, 64, 32)) {
-    pool_free(part); pool_free(delta);
+    pool_free(part);
+    if (!delta_in) pool_free(delta);
     return 1;
   }
   ALPHA_CUDA(launch_overlapped(OVL_ATTN_BWD, attn_tc_bwd_kernel, dim3(grid), dim3(ABP_THREADS), AK_DYN, tq, tk, tv, tdo, tpart, a, n_items, BH));
@@ -1390,7 +1397,7 @@ int attn_tc_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_
                                (const float *)part, ptr<__nv_bfloat16>(dq), p->q_sb, p->q_sh, p->q_st, (int)p->heads,
                                (int)p->T, n_qb));
   pool_free(part);
-  pool_free(delta);
+  if (!delta_in) pool_free(delta);
   ALPHA_LAUNCHED();
   return 0;
 }

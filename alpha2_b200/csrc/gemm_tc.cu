@@ -37,6 +37,7 @@ namespace alpha {
 using namespace tc;
 
 constexpr int GBM = 128, GBK = 64;
+constexpr int ALPHA_EPI_ROWDOT = 4;   // internal epilogue code (alpha_gemm_nn_rowdot)
 constexpr int GEMM_THREADS = 192;
 
 struct GemmTcArgs {
@@ -47,6 +48,10 @@ struct GemmTcArgs {
   int M, N, K;
   int tiles_m, tiles_n, splits, kb_per_split, kblocks;
   int m_pad;             // split-K: rows per workspace slab (tiles_m * tile rows), >= M
+  // ALPHA_EPI_ROWDOT (internal): C = acc and, per row and 64-column group h (one attention head),
+  // rowdot[(row / rd_T * rd_H + h) * rd_T + row % rd_T] = sum_j bf16(acc[row, 64h + j]) * aux[row, 64h + j]
+  float *rowdot;
+  int rd_T, rd_H;
   int out_f32;           // 1: C is fp32, 0: bf16
   int epilogue, accumulate;
   int tma_epi;           // 1: outputs (and epilogue operands) move through shared memory with TMA
@@ -217,7 +222,8 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   constexpr int CH = 128 / (int)sizeof(OutT);  // columns per staged chunk (64 bf16 / 32 f32)
   constexpr int V = Vec16<OutT>::N;
   const bool gelu = g.epilogue == ALPHA_EPI_GELU;
-  const bool has_in = g.epilogue == ALPHA_EPI_ADD || g.epilogue == ALPHA_EPI_GELU_BWD;
+  const bool rowdot = g.epilogue == ALPHA_EPI_ROWDOT;
+  const bool has_in = g.epilogue == ALPHA_EPI_ADD || g.epilogue == ALPHA_EPI_GELU_BWD || rowdot;
   const uint32_t sw = (uint32_t)(lane & 7);
   const uint64_t policy = l2_policy_evict_first();
 #pragma unroll 1
@@ -252,6 +258,7 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
     if (has_in) {
       if (!mbar_wait(aux_bar, aux_phase, abort_flag)) return false;
       aux_phase ^= 1;
+      float dot = 0.f;   // ROWDOT: this lane's row of one head, (rounded) output times operand
 #pragma unroll
       for (int q = 0; q < 8; q++) {
         Vec16<OutT> t;
@@ -261,9 +268,19 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
         if (g.epilogue == ALPHA_EPI_ADD) {
 #pragma unroll
           for (int j = 0; j < V; j++) v[q * V + j] += x[j];
+        } else if (rowdot) {
+#pragma unroll
+          for (int j = 0; j < V; j++) dot = fmaf(to_f32(from_f32<OutT>(v[q * V + j])), x[j], dot);
         } else {
 #pragma unroll
           for (int j = 0; j < V; j += 2) gelu_grad_mul2(v[q * V + j], v[q * V + j + 1], x[j], x[j + 1]);
+        }
+      }
+      if (rowdot) {
+        const int row = row0 + lane;
+        if (row < g.M) {
+          const int b = row / g.rd_T, tpos = row - b * g.rd_T;
+          g.rowdot[((int64_t)b * g.rd_H + col0 / CH) * g.rd_T + tpos] = dot;
         }
       }
     }
@@ -690,7 +707,7 @@ static int launch_pair_variant(const CUtensorMap &ta, const CUtensorMap &tb, con
 
 int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K, int64_t lda,
                    int64_t ldb, int64_t ldc, int out_dtype, int epilogue, alpha_buf aux, int64_t ld_aux,
-                   int accumulate) {
+                   int accumulate, float *rowdot = nullptr, int rd_T = 0, int rd_H = 0) {
   if (M == 0 || N == 0) return 0;
   ALPHA_CHECK(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "alpha_gemm: dimension exceeds int32");
   ALPHA_CHECK(out_dtype == ALPHA_F32 || out_dtype == ALPHA_BF16, "alpha_gemm: bad out dtype %d", out_dtype);
@@ -777,6 +794,11 @@ int gemm_tc_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M,
     if (epilogue != ALPHA_EPI_NONE && get_tmap_out(&txm, ptr<void>(aux), out_dtype, N, M, ld_aux)) return 1;
     g.tma_epi = 1;
   }
+  if (epilogue == ALPHA_EPI_ROWDOT) {
+    ALPHA_CHECK(g.tma_epi && out_dtype == ALPHA_BF16 && K > 0,
+                "alpha_gemm_nn_rowdot: needs bf16 output and 16-byte aligned output and operand rows");
+    g.rowdot = rowdot; g.rd_T = rd_T; g.rd_H = rd_H;
+  }
   if (splits > 1 && N % 4 == 0) {
     // the partial products leave through shared memory and TMA stores as well (full lines
     // instead of one row per lane); measured on the 3072 x 768 x 16384 weight gradient:
@@ -825,6 +847,21 @@ int gemm_f32_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M
 }  // namespace alpha
 
 using namespace alpha;
+
+// dO = G W with the row-dot of attention's backward in the epilogue: besides C = A B (NN,
+// bf16, N = heads * 64) it writes delta[b, h, t] = sum_d C[b*T + t, 64h + d] * O[b*T + t, 64h + d]
+// (C as rounded to bf16), which alpha_flash_attn_bwd_delta then takes instead of computing it
+// from O and dO in a pass of its own.
+extern "C" int alpha_gemm_nn_rowdot(alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K, int64_t lda,
+                                    int64_t ldb, int64_t ldc, alpha_buf O, int64_t ld_o, alpha_buf delta, int64_t T,
+                                    int64_t heads) {
+  ALPHA_REQUIRE_INIT();
+  ALPHA_CHECK(heads > 0 && N == heads * 64, "alpha_gemm_nn_rowdot: N = %lld is not heads * 64", (long long)N);
+  ALPHA_CHECK(T > 0 && M % T == 0, "alpha_gemm_nn_rowdot: M = %lld is not a multiple of T = %lld", (long long)M, (long long)T);
+  ALPHA_CHECK(O != 0 && delta != 0, "alpha_gemm_nn_rowdot: null operand");
+  return gemm_tc_launch(ALPHA_GEMM_NN, A, B, C, M, N, K, lda, ldb, ldc, ALPHA_BF16, ALPHA_EPI_ROWDOT, O, ld_o, 0,
+                        ptr<float>(delta), (int)T, (int)heads);
+}
 
 extern "C" int alpha_gemm(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K,
                           int64_t lda, int64_t ldb, int64_t ldc, int in_dtype, int out_dtype, int epilogue,

@@ -226,8 +226,7 @@ def _block_fused(ctx: Ctx, cfg: ModelConfig, x: Variable, P: GPTParams, i: int, 
     qkv = ag.linear(ctx, ln1, P[f"{pre}.attn.wqkv"])
     if cfg.rope:
         qkv = ag.ropeQk(ctx, qkv, Bn, T, H)
-    att = ag.attentionQkv(ctx, qkv, Bn, T, H, 1 / math.sqrt(D), cap)
-    x = ag.linearAdd(ctx, att, P[f"{pre}.attn.wo"], x)
+    x = ag.attentionProj(ctx, qkv, P[f"{pre}.attn.wo"], x, Bn, T, H, 1 / math.sqrt(D), cap)
     ln2 = _norm(ctx, cfg, x, P, f"{pre}.ln2")
     if cfg.ffnActivation == "swiglu":
         gate = ag.linear(ctx, ln2, P[f"{pre}.mlp.fc_gate"])

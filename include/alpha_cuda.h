@@ -249,6 +249,14 @@ enum { ALPHA_EPI_NONE = 0, ALPHA_EPI_GELU = 1, ALPHA_EPI_ADD = 2, ALPHA_EPI_GELU
 int alpha_gemm(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K,
                int64_t lda, int64_t ldb, int64_t ldc, int in_dtype, int out_dtype, int epilogue,
                alpha_buf aux, int64_t ld_aux, int accumulate);
+/* C = A B (NN, bf16 in and out, N = heads * 64) whose epilogue also writes, for every row and
+ * head, delta[(row / T) * heads + h][row % T] = sum_d C[row, 64h + d] * O[row, 64h + d] with C as
+ * rounded to bf16: the gradient of the attention output (dO = G Wo) together with the row-dots
+ * attention's backward needs, in one launch (packages/helios/src/kernels/attention.ts:1217-1231
+ * computes them in a pass of their own).  O has leading dimension ld_o; delta is f32. */
+int alpha_gemm_nn_rowdot(alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K,
+                         int64_t lda, int64_t ldb, int64_t ldc, alpha_buf O, int64_t ld_o,
+                         alpha_buf delta, int64_t T, int64_t heads);
 int alpha_gemm_batched_f32(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N,
                            int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch,
                            int64_t stride_a, int64_t stride_b, int64_t stride_c);
@@ -276,6 +284,14 @@ int alpha_flash_attn_fwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alp
 int alpha_flash_attn_bwd(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf o, alpha_buf d_o,
                          alpha_buf lse, alpha_buf dq, alpha_buf dk, alpha_buf dv,
                          const alpha_attn_params_t *p);
+
+/* The same backward when the caller already has delta[b, h, t] = sum_d dO*O (f32 [batch, heads,
+ * T]): the forward output is not read.  bf16 with head dim 64 only (the tensor-core kernels);
+ * anything else is refused and alpha_flash_attn_bwd should be called.  No reference counterpart:
+ * it pairs with alpha_gemm_nn_rowdot, which produces dO and delta in one GEMM. */
+int alpha_flash_attn_bwd_delta(alpha_buf q, alpha_buf k, alpha_buf v, alpha_buf d_o, alpha_buf lse,
+                               alpha_buf delta, alpha_buf dq, alpha_buf dk, alpha_buf dv,
+                               const alpha_attn_params_t *p);
 
 /* RoPE (no reference counterpart; asked for by the 350M configuration): rotate-half
  * convention on x[rows=B*T, heads, D] with row stride ld, angle(t,i) = t * theta^(-2i/D);

@@ -604,6 +604,33 @@ def test_attention_on_fused_qkv(B, dtype, geom):
     assert rel_err(dqkv, ref) < tol * 2
 
 
+@pytest.mark.parametrize("geom", [(2, 128, 2, 192), (3, 200, 12, 768), (16, 1024, 12, 768)])
+def test_rowdot_gemm_feeds_attention_backward(B, geom):
+    """dO = G @ Wo with the row-dots dO.O taken in the GEMM's epilogue (one per row and head of 64
+    columns), and attention's backward fed with them: dO equals the plain GEMM bit for bit, the
+    row-dots equal the f64 products of the rounded values, and the gradients equal those of the
+    backward that computes the row-dots itself."""
+    Bn, T, H, K = geom
+    E, N = 64 * H, Bn * T
+    r = rng(Bn * 7 + T)
+    g = bf16_round(r.standard_normal((N, K)) * 0.1)
+    w = bf16_round(r.standard_normal((K, E)) * 0.1)
+    qkv = bf16_round(r.standard_normal((N, 3 * E)))
+    G, W, QKV = B.upload(g, "bf16"), B.upload(w, "bf16"), B.upload(qkv, "bf16")
+    scale = 1 / math.sqrt(64)
+    out, lse = B.attentionQkv(QKV, Bn, T, H, scale, 30.0)
+    dO, delta = B.matmulRowdot(G, W, out, T, H)
+    plain = B.matmul(G, W)
+    assert np.array_equal(dO.data, plain.data)
+    want = (plain.data.astype(np.float64) * out.data.astype(np.float64)).reshape(Bn, T, H, 64).sum(-1).transpose(0, 2, 1)
+    assert delta.shape == (Bn, H, T)
+    assert float(np.max(np.abs(delta.data - want))) < 1e-5 * max(1.0, float(np.max(np.abs(want))))
+    a = B.attentionQkvBackward(QKV, out, dO, lse, Bn, T, H, scale, 30.0, delta=delta).data
+    b = B.attentionQkvBackward(QKV, out, dO, lse, Bn, T, H, scale, 30.0).data
+    assert float(np.max(np.abs(a - b))) <= 2 ** -7 * float(np.max(np.abs(b)))
+    B.checkAsyncError()
+
+
 def test_rope_matches_oracle_and_inverts(B):
     from oracle import autograd as oag
     from oracle.autograd import Ctx, Tape, Variable
