@@ -378,20 +378,22 @@ constexpr float TANH_POLY_LIMIT2 = 0.1225f;  // x^2 bound of the polynomial bran
 
 struct BwdRowConsts {
   float c1, c2, lse2, scale, delta;  // lse2 = +inf for a query row past the end (its P becomes 0)
+  // polynomial tanh on the raw score s: tanh(c1*s) = s*(c1 + u*(a1 + u*(a2 + u*a3))), u = s^2,
+  // a_k = p_k * c1^(2k+1); u_limit is the largest u it accepts (|c1*s| <= 0.35)
+  float a1, a2, a3, u_limit;
 };
 
 // Phase A for AB_NC scores of one row.  pk: P as packed bf16 pairs; fk: -P * dcap as packed
 // bf16 pairs (dcap = 1 - tanh^2, or 1 without a cap).  The scores are read 16 columns at a
 // time to keep registers free for interleaving the per-pair dependency chains.
-// Returns the largest squared tanh argument seen (0 when not capped).
+// Returns the largest squared score seen by the polynomial branch (0 otherwise).
 template <bool DIAG, bool CAPPED, bool POLY>
 __device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, const BwdRowConsts &k,
                                              uint32_t (&pk)[AB_NC / 2], uint32_t (&fk)[AB_NC / 2]) {
   float big = 0.f;
   const uint64_t c1 = f2_pack(k.c1, k.c1), c2 = f2_pack(k.c2, k.c2), nl = f2_pack(-k.lse2, -k.lse2);
   const uint64_t m1 = f2_pack(-1.f, -1.f);
-  const uint64_t p1 = f2_pack(-0.3333333333f, -0.3333333333f), p2 = f2_pack(0.1333333333f, 0.1333333333f),
-                 p3 = f2_pack(-0.0539682540f, -0.0539682540f);
+  const uint64_t a1 = f2_pack(k.a1, k.a1), a2 = f2_pack(k.a2, k.a2), a3 = f2_pack(k.a3, k.a3);
 #pragma unroll
   for (int part = 0; part < AB_NC / 16; part++) {
     uint32_t r[16];
@@ -402,19 +404,19 @@ __device__ __forceinline__ float bwd_phase_a(uint32_t t_s, int row, int col0, co
       const uint64_t s = f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
       uint64_t e, ndcap = m1;  // ndcap = tanh^2 - 1
       if (CAPPED) {
-        const uint64_t x = f2_mul(s, c1);
         uint64_t th;
         if (POLY) {
-          const uint64_t x2 = f2_mul(x, x);
-          float xa, xb;
-          f2_unpack(x2, xa, xb);
-          big = fmax3(big, xa, xb);
-          uint64_t t = f2_fma(x2, p3, p2);
-          t = f2_fma(t, x2, p1);
-          th = f2_fma(f2_mul(x, x2), t, x);
+          const uint64_t u = f2_mul(s, s);
+          float ua, ub;
+          f2_unpack(u, ua, ub);
+          big = fmax3(big, ua, ub);
+          uint64_t t = f2_fma(u, a3, a2);
+          t = f2_fma(t, u, a1);
+          t = f2_fma(t, u, c1);
+          th = f2_mul(s, t);
         } else {
           float xa, xb;
-          f2_unpack(x, xa, xb);
+          f2_unpack(f2_mul(s, c1), xa, xb);
           th = f2_pack(tanh_approx(xa), tanh_approx(xb));
         }
         e = f2_fma(th, c2, nl);
@@ -488,7 +490,7 @@ __device__ __forceinline__ void bwd_phase_a_any(uint32_t t_s, int row, int col0,
   }
   const float big = diag ? bwd_phase_a<true, true, true>(t_s, row, col0, k, pk, fk)
                          : bwd_phase_a<false, true, true>(t_s, row, col0, k, pk, fk);
-  if (__any_sync(0xffffffffu, !(big <= TANH_POLY_LIMIT2))) {  // also catches NaN
+  if (__any_sync(0xffffffffu, !(big <= k.u_limit))) {  // also catches NaN
     if (diag) bwd_phase_a<true, true, false>(t_s, row, col0, k, pk, fk);
     else bwd_phase_a<false, true, false>(t_s, row, col0, k, pk, fk);
   }
@@ -730,6 +732,13 @@ attn_tc_bwd_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_cons
     k.c1 = capped ? a.scale / a.cap : a.scale * LOG2E;
     k.c2 = a.cap * LOG2E;
     k.scale = a.scale;
+    {
+      const float q = k.c1 * k.c1;
+      k.a1 = k.c1 * q * -0.3333333333f;
+      k.a2 = k.c1 * q * q * 0.1333333333f;
+      k.a3 = k.c1 * q * q * q * -0.0539682540f;
+      k.u_limit = TANH_POLY_LIMIT2 / q;
+    }
     uint8_t *p_row = smem + AK_P + (colq >> 1) * AT_TILE + row * 128;
     uint8_t *ds_row = smem + AK_DS + (colq >> 1) * AT_TILE + row * 128;
     int t = 0;
@@ -936,15 +945,35 @@ constexpr int AF2_LSUM = AF2_BAR + 256;                    // [4 items][4 column
 constexpr int AF2_DYN = AF2_LSUM + 8192 + 1024;
 constexpr float AF2_MAX_C2 = 50.f;                         // largest cap*log2(e) this kernel accepts
 
-// P for 32 scores of one row (bounded-score softmax).  Returns the largest squared tanh
-// argument seen; adds the row's probabilities to lsum.
+// Constants of the bounded-score softmax with the polynomial tanh, folded so that the exponent
+// comes straight from the raw score s:  c2*tanh(c1*s) - c2 = s*(b0 + u*(b1 + u*(b2 + u*b3))) - c2
+// with u = s^2 and b_k = c2 * p_k * c1^(2k+1)  (p = 1, -1/3, 2/15, -17/315).
+struct Fwd2Consts {
+  float c1, c2;      // scale / cap, cap * log2(e)
+  float b0, b1, b2, b3;
+  float u_limit;     // largest s^2 the polynomial branch accepts (|c1*s| <= 0.35)
+};
+__device__ __forceinline__ Fwd2Consts fwd2_consts(float scale, float cap) {
+  Fwd2Consts k;
+  k.c1 = scale / cap;
+  k.c2 = cap * 1.4426950408889634f;
+  const float q = k.c1 * k.c1;
+  k.b0 = k.c2 * k.c1;
+  k.b1 = k.b0 * q * -0.3333333333f;
+  k.b2 = k.b0 * q * q * 0.1333333333f;
+  k.b3 = k.b0 * q * q * q * -0.0539682540f;
+  k.u_limit = TANH_POLY_LIMIT2 / q;
+  return k;
+}
+
+// P for 32 scores of one row (bounded-score softmax).  Returns the largest squared score seen
+// (polynomial branch only); adds the row's probabilities to lsum.
 template <bool DIAG, bool POLY>
-__device__ __forceinline__ float fwd2_scores(uint32_t t_s, int row, int col0, float c1f, float c2f, uint64_t &lsum,
+__device__ __forceinline__ float fwd2_scores(uint32_t t_s, int row, int col0, const Fwd2Consts &k, uint64_t &lsum,
                                              uint32_t (&pk)[16]) {
   float big = 0.f;
-  const uint64_t c1 = f2_pack(c1f, c1f), c2 = f2_pack(c2f, c2f), nm = f2_pack(-c2f, -c2f);
-  const uint64_t p1 = f2_pack(-0.3333333333f, -0.3333333333f), p2 = f2_pack(0.1333333333f, 0.1333333333f),
-                 p3 = f2_pack(-0.0539682540f, -0.0539682540f);
+  const uint64_t c1 = f2_pack(k.c1, k.c1), c2 = f2_pack(k.c2, k.c2), nm = f2_pack(-k.c2, -k.c2);
+  const uint64_t b0 = f2_pack(k.b0, k.b0), b1 = f2_pack(k.b1, k.b1), b2 = f2_pack(k.b2, k.b2), b3 = f2_pack(k.b3, k.b3);
 #pragma unroll
   for (int part = 0; part < 2; part++) {
     uint32_t r[16];
@@ -952,23 +981,24 @@ __device__ __forceinline__ float fwd2_scores(uint32_t t_s, int row, int col0, fl
     tmem_ld_wait();
 #pragma unroll
     for (int i = 0; i < 16; i += 2) {
-      const uint64_t x = f2_mul(f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), c1);
-      uint64_t th;
+      const uint64_t s = f2_pack(__uint_as_float(r[i]), __uint_as_float(r[i + 1]));
+      uint64_t e;
       if (POLY) {
-        const uint64_t x2 = f2_mul(x, x);
-        float xa, xb;
-        f2_unpack(x2, xa, xb);
-        big = fmax3(big, xa, xb);
-        uint64_t t = f2_fma(x2, p3, p2);
-        t = f2_fma(t, x2, p1);
-        th = f2_fma(f2_mul(x, x2), t, x);
+        const uint64_t u = f2_mul(s, s);
+        float ua, ub;
+        f2_unpack(u, ua, ub);
+        big = fmax3(big, ua, ub);
+        uint64_t t = f2_fma(u, b3, b2);
+        t = f2_fma(t, u, b1);
+        t = f2_fma(t, u, b0);
+        e = f2_fma(s, t, nm);
       } else {
         float xa, xb;
-        f2_unpack(x, xa, xb);
-        th = f2_pack(tanh_approx(xa), tanh_approx(xb));
+        f2_unpack(f2_mul(s, c1), xa, xb);
+        e = f2_fma(f2_pack(tanh_approx(xa), tanh_approx(xb)), c2, nm);
       }
       float ea, eb;
-      f2_unpack(f2_fma(th, c2, nm), ea, eb);
+      f2_unpack(e, ea, eb);
       float pa = ex2_approx(ea), pb = ex2_approx(eb);
       if (DIAG) {
         const int c = col0 + part * 16 + i;
@@ -1156,8 +1186,7 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
     const int col0 = colq * 32;
     const int row = quad * 32 + lane;
     const uint32_t lane_off = (uint32_t)(quad * 32) << 16;
-    const float LOG2E = 1.4426950408889634f;
-    const float c1 = a.scale / a.cap, c2 = a.cap * LOG2E;
+    const Fwd2Consts kc = fwd2_consts(a.scale, a.cap);
     int t = 0, n = 0;
     bool ok = true;
     for (int item = snake_item(0); item < n_items && ok; item = snake_item(++n)) {
@@ -1173,12 +1202,12 @@ attn_tc_fwd2_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_con
         uint32_t pk[16];
         const bool diag = j == qb;
         const uint64_t l_before = lsum;
-        const float big = diag ? fwd2_scores<true, true>(t_s, row, col0, c1, c2, lsum, pk)
-                               : fwd2_scores<false, true>(t_s, row, col0, c1, c2, lsum, pk);
-        if (__any_sync(0xffffffffu, !(big <= TANH_POLY_LIMIT2))) {  // out of the polynomial's range (or NaN)
+        const float big = diag ? fwd2_scores<true, true>(t_s, row, col0, kc, lsum, pk)
+                               : fwd2_scores<false, true>(t_s, row, col0, kc, lsum, pk);
+        if (__any_sync(0xffffffffu, !(big <= kc.u_limit))) {  // out of the polynomial's range (or NaN)
           lsum = l_before;
-          if (diag) fwd2_scores<true, false>(t_s, row, col0, c1, c2, lsum, pk);
-          else fwd2_scores<false, false>(t_s, row, col0, c1, c2, lsum, pk);
+          if (diag) fwd2_scores<true, false>(t_s, row, col0, kc, lsum, pk);
+          else fwd2_scores<false, false>(t_s, row, col0, kc, lsum, pk);
         }
         // the P buffer is free once O += P V of two tiles ago has read it
         if (tt >= 2 && !mbar_wait(p_free0 + 8 * buf, ((tt >> 1) - 1) & 1, abort_flag)) { ok = false; break; }

@@ -546,6 +546,70 @@ __global__ void __launch_bounds__(LN_CTA) ln_bwd_cta(const T *__restrict__ x, co
 // are warp shuffles only (no block barrier in the loop), dw / db sums stay in registers
 // and are combined across the four warps once at the end, in fixed order.
 constexpr int LR_WARPS = 4, LR_STAGES = 3, LR_THREADS = (LR_WARPS + 1) * 32;
+// The ring kernels keep a row as packed fp32 pairs (two values per 64-bit register) and use
+// the packed add / mul / fma of sm_100: half the issue slots of scalar fp32 for the same,
+// equally rounded, arithmetic.  Pair i of a 16-byte vector holds its elements 2i and 2i + 1.
+template <typename T> struct RowPairs;
+template <> struct RowPairs<float> {
+  static constexpr int NP = 2;
+  static __device__ __forceinline__ void get(const Vec16<float> &v, uint64_t *p) {
+    p[0] = tc::f2_pack(v.raw.x, v.raw.y);
+    p[1] = tc::f2_pack(v.raw.z, v.raw.w);
+  }
+  static __device__ __forceinline__ void set(Vec16<float> &v, const uint64_t *p) {
+    tc::f2_unpack(p[0], v.raw.x, v.raw.y);
+    tc::f2_unpack(p[1], v.raw.z, v.raw.w);
+  }
+};
+template <> struct RowPairs<__nv_bfloat16> {
+  static constexpr int NP = 4;
+  static __device__ __forceinline__ void get(const Vec16<__nv_bfloat16> &v, uint64_t *p) {
+    p[0] = tc::bf16x2_to_f2(v.raw.x);
+    p[1] = tc::bf16x2_to_f2(v.raw.y);
+    p[2] = tc::bf16x2_to_f2(v.raw.z);
+    p[3] = tc::bf16x2_to_f2(v.raw.w);
+  }
+  static __device__ __forceinline__ void set(Vec16<__nv_bfloat16> &v, const uint64_t *p) {
+    float a, b;
+    tc::f2_unpack(p[0], a, b); v.raw.x = tc::bf16x2_pack(a, b);
+    tc::f2_unpack(p[1], a, b); v.raw.y = tc::bf16x2_pack(a, b);
+    tc::f2_unpack(p[2], a, b); v.raw.z = tc::bf16x2_pack(a, b);
+    tc::f2_unpack(p[3], a, b); v.raw.w = tc::bf16x2_pack(a, b);
+  }
+};
+__device__ __forceinline__ float pair_total(uint64_t v) {
+  float a, b;
+  tc::f2_unpack(v, a, b);
+  return a + b;
+}
+__device__ __forceinline__ uint64_t pair_of(float v) { return tc::f2_pack(v, v); }
+// Mean (0 for RMSNorm) and 1/std of a row held as NP2 pairs per lane; on return the pairs are
+// centred (x - mean).
+template <int NP2, bool RMS>
+__device__ __forceinline__ void row_stats(uint64_t (&xp)[NP2], float inv_dim, float eps, float &rstd) {
+  using namespace tc;
+  if (RMS) {
+    uint64_t acc = f2_mul(xp[0], xp[0]);
+#pragma unroll
+    for (int j = 1; j < NP2; j++) acc = f2_fma(xp[j], xp[j], acc);
+    rstd = rsqrtf(warp_sum(pair_total(acc)) * inv_dim + eps);
+  } else {
+    uint64_t acc = xp[0];
+#pragma unroll
+    for (int j = 1; j < NP2; j++) acc = f2_add(acc, xp[j]);
+    const float mean = warp_sum(pair_total(acc)) * inv_dim;
+    const uint64_t nm = pair_of(-mean);
+    xp[0] = f2_add(xp[0], nm);
+    uint64_t q = f2_mul(xp[0], xp[0]);
+#pragma unroll
+    for (int j = 1; j < NP2; j++) {
+      xp[j] = f2_add(xp[j], nm);
+      q = f2_fma(xp[j], xp[j], q);
+    }
+    rstd = 1.f / sqrtf(warp_sum(pair_total(q)) * inv_dim + eps);
+  }
+}
+
 // Position of per-column constant c (weight, bias) in shared memory: a lane owns V consecutive
 // columns per vector and reads them as float4s, so the float4s of one (vector, quarter) are laid
 // side by side across the 32 lanes (16-byte lane stride: no bank conflicts) instead of V*4 bytes apart.
@@ -567,7 +631,6 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
             uint32_t *err) {
   using namespace tc;
   constexpr int V = Vec16<T>::N;
-  constexpr int NE = NV * V;  // elements per lane per row
   constexpr int NS = HAS_ADD ? 3 : 2;
   extern __shared__ __align__(128) uint8_t lr_smem[];
   const uint32_t row_bytes = (uint32_t)dim * sizeof(T);
@@ -579,41 +642,66 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
   volatile uint32_t *abort_flag = (volatile uint32_t *)(lr_smem + LR_STAGES * stage_bytes + 16 * LR_STAGES);
   float *w_sm = reinterpret_cast<float *>(lr_smem + LR_STAGES * stage_bytes + 64);  // the weight row
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
+  auto load_group = [&](int s, int64_t grp) {
+    const int64_t r0 = grp * LR_WARPS;
+    const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
+    const uint32_t dst = ring + s * stage_bytes;
+    if (elect_one()) {
+      mbar_expect_tx(full_bar(s), NS * bytes);
+      bulk_load_1d(dst, x + r0 * dim, bytes, full_bar(s));
+      bulk_load_1d(dst + slab, g + r0 * dim, bytes, full_bar(s));
+      if (HAS_ADD) bulk_load_1d(dst + 2 * slab, dx_add + r0 * dim, bytes, full_bar(s));
+    }
+    __syncwarp();
+  };
+  // The producer warp sets the barriers up and fills the whole ring before the block's first
+  // barrier, so that the first rows are on their way while the workers fetch the weight row.
+  if (warp == LR_WARPS) {
+    if (lane == 0) {
+      for (int s = 0; s < LR_STAGES; s++) {
+        mbar_init(full_bar(s), 1);
+        mbar_init(empty_bar(s), LR_WARPS);
+      }
+      *abort_flag = 0;
+      fence_barrier_init();
+      fence_proxy_async();
+    }
+    __syncwarp();
+  }
   grid_dependency_trigger();
   grid_dependency_wait();
-  for (int c = threadIdx.x; c < dim; c += LR_THREADS) w_sm[lr_const_pos<V>(c)] = w[c];
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < LR_STAGES; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), LR_WARPS);
+  int p_i = 0;                     // producer cursor: groups issued so far, next group
+  int64_t p_grp = blockIdx.x;
+  if (warp == LR_WARPS)
+    for (; p_i < LR_STAGES && p_grp < n_groups; p_i++, p_grp += gridDim.x) load_group(p_i, p_grp);
+  {
+    constexpr int TRIPS = (NV * 32 * V + LR_THREADS - 1) / LR_THREADS;  // dim <= NV * 32 * V: a fixed trip count
+    float wv[TRIPS];
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+      const int c = threadIdx.x + k * LR_THREADS;
+      wv[k] = c < dim ? w[c] : 0.f;
     }
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async();
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+      const int c = threadIdx.x + k * LR_THREADS;
+      if (c < dim) w_sm[lr_const_pos<V>(c)] = wv[k];
+    }
   }
   __syncthreads();
-  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
 
-  float dw_acc[NE], db_acc[NE];
+  constexpr int NP = RowPairs<T>::NP, NP2 = NV * NP;  // pairs per vector, per lane and row
+  uint64_t dw_acc[NP2], db_acc[NP2];
 #pragma unroll
-  for (int j = 0; j < NE; j++) dw_acc[j] = db_acc[j] = 0.f;
+  for (int j = 0; j < NP2; j++) dw_acc[j] = db_acc[j] = 0ull;
 
   if (warp == LR_WARPS) {
-    // producer
-    int i = 0;
-    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
-      const int s = i % LR_STAGES;
-      if (!mbar_wait(empty_bar(s), ((i / LR_STAGES) & 1) ^ 1, abort_flag)) break;
-      const int64_t r0 = grp * LR_WARPS;
-      const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
-      const uint32_t dst = ring + s * stage_bytes;
-      if (elect_one()) {
-        mbar_expect_tx(full_bar(s), NS * bytes);
-        bulk_load_1d(dst, x + r0 * dim, bytes, full_bar(s));
-        bulk_load_1d(dst + slab, g + r0 * dim, bytes, full_bar(s));
-        if (HAS_ADD) bulk_load_1d(dst + 2 * slab, dx_add + r0 * dim, bytes, full_bar(s));
-      }
-      __syncwarp();
+    // producer: the rest of the groups, each into a slot the workers have released
+    for (; p_grp < n_groups; p_grp += gridDim.x, p_i++) {
+      const int s = p_i % LR_STAGES;
+      if (!mbar_wait(empty_bar(s), ((p_i / LR_STAGES) & 1) ^ 1, abort_flag)) break;
+      load_group(s, p_grp);
     }
   } else {
     const float inv_dim = 1.f / (float)dim;
@@ -623,7 +711,7 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
       if (!mbar_wait(full_bar(s), (i / LR_STAGES) & 1, abort_flag)) break;
       const int64_t r = grp * LR_WARPS + warp;
       const uint8_t *src = lr_smem + s * stage_bytes + warp * row_bytes;
-      float xv[NE], gv[NE];
+      uint64_t xp[NP2], gp[NP2];
       Vec16<T> av[NV];
 #pragma unroll
       for (int v = 0; v < NV; v++) {
@@ -631,8 +719,8 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
         t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
         u.load(reinterpret_cast<const T *>(src + slab + (v * 32 + lane) * 16));
         if (HAS_ADD) av[v].load(reinterpret_cast<const T *>(src + 2 * slab + (v * 32 + lane) * 16));
-        t.get(&xv[v * V]);
-        u.get(&gv[v * V]);
+        RowPairs<T>::get(t, &xp[v * NP]);
+        RowPairs<T>::get(u, &gp[v * NP]);
       }
       // The rows were read through the generic proxy and the slot's next contents arrive through
       // the async proxy (bulk copy): without this fence the refill may overtake the reads.
@@ -640,60 +728,49 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the stage may be refilled
       if (r >= rows) continue;                   // warp-uniform (a short last group)
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
-      sum = warp_sum(sum);
-      float mean = 0.f, rstd;
-      if (RMS) {
-        rstd = rsqrtf(sum * inv_dim + eps);
-      } else {
-        mean = sum * inv_dim;
-        float q = 0.f;
-#pragma unroll
-        for (int j = 0; j < NE; j++) {
-          const float d = xv[j] - mean;
-          q += d * d;
-        }
-        q = warp_sum(q);
-        rstd = 1.f / sqrtf(q * inv_dim + eps);
-      }
-      float s1 = 0.f, s2 = 0.f;
+      float rstd;
+      row_stats<NP2, RMS>(xp, inv_dim, eps, rstd);
+      const uint64_t rs2 = pair_of(rstd);
+      uint64_t s1 = 0ull, s2 = 0ull;
 #pragma unroll
       for (int v = 0; v < NV; v++)
 #pragma unroll
-        for (int j4 = 0; j4 < V; j4 += 4) {
-          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + ((v * (V / 4) + j4 / 4) * 32 + lane) * 4);
-          const float wq[4] = {w4.x, w4.y, w4.z, w4.w};
+        for (int h = 0; h < NP / 2; h++) {   // one float4 of weights = two pairs
+          const ulonglong2 w2 = *reinterpret_cast<const ulonglong2 *>(w_sm + ((v * (V / 4) + h) * 32 + lane) * 4);
+          const uint64_t wq[2] = {w2.x, w2.y};
 #pragma unroll
-          for (int q = 0; q < 4; q++) {
-            const int j = v * V + j4 + q;
-            const float xhat = (xv[j] - mean) * rstd;
-            const float dy = gv[j] * wq[q];
-            dw_acc[j] += gv[j] * xhat;
-            db_acc[j] += gv[j];
-            s1 += dy;
-            s2 += dy * xhat;
-            xv[j] = xhat;
-            gv[j] = dy;
+          for (int q = 0; q < 2; q++) {
+            const int j = v * NP + h * 2 + q;
+            const uint64_t xhat = f2_mul(xp[j], rs2);
+            const uint64_t dy = f2_mul(gp[j], wq[q]);
+            dw_acc[j] = f2_fma(gp[j], xhat, dw_acc[j]);
+            db_acc[j] = f2_add(db_acc[j], gp[j]);
+            s1 = f2_add(s1, dy);
+            s2 = f2_fma(dy, xhat, s2);
+            xp[j] = xhat;
+            gp[j] = dy;
           }
         }
-      s1 = RMS ? 0.f : warp_sum(s1);
-      s2 = warp_sum(s2);
+      const float s1t = RMS ? 0.f : warp_sum(pair_total(s1));
+      const float s2t = warp_sum(pair_total(s2));
+      const uint64_t s1p = pair_of(s1t), s2p = pair_of(s2t), ninv = pair_of(-inv_dim);
       T *dr = dx + r * dim;
 #pragma unroll
       for (int v = 0; v < NV; v++) {
-        float o[V];
+        uint64_t o[NP];
 #pragma unroll
-        for (int j = 0; j < V; j++) o[j] = rstd * (gv[v * V + j] - (s1 + xv[v * V + j] * s2) * inv_dim);
+        for (int j = 0; j < NP; j++) {
+          const uint64_t t = f2_fma(xp[v * NP + j], s2p, s1p);
+          o[j] = f2_mul(f2_fma(t, ninv, gp[v * NP + j]), rs2);
+        }
         if (HAS_ADD) {
-          float e[V];
-          av[v].get(e);
+          uint64_t e[NP];
+          RowPairs<T>::get(av[v], e);
 #pragma unroll
-          for (int j = 0; j < V; j++) o[j] += e[j];
+          for (int j = 0; j < NP; j++) o[j] = f2_add(o[j], e[j]);
         }
         Vec16<T> t;
-        t.set(o);
+        RowPairs<T>::set(t, o);
         t.store(dr + (v * 32 + lane) * V);
       }
     }
@@ -706,12 +783,10 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
 #pragma unroll
     for (int v = 0; v < NV; v++)
 #pragma unroll
-      for (int j = 0; j < V; j += 4) {
-        const int c = (v * 32 + lane) * V + j;
-        *reinterpret_cast<float4 *>(mine + c) =
-            make_float4(dw_acc[v * V + j], dw_acc[v * V + j + 1], dw_acc[v * V + j + 2], dw_acc[v * V + j + 3]);
-        *reinterpret_cast<float4 *>(mine + dim + c) =
-            make_float4(db_acc[v * V + j], db_acc[v * V + j + 1], db_acc[v * V + j + 2], db_acc[v * V + j + 3]);
+      for (int h = 0; h < NP / 2; h++) {
+        const int c = (v * 32 + lane) * V + h * 4;
+        *reinterpret_cast<ulonglong2 *>(mine + c) = make_ulonglong2(dw_acc[v * NP + 2 * h], dw_acc[v * NP + 2 * h + 1]);
+        *reinterpret_cast<ulonglong2 *>(mine + dim + c) = make_ulonglong2(db_acc[v * NP + 2 * h], db_acc[v * NP + 2 * h + 1]);
       }
   }
   __syncthreads();
@@ -731,7 +806,11 @@ ln_bwd_ring(const T *__restrict__ x, const float *__restrict__ w, const T *__res
 }
 
 // Forward with the same structure: four worker warps, one row each per group, x streamed
-// through a 4-stage bulk-copy ring; weight and bias rows sit in shared memory.
+// through a 4-stage bulk-copy ring; weight and bias rows sit in shared memory.  Measured at
+// 16384 x 768 bf16: a deeper ring (up to all of a block's rows in flight at once) is slower,
+// 19.0 against 16.5 us, and five or six resident blocks per SM (72 / 64 registers) change
+// nothing; a launch over 4 rows takes 7 us in the same harness and 4x the rows add data at
+// 6-7 TB/s, so what is left at this size is the fixed cost of a launch.
 constexpr int LRF_STAGES = 4;
 
 template <typename T, int NV, bool RMS>
@@ -740,7 +819,6 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
             int64_t rows, int dim, float eps, uint32_t *err) {
   using namespace tc;
   constexpr int V = Vec16<T>::N;
-  constexpr int NE = NV * V;
   extern __shared__ __align__(128) uint8_t lr_smem[];
   const uint32_t row_bytes = (uint32_t)dim * sizeof(T);
   const uint32_t stage_bytes = LR_WARPS * row_bytes;
@@ -752,35 +830,60 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
   float *w_sm = reinterpret_cast<float *>(lr_smem + LRF_STAGES * stage_bytes + 128);
   float *b_sm = w_sm + dim;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
+  auto load_group = [&](int s, int64_t grp) {
+    const int64_t r0 = grp * LR_WARPS;
+    const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
+    if (elect_one()) {
+      mbar_expect_tx(full_bar(s), bytes);
+      bulk_load_1d(ring + s * stage_bytes, x + r0 * dim, bytes, full_bar(s));
+    }
+    __syncwarp();
+  };
+  // as in the backward kernel: the producer fills the ring while the workers fetch weight and bias
+  if (warp == LR_WARPS) {
+    if (lane == 0) {
+      for (int s = 0; s < LRF_STAGES; s++) {
+        mbar_init(full_bar(s), 1);
+        mbar_init(empty_bar(s), LR_WARPS);
+      }
+      *abort_flag = 0;
+      fence_barrier_init();
+      fence_proxy_async();
+    }
+    __syncwarp();
+  }
   grid_dependency_trigger();
   grid_dependency_wait();
-  for (int c = threadIdx.x; c < dim; c += LR_THREADS) {
-    w_sm[lr_const_pos<V>(c)] = w[c];
-    b_sm[lr_const_pos<V>(c)] = RMS ? 0.f : b[c];
-  }
-  if (threadIdx.x == 0) {
-    for (int s = 0; s < LRF_STAGES; s++) {
-      mbar_init(full_bar(s), 1);
-      mbar_init(empty_bar(s), LR_WARPS);
+  int p_i = 0;
+  int64_t p_grp = blockIdx.x;
+  if (warp == LR_WARPS)
+    for (; p_i < LRF_STAGES && p_grp < n_groups; p_i++, p_grp += gridDim.x) load_group(p_i, p_grp);
+  {
+    // dim <= NV * 32 * V: a fixed trip count lets all of a thread's loads be in flight together
+    constexpr int TRIPS = (NV * 32 * V + LR_THREADS - 1) / LR_THREADS;
+    float wv[TRIPS], bv[TRIPS];
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+      const int c = threadIdx.x + k * LR_THREADS;
+      wv[k] = c < dim ? w[c] : 0.f;
+      bv[k] = (!RMS && c < dim) ? b[c] : 0.f;
     }
-    *abort_flag = 0;
-    fence_barrier_init();
-    fence_proxy_async();
+#pragma unroll
+    for (int k = 0; k < TRIPS; k++) {
+      const int c = threadIdx.x + k * LR_THREADS;
+      if (c < dim) {
+        w_sm[lr_const_pos<V>(c)] = wv[k];
+        b_sm[lr_const_pos<V>(c)] = bv[k];
+      }
+    }
   }
   __syncthreads();
-  const int64_t n_groups = (rows + LR_WARPS - 1) / LR_WARPS;
   if (warp == LR_WARPS) {
-    int i = 0;
-    for (int64_t grp = blockIdx.x; grp < n_groups; grp += gridDim.x, i++) {
-      const int s = i % LRF_STAGES;
-      if (!mbar_wait(empty_bar(s), ((i / LRF_STAGES) & 1) ^ 1, abort_flag)) break;
-      const int64_t r0 = grp * LR_WARPS;
-      const uint32_t bytes = (uint32_t)min((int64_t)LR_WARPS, rows - r0) * row_bytes;
-      if (elect_one()) {
-        mbar_expect_tx(full_bar(s), bytes);
-        bulk_load_1d(ring + s * stage_bytes, x + r0 * dim, bytes, full_bar(s));
-      }
-      __syncwarp();
+    for (; p_grp < n_groups; p_grp += gridDim.x, p_i++) {
+      const int s = p_i % LRF_STAGES;
+      if (!mbar_wait(empty_bar(s), ((p_i / LRF_STAGES) & 1) ^ 1, abort_flag)) break;
+      load_group(s, p_grp);
     }
   } else {
     const float inv_dim = 1.f / (float)dim;
@@ -790,51 +893,40 @@ ln_fwd_ring(const T *__restrict__ x, const float *__restrict__ w, const float *_
       if (!mbar_wait(full_bar(s), (i / LRF_STAGES) & 1, abort_flag)) break;
       const int64_t r = grp * LR_WARPS + warp;
       const uint8_t *src = lr_smem + s * stage_bytes + warp * row_bytes;
-      float xv[NE];
+      constexpr int NP = RowPairs<T>::NP, NP2 = NV * NP;
+      uint64_t xp[NP2];
 #pragma unroll
       for (int v = 0; v < NV; v++) {
         Vec16<T> t;
         t.load(reinterpret_cast<const T *>(src + (v * 32 + lane) * 16));
-        t.get(&xv[v * V]);
+        RowPairs<T>::get(t, &xp[v * NP]);
       }
       fence_proxy_async();  // generic-proxy reads before the async-proxy refill of the slot
       __syncwarp();
       if (lane == 0) mbar_arrive(empty_bar(s));  // the row is in registers: the slot can be refilled
       if (r >= rows) continue;
-      float sum = 0.f;
-#pragma unroll
-      for (int j = 0; j < NE; j++) sum += RMS ? xv[j] * xv[j] : xv[j];
-      sum = warp_sum(sum);
-      float mean = 0.f, rstd;
-      if (RMS) {
-        rstd = rsqrtf(sum * inv_dim + eps);
-      } else {
-        mean = sum * inv_dim;
-        float q = 0.f;
-#pragma unroll
-        for (int j = 0; j < NE; j++) {
-          const float d = xv[j] - mean;
-          q += d * d;
-        }
-        q = warp_sum(q);
-        rstd = 1.f / sqrtf(q * inv_dim + eps);
-      }
+      float rstd;
+      row_stats<NP2, RMS>(xp, inv_dim, eps, rstd);
+      const uint64_t rs2 = pair_of(rstd);
       T *yr = y + r * dim;
 #pragma unroll
       for (int v = 0; v < NV; v++) {
-        float o[V];
+        uint64_t o[NP];
 #pragma unroll
-        for (int j4 = 0; j4 < V; j4 += 4) {
-          const int cp = ((v * (V / 4) + j4 / 4) * 32 + lane) * 4;
-          const float4 w4 = *reinterpret_cast<const float4 *>(w_sm + cp);
-          const float4 b4 = *reinterpret_cast<const float4 *>(b_sm + cp);
-          o[j4] = (xv[v * V + j4] - mean) * rstd * w4.x + b4.x;
-          o[j4 + 1] = (xv[v * V + j4 + 1] - mean) * rstd * w4.y + b4.y;
-          o[j4 + 2] = (xv[v * V + j4 + 2] - mean) * rstd * w4.z + b4.z;
-          o[j4 + 3] = (xv[v * V + j4 + 3] - mean) * rstd * w4.w + b4.w;
+        for (int h = 0; h < NP / 2; h++) {   // one float4 of weight and of bias = two pairs
+          const int cp = ((v * (V / 4) + h) * 32 + lane) * 4;
+          const ulonglong2 w2 = *reinterpret_cast<const ulonglong2 *>(w_sm + cp);
+          if (RMS) {
+            o[2 * h] = f2_mul(f2_mul(xp[v * NP + 2 * h], rs2), w2.x);
+            o[2 * h + 1] = f2_mul(f2_mul(xp[v * NP + 2 * h + 1], rs2), w2.y);
+          } else {
+            const ulonglong2 b2 = *reinterpret_cast<const ulonglong2 *>(b_sm + cp);
+            o[2 * h] = f2_fma(f2_mul(xp[v * NP + 2 * h], rs2), w2.x, b2.x);
+            o[2 * h + 1] = f2_fma(f2_mul(xp[v * NP + 2 * h + 1], rs2), w2.y, b2.y);
+          }
         }
         Vec16<T> t;
-        t.set(o);
+        RowPairs<T>::set(t, o);
         t.store(yr + (v * 32 + lane) * V);
       }
     }

@@ -10,7 +10,8 @@ plus LayerNorm, AdamW and the embedding scatter-add at the train-step sizes.
 
 Every launch is timed alone with CUDA events on the library's stream after 3 warm-up
 launches; a 256 MiB buffer is overwritten between launches so that each one starts with a
-cold L2.  Printed per op: mean device time, achieved TFLOP/s or GB/s from the algorithmic
+cold L2 (``--flush read`` reads it instead: the lines a kernel evicts are then clean, while
+with the default they are dirty and their write-back is part of what the kernel waits for).  Printed per op: mean device time, achieved TFLOP/s or GB/s from the algorithmic
 work, and the fraction of the measured peak (MEASURED_PEAKS.json: burst figures, since the
 kernel runs alone).
 
@@ -45,8 +46,9 @@ def _peaks():
 
 
 class Bench:
-    def __init__(self, iters: int, cublas: bool = False):
+    def __init__(self, iters: int, cublas: bool = False, flush: str = "write"):
         self.cublas = cublas
+        self.flush = flush
         self.B = CudaBackend(0)
         self.lib = self.B.lib
         self.iters = iters
@@ -57,6 +59,16 @@ class Bench:
         for e in self.ev:
             check(self.lib.alpha_event_create(C.byref(e)))
         self.rng = np.random.default_rng(0)
+        self.scalar = self.B._new((), "f32")
+
+    def flush_l2(self):
+        """write: L2 ends up full of dirty lines of another buffer (what a kernel meets inside a
+        train step, where its predecessor's output is still dirty in L2: its own traffic then
+        also pays for writing those lines back).  read: full of clean lines."""
+        if self.flush == "write":
+            check(self.lib.alpha_memset(self.flush_ptr, 1, 256 << 20))
+        else:
+            check(self.lib.alpha_check_finite(self.flush_ptr, (256 << 20) // 4, L.F32, self.scalar.ptr))
 
     def normal(self, shape, std, dtype="bf16"):
         n = int(np.prod(shape))
@@ -71,7 +83,7 @@ class Bench:
             fn()
         total = 0.0
         for _ in range(self.iters):
-            check(self.lib.alpha_memset(self.flush_ptr, 1, 256 << 20))
+            self.flush_l2()
             check(self.lib.alpha_event_record(self.ev[0].value))
             fn()
             check(self.lib.alpha_event_record(self.ev[1].value))
@@ -259,9 +271,11 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--json", action="store_true")
     ap.add_argument("--cublas", action="store_true", help="time torch.matmul beside every plain GEMM row")
+    ap.add_argument("--flush", choices=["write", "read"], default="write",
+                    help="how L2 is emptied before each launch: by writing (dirty lines, default) or reading (clean lines) 256 MiB")
     args = ap.parse_args()
     tf_peak, gb_peak, src = _peaks()
-    b = Bench(args.iters, args.cublas)
+    b = Bench(args.iters, args.cublas, args.flush)
     rows = []
     for name in (args.op or list(CASES)):
         r = CASES[name](b)
