@@ -39,6 +39,10 @@ if ROOT not in sys.path:
 SAMPLES = 2048
 
 CASES = {
+    "small_gpt_b32_100steps": dict(
+        model=dict(vocabSize=4096, blockSize=256, nLayer=6, nEmbd=384, nHead=6, tied=True, init="plain"),
+        train=dict(iters=100, batchSize=32, lr=3e-4, seed=42), data_seed=5, batch=32, accum=1, steps=100,
+        snapshots=(1, 50, 100)),
     "gpt2_124m_3steps": dict(
         model=dict(vocabSize=50257, blockSize=1024, nLayer=12, nEmbd=768, nHead=12, tied=True, init="plain"),
         train=dict(iters=100, batchSize=1, lr=3e-4, seed=42), data_seed=6, batch=1, accum=1, steps=3,

@@ -10,13 +10,17 @@ same seeded batches:
 * the 350M shape (24 layers, width 1024, context 2048, RMSNorm, SwiGLU, RoPE, untied head) on
   sequences of 1024 tokens with two accumulated micro-steps, 2 steps,
 
-each in fp32 and in bf16 (fp32 master weights and AdamW state).  Tolerances: fp32 — loss within
-1e-4 relative at every step, gradient norm within 2e-3 relative, every parameter tensor's sample
-within 1e-4 relative (L2) plus the absolute floor the other step tests use (AdamW moves an
-element whose gradient is rounding noise by up to about lr); bf16 — loss within 2e-2 relative at
-every step, gradient norm within 1e-1 relative.  The reference's own criterion for this
-comparison is a final-loss difference below 0.01 (apps/cli/src/commands/bench.ts:381-382); it is
-asserted as well.
+each in fp32 and in bf16 (fp32 master weights and AdamW state).  Tolerances, with what the
+committed build measures in brackets: fp32 — loss within 1e-5 relative at every step [8.9e-8
+over the 100 steps, 1.9e-7 at the 124M shape], gradient norm within 5e-4 relative [4.1e-5,
+3.1e-6], every parameter tensor's sample within 1e-4 relative (L2) plus the absolute floor the
+other step tests use (AdamW moves an element whose gradient is rounding noise by up to about
+lr); bf16 — loss within 2e-3 relative at every step [1.9e-4 over the 100 steps, 4.7e-4 at the
+124M shape], gradient norm within 1e-1 relative in runs of up to ten steps [7.6e-3] and, over
+the 100-step run, where the norm itself falls to 0.2 and jitters by a factor of two from step
+to step, within 2e-1 at every step [0.109 at step 65] and 5e-2 on average [0.019].  The
+reference's own criterion for this comparison is a final-loss difference below 0.01
+(apps/cli/src/commands/bench.ts:381-382); it is asserted as well [2.3e-5 in bf16].
 """
 import math
 import os
@@ -63,16 +67,17 @@ def test_step_trajectory_against_the_oracle_fixture(B, case, dtype):
         _, got = _sampled(tr, n)
         assert np.array_equal(got, fx[f"init/{n}/sample"]), n
     f32_run = dtype == "f32"
-    loss_tol, gn_tol = (1e-4, 2e-3) if f32_run else (2e-2, 1e-1)
+    long_run = spec["steps"] > 10
+    loss_tol, gn_tol = (1e-5, 5e-4) if f32_run else (2e-3, 2e-1 if long_run else 1e-1)
     acc = spec["accum"]
-    worst_loss = worst_gn = 0.0
+    worst_loss = worst_gn = sum_gn = 0.0
     for s in range(spec["steps"]):
         micro = [(B.upload(t, "i32"), B.upload(g, "i32")) for t, g in batches[s * acc:(s + 1) * acc]]
         r = tr.train_step(micro)
         assert math.isfinite(r["loss"]) and math.isfinite(r["gradNorm"])
         want_loss, want_gn = float(fx["loss"][s]), float(fx["gradNorm"][s])
         el, eg = abs(r["loss"] - want_loss) / abs(want_loss), abs(r["gradNorm"] - want_gn) / want_gn
-        worst_loss, worst_gn = max(worst_loss, el), max(worst_gn, eg)
+        worst_loss, worst_gn, sum_gn = max(worst_loss, el), max(worst_gn, eg), sum_gn + eg
         assert el < loss_tol, (case, dtype, s, r["loss"], want_loss)
         assert eg < gn_tol, (case, dtype, s, r["gradNorm"], want_gn)
         assert abs(r["lr"] - float(fx["lr"][s])) < 1e-12
@@ -87,6 +92,7 @@ def test_step_trajectory_against_the_oracle_fixture(B, case, dtype):
                 full = float(np.linalg.norm(flat.astype(np.float64)))
                 assert abs(full - float(fx[f"step{s + 1}/{n}/norm"])) <= 1e-4 * full + 4 * lr * 1e-3 * math.sqrt(flat.size)
     assert abs(r["loss"] - float(fx["loss"][-1])) < 0.01     # bench.ts:381-382
+    assert f32_run or sum_gn / spec["steps"] < 5e-2
     print(f"{case} {dtype}: worst relative loss error {worst_loss:.2e}, gradient norm {worst_gn:.2e}")
     B.checkAsyncError()
     del tr
