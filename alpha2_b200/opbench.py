@@ -202,11 +202,12 @@ def swiglu_case(b: Bench, rows=16384, F=2816, backward=False):
 
 
 def rope_case(b: Bench, Bn=8, T=2048, H=16, D=64):
-    """Rotation of the q and k column blocks of a fused [B*T, 3E] activation into a new tensor."""
+    """Rotation of the q and k column blocks of a fused [B*T, 3E] activation, in place (what the
+    train step does; v is not touched)."""
     B = b.B
     E = H * D
     qkv = b.normal((Bn * T, 3 * E), 1.0)
-    return {"ms": b.time(lambda: B.ropeQkv(qkv, Bn, T, H)), "work": 2.0 * Bn * T * 3 * E * 2, "kind": "byte"}
+    return {"ms": b.time(lambda: B.rope(qkv, Bn, T, 2 * H, D, 3 * E)), "work": 2.0 * Bn * T * 2 * E * 2, "kind": "byte"}
 
 
 def adamw_case(b: Bench, n=124_000_000):
