@@ -13,11 +13,25 @@ three steps and saves its parameters and gradient norms; the parent then runs th
 on one GPU as accumulated micro-steps and compares:
 
 * the replicas are bit-identical to each other,
-* they equal the single-GPU run: fp32 parameters within 2e-6 absolute and the gradient norm
-  within 2e-5 relative (the two runs differ only in the order of one fp32 sum per gradient
-  element); the bf16 case uses the same bounds on its fp32 master weights.  With the bf16 wire
-  format (gradients rounded to bf16 for the exchange) the bounds are those of that rounding:
-  gradient norm within 5e-3, parameters within 2.5 learning rates per step.
+* they equal the single-GPU run.  fp32 case: parameters within 2e-6 absolute and every gradient
+  norm within 2e-5 relative (the two runs differ only in the order of one fp32 sum per gradient
+  element).  bf16 cases: the first step's gradient norm within 2e-5 and the parameters after
+  the first step within 2e-6 on a strided sample of every tensor (the state is identical before
+  that step); after that the runs can drift apart for a reason that has nothing to do with the
+  exchange.  The tied embedding's gradient is summed in a different order in the two runs, so
+  the global norm can differ in its last bits (5.7e-8 at step two in the build measured here),
+  the clip coefficient with it, and then about one master weight in sixty differs in its last
+  fp32 bit; of those, 17 rounded to the other bf16 neighbour in the shadow copies the kernels
+  read, the third step's gradient norm moved by 5.6e-5, and AdamW moved elements whose
+  gradient is that small by up to 0.75 learning rates (2.2e-4; 14 488 of 38.6 M embedding
+  elements above 1e-6).  With three other builds of the kernels the step-two norms happened to
+  be equal to the last bit and everything stayed equal to 7e-8; each kernel is the same in both
+  runs either way.
+  Bounds for steps two and three: norms within 5e-4; every parameter tensor within 2.5 learning
+  rates per step absolute and, in L2, within 1e-4 of its norm plus a twentieth of the largest
+  move AdamW could have made.  With the bf16 wire format (gradients rounded to bf16 for the
+  exchange) the bounds are those of that rounding: gradient norm within 5e-3, parameters within
+  2.5 learning rates per step.
 
 Needs two visible GPUs; skipped otherwise.  NCCL runs with its defaults except NVLS, which is
 switched off because the children exit on their own schedule.
@@ -61,6 +75,11 @@ def _batches(case: dict, rank: int):
     return zipf_batches(100 + rank, STEPS, case["batch"], m["blockSize"], m["vocabSize"])
 
 
+def _sample(a, k: int = 8192):
+    flat = np.asarray(a).reshape(-1)
+    return flat[::max(1, flat.size // k)].copy()
+
+
 def _trainer(B, case: dict, dp=None):
     from alpha2_b200.gpt import ModelConfig
     from alpha2_b200.trainer import TrainConfig, Trainer
@@ -75,11 +94,15 @@ def _worker(args) -> None:
     B = CudaBackend(args.rank)
     dp = DataParallel(B, args.world, args.rank, bytes.fromhex(args.uid), wire=case.get("wire", "f32"))
     tr = _trainer(B, case, dp)
-    res = [tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))]) for t, g in _batches(case, args.rank)]
+    res, first = [], {}
+    for t, g in _batches(case, args.rank):
+        res.append(tr.train_step([(B.upload(t, "i32"), B.upload(g, "i32"))]))
+        if len(res) == 1:                                     # a strided sample of every tensor after the first step
+            first = {f"step1/{n}": _sample(v.data.data) for n, v in tr.entries}
     B.checkAsyncError()
     np.savez(os.path.join(args.out, f"{args.case}_rank{args.rank}.npz"),
              gn=np.array([r["gradNorm"] for r in res]), loss=np.array([r["loss"] for r in res]),
-             **{n: np.array(v.data.data) for n, v in tr.entries})
+             **first, **{n: np.array(v.data.data) for n, v in tr.entries})
     B.lib.alpha_comm_destroy()
 
 
@@ -119,18 +142,31 @@ def test_two_nccl_ranks_equal_one_gpu_with_two_microsteps(tmp_path, case):
         pair = [(B.upload(t, "i32"), B.upload(g, "i32")) for t, g in (b0[i], b1[i])]
         r = tr.train_step(pair)
         gns.append(r["gradNorm"]); losses.append(r["loss"])
+        if i == 0 and spec.get("wire") != "bf16":             # one step from identical state: equal in every dtype
+            for n, v in tr.entries:
+                d1 = float(np.max(np.abs(r0[f"step1/{n}"] - _sample(v.data.data))))
+                assert d1 <= 2e-6, (n, d1)
     B.checkAsyncError()
     # bf16 on the wire: every gradient element carries a relative rounding error of up to 2^-9
     # before the sum, so the norm agrees to a few 1e-3 and AdamW may move an element whose
     # gradient is near zero by up to ~2 lr per step in the other direction
     bf16_wire = spec.get("wire") == "bf16"
-    np.testing.assert_allclose(r0["gn"], gns, rtol=5e-3 if bf16_wire else 2e-5)
+    np.testing.assert_allclose(r0["gn"][:1], gns[:1], rtol=5e-3 if bf16_wire else 2e-5)
+    np.testing.assert_allclose(r0["gn"], gns, rtol=5e-3 if bf16_wire else (5e-4 if spec["dtype"] == "bf16" else 2e-5))
     np.testing.assert_allclose((r0["loss"] + r1["loss"]) / 2, losses, rtol=1e-3 if bf16_wire else 2e-5)
     worst = 0.0
+    bf16_run = spec["dtype"] == "bf16"
     for n, v in tr.entries:
-        d = float(np.max(np.abs(r0[n] - v.data.data)))
+        diff = r0[n].astype(np.float64) - v.data.data
+        d = float(np.max(np.abs(diff)))
         worst = max(worst, d)
-        assert d <= (2.5 * TRAIN["lr"] * STEPS if bf16_wire else 2e-6), (n, d)
+        assert d <= (2.5 * TRAIN["lr"] * STEPS if bf16_run else 2e-6), (n, d)
+        if bf16_run and not bf16_wire:
+            # L2: 1e-4 of the tensor plus a twentieth of what AdamW could have moved it at most
+            # (tensors that start at zero, like the biases, have only the second term to offer)
+            bound = 1e-4 * float(np.linalg.norm(v.data.data.astype(np.float64))) + \
+                0.05 * TRAIN["lr"] * STEPS * float(np.sqrt(diff.size))
+            assert float(np.linalg.norm(diff)) <= bound, (n, float(np.linalg.norm(diff)), bound)
     print(f"{case}: 2 NCCL ranks == 1 GPU x 2 micro-steps; worst parameter difference {worst:.2e}, "
           f"gradient norms {r0['gn'].tolist()} vs {gns}")
 
