@@ -501,6 +501,22 @@ export class CudaBackend implements Backend {
     return [out, lse];
   }
 
+  /** Rotary embedding of `heads` heads of width D in the column block that starts at column
+   *  `colOffset` of x [B*T, ld], in place (`inverse`: the transposed rotation, i.e. the backward).
+   *  For the fused projection [B*T, 3E]: heads = 2H, ld = 3E, colOffset = 0 rotates q and k. */
+  rope(x: TensorData, B: number, T: number, heads: number, D: number, ld: number, colOffset = 0, theta = 10000, inverse = false): void {
+    const p = this.addr(x) + BigInt(colOffset * SIZE[x.dtype]);
+    check(C.alpha_rope(p, p, BigInt(B), BigInt(T), BigInt(heads), BigInt(D), BigInt(ld), theta, inverse ? 1 : 0, CODE[x.dtype]));
+    this.invalidate(x);
+  }
+  /** The same for q and k of a fused [B*T, 3E] activation into a new tensor (v copied). */
+  ropeQkv(qkv: TensorData, B: number, T: number, H: number, theta = 10000, inverse = false): TensorData {
+    const D = qkv.shape[1] / 3 / H;
+    const out = this.make(qkv.shape, qkv.dtype as DType);
+    check(C.alpha_rope_qkv(this.addr(qkv), this.addr(out), BigInt(B), BigInt(T), BigInt(H), BigInt(D), theta, inverse ? 1 : 0, CODE[qkv.dtype]));
+    return out;
+  }
+
   // ── optimizer (interfaces.ts:149-150) ────────────────────────────────────────────
   adamwStep(params: TensorData, grads: TensorData, m: TensorData, v: TensorData, lr: number, beta1: number, beta2: number, eps: number, weightDecay: number, bc1: number, bc2: number, gradScale = 1, shadow?: TensorData): void {
     check(C.alpha_adamw(this.addr(params), this.addr(grads), this.addr(m), this.addr(v), BigInt(sizeOf(params.shape)), lr, beta1, beta2, eps, weightDecay, bc1, bc2, gradScale, CODE[grads.dtype], shadow ? this.addr(shadow) : 0n));
