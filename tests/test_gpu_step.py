@@ -154,14 +154,19 @@ def test_config5_shape_small(B):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("arch", ["gpt2", "rms_rope_swiglu"])
 @pytest.mark.parametrize("dtype", ["f32", "bf16"])
-def test_activation_checkpointing_on_the_device(B, dtype):
+def test_activation_checkpointing_on_the_device(B, dtype, arch):
     """Every block recomputed during backward (packages/autograd/src/checkpoint.ts): same
-    losses and parameters as the plain run, bit for bit (the kernels are deterministic)."""
+    losses and parameters as the plain run, bit for bit (the kernels are deterministic).  The
+    second architecture rotates q and k in place on the projection's output, which the
+    recompute has to produce afresh."""
     from alpha2_b200.gpt import ModelConfig
     from alpha2_b200.trainer import TrainConfig, Trainer
-    mc = ModelConfig(vocabSize=512, blockSize=128, nLayer=3, nEmbd=128, nHead=2, tied=True, init="plain",
-                     compute_dtype=dtype)
+    extra = dict(tied=True) if arch == "gpt2" else dict(tied=False, ffnActivation="swiglu", ffnDim=352, norm="rms",
+                                                        rope=True, softCap=0.0)
+    mc = ModelConfig(vocabSize=512, blockSize=128, nLayer=3, nEmbd=128, nHead=2, init="plain",
+                     compute_dtype=dtype, **extra)
     batches = otrain.zipf_batches(9, 3, 4, 128, 512)
     runs = []
     for ck in (False, True):

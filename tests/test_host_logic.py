@@ -110,7 +110,11 @@ def test_product_rng_equals_oracle_rng():
     assert np.array_equal(a.fill_gauss((7, 9), 0.02), b.fill_gauss((7, 9), 0.02))
 
 
-def test_activation_checkpointing_matches_plain_training():
+@pytest.mark.parametrize("arch", [dict(tied=True),
+                                  # rotary embedding is applied in place on the projection's output: the
+                                  # recompute must start from a fresh projection, not from the rotated one
+                                  dict(tied=False, ffnActivation="swiglu", ffnDim=48, norm="rms", rope=True, softCap=0.0)])
+def test_activation_checkpointing_matches_plain_training(arch):
     """packages/tests/src/autograd.test.ts:157-189 (checkpoint equivalence): the same steps
     with every block checkpointed give the same losses and parameters, bit for bit on a
     deterministic backend, while the outer tape holds one entry per block."""
@@ -119,7 +123,7 @@ def test_activation_checkpointing_matches_plain_training():
     from alpha2_b200.gpt import ModelConfig, gptForward
     from alpha2_b200.trainer import TrainConfig, Trainer
     from tests.fake_backend import NumpyBackend, T
-    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=3, nEmbd=32, nHead=2, tied=True, init="plain")
+    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=3, nEmbd=32, nHead=2, init="plain", **arch)
     batches = uniform_batches(5, 3, 2, 16, 64)
     runs = []
     for ck in (False, True):
