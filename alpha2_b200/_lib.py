@@ -104,6 +104,7 @@ SIGNATURES = {
     "alpha_rmsnorm_bwd": [_B, _B, _B, _B, _B, _L, _L, _F, _I, _I, _B],
     "alpha_gemm": [_I, _B, _B, _B, _L, _L, _L, _L, _L, _L, _I, _I, _I, _B, _L, _I],
     "alpha_gemm_nn_rowdot": [_B, _B, _B, _L, _L, _L, _L, _L, _L, _B, _L, _B, _L, _L],
+    "alpha_gemm_tn_pair": [_B, _B, _B, _L, _L, _L, _L, _L, _I, _B, _B, _B, _L, _L, _L, _L, _L, _I, _L],
     "alpha_flash_attn_bwd_delta": [_B, _B, _B, _B, _B, _B, _B, _B, _B, C.POINTER(AttnParams)],
     "alpha_gemm_batched_f32": [_I, _B, _B, _B, _L, _L, _L, _L, _L, _L, _L, _L, _L, _L],
     "alpha_flash_attn_fwd": [_B, _B, _B, _B, _B, C.POINTER(AttnParams)],

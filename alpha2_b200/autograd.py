@@ -531,10 +531,17 @@ def mlpGelu(ctx, x: Variable, w1: Variable, w2: Variable, residual: Variable) ->
     out = B0.matmulTransposedAdd(act, w2d, residual.data)
 
     def bw(g, B, rel, needs, acc):
-        dw2 = _dw_gemm(B, g, act, acc[2]) if needs[2] else None
         dpre = B.matmulGeluBackward(g, w2d, pre)
         dx = B.matmul(dpre, w1d) if needs[0] else None
-        dw1 = _dw_gemm(B, dpre, xd, acc[1]) if needs[1] else None
+        if needs[1] and needs[2] and hasattr(B, "matmulTransposedAPair") and g.dtype == "bf16" and \
+                getattr(B, "param_grads_f32", False) and all(a is None or a.dtype == "f32" for a in (acc[1], acc[2])):
+            # both weight gradients in one launch (each alone would have to split its K)
+            r2, r1 = B.matmulTransposedAPair((g, act, acc[2]), (dpre, xd, acc[1]))
+            dw2 = ACCUMULATED if acc[2] is not None else r2
+            dw1 = ACCUMULATED if acc[1] is not None else r1
+        else:
+            dw2 = _dw_gemm(B, g, act, acc[2]) if needs[2] else None
+            dw1 = _dw_gemm(B, dpre, xd, acc[1]) if needs[1] else None
         return [dx, dw1, dw2, g]
     return _record(ctx, out, [x, w1, w2, residual], bw, in_place=True)
 

@@ -516,6 +516,29 @@ class CudaBackend:
             return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype, out=into, accumulate=True)
         return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype)
 
+    def matmulTransposedAPair(self, first, second) -> list:
+        """Two weight gradients A_i^T @ B_i over the same K in one launch: each argument is
+        (a [K, M], b [K, N], into or None) as for ``matmulTransposedA``; returns the two results.
+        bf16 operands with f32 gradients only; two GEMMs that would each fill half of the device
+        share the launch and need no split over K, any other pair runs as two GEMMs inside the
+        library."""
+        outs, args = [], []
+        K = first[0].size // first[0].shape[-1]
+        for a, b, into in (first, second):
+            Ka, M = a.size // a.shape[-1], a.shape[-1]
+            Kb, N = b.size // b.shape[-1], b.shape[-1]
+            if Ka != K or Kb != K or a.dtype != "bf16" or b.dtype != "bf16" or not self.param_grads_f32:
+                raise AlphaCudaError("matmulTransposedAPair: needs bf16 operands over one K and f32 gradients")
+            if into is not None and (into.size != M * N or into.dtype != "f32"):
+                raise AlphaCudaError(f"matmulTransposedAPair: cannot accumulate into {list(into.shape)} {into.dtype}")
+            out = into if into is not None else self._new((M, N), "f32")
+            outs.append(out)
+            args += [a.ptr, b.ptr, out.ptr, M, N, M, N, N, 1 if into is not None else 0]
+        check(self.lib.alpha_gemm_tn_pair(*args, K))
+        for o in outs:
+            o.invalidate_host()
+        return outs
+
     def matmulInto(self, a: TensorData, b: TensorData, into: TensorData) -> TensorData:
         """into += A @ B for A [rows, K], B [K, N] with the add in the GEMM epilogue (the
         gradient of an activation that already has one from another consumer)."""

@@ -312,11 +312,29 @@ __device__ __forceinline__ bool epilogue_tile_tma(const GemmTcArgs &g, const CUt
   return true;
 }
 
-template <int BN, bool A_MN, bool B_MN, bool PAIR, bool WIDE>
-__device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CUtensorMap &tmap_b,
-                                             const CUtensorMap &tmap_c, const CUtensorMap &tmap_aux,
-                                             const GemmTcArgs &g) {
+// One GEMM of a launch: its operand and output maps and its arguments.
+struct GemmProblem {
+  const CUtensorMap *a, *b, *c, *aux;
+  const GemmTcArgs *g;
+};
+
+// GROUP2: the launch carries a second, independent GEMM of the same layout and K (p1).  The tile
+// walkers take p0's tiles first and p1's after them, so that two GEMMs which alone would each
+// fill half of the device (and would have to split K to fill it) run side by side, unsplit.
+template <int BN, bool A_MN, bool B_MN, bool PAIR, bool WIDE, bool GROUP2 = false>
+__device__ __forceinline__ void gemm_tc_body(const GemmProblem &p0, const GemmProblem &p1) {
   using L = GemmSmemLayout<BN, PAIR, WIDE>;
+  const GemmTcArgs &g = *p0.g;
+  const int tiles_p0 = g.tiles_m * g.tiles_n * g.splits;
+  // the problem a tile index belongs to and the index inside that problem
+  auto problem_of = [&](int tile, int &local) -> const GemmProblem & {
+    if (GROUP2 && tile >= tiles_p0) {
+      local = tile - tiles_p0;
+      return p1;
+    }
+    local = tile;
+    return p0;
+  };
   constexpr int STAGES = L::STAGES;
   constexpr int TILE_M = PAIR ? 2 * GBM : GBM;  // rows of C per tile walker (CTA or CTA pair)
   extern __shared__ uint8_t smem_raw[];
@@ -373,21 +391,28 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
   // start at the same column; each CTA takes all 512 columns of its SM, which puts them at 0.
   if (PAIR && (tmem_base & 0xFFFFu) != 0 && threadIdx.x == 0 && g.err) atomicExch(g.err, 0x6F000000u);
 
-  const int total_tiles = g.tiles_m * g.tiles_n * g.splits;
+  const int total_tiles = tiles_p0 + (GROUP2 ? p1.g->tiles_m * p1.g->tiles_n * p1.g->splits : 0);
 
   if (warp == 0) {
     // ── TMA producer (each CTA loads its own share); the warp runs the loop, one lane issues ──
     {
       if (elect_one()) {
-        tma_prefetch_desc(&tmap_a);
-        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(p0.a);
+        tma_prefetch_desc(p0.b);
+        if (GROUP2) {
+          tma_prefetch_desc(p1.a);
+          tma_prefetch_desc(p1.b);
+        }
       }
       int stage = 0;
       uint32_t phase = 0;
       bool ok = true;
       for (int tile = walker; tile < total_tiles && ok; tile += n_walkers) {
-        int split, mt, nt;
-        tile_coords(g, tile, split, mt, nt);
+        int split, mt, nt, local;
+        const GemmProblem &pr = problem_of(tile, local);
+        const GemmTcArgs &g = *pr.g;
+        const CUtensorMap &tmap_a = *pr.a, &tmap_b = *pr.b;
+        tile_coords(g, local, split, mt, nt);
         const int m0 = mt * TILE_M + (int)rank * GBM;
         const int n0 = nt * BN + (PAIR ? (int)rank * L::B_ROWS : 0);
         const int kb0 = split * g.kb_per_split;
@@ -431,8 +456,9 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       int it = 0;
       bool ok = true;
       for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, it++) {
-        int split, mt, nt;
-        tile_coords(g, tile, split, mt, nt);
+        int split, mt, nt, local;
+        const GemmTcArgs &g = *problem_of(tile, local).g;
+        tile_coords(g, local, split, mt, nt);
         const int kb0 = split * g.kb_per_split;
         const int kb1 = min(g.kblocks, kb0 + g.kb_per_split);
         const int acc = it & 1;
@@ -479,8 +505,12 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
     const uint32_t stage_u32 = smem_base + L::STAGE_OFF + ew * (L::EPI_BUFS * 4096);
     uint32_t aux_phase = 0, chunk_count = 0;
     if (g.tma_epi && lane == 0) {
-      tma_prefetch_desc(&tmap_c);
-      if (g.epilogue != ALPHA_EPI_NONE) tma_prefetch_desc(&tmap_aux);
+      tma_prefetch_desc(p0.c);
+      if (g.epilogue != ALPHA_EPI_NONE) tma_prefetch_desc(p0.aux);
+    }
+    if (GROUP2 && p1.g->tma_epi && lane == 0) {
+      tma_prefetch_desc(p1.c);
+      if (p1.g->epilogue != ALPHA_EPI_NONE) tma_prefetch_desc(p1.aux);
     }
     auto release_acc = [&](int acc) {  // this warp has read its accumulator rows
       tc_fence_before();
@@ -491,8 +521,11 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       }
     };
     for (int tile = walker; tile < total_tiles && ok; tile += n_walkers, it++) {
-      int split, mt, nt;
-      tile_coords(g, tile, split, mt, nt);
+      int split, mt, nt, local;
+      const GemmProblem &pr = problem_of(tile, local);
+      const GemmTcArgs &g = *pr.g;
+      const CUtensorMap &tmap_c = *pr.c, &tmap_aux = *pr.aux;
+      tile_coords(g, local, split, mt, nt);
       const int m0 = mt * TILE_M + (int)rank * GBM, n0 = nt * BN;
       const int acc = it & 1;
       const uint32_t acc_phase = (it >> 1) & 1;
@@ -532,7 +565,7 @@ __device__ __forceinline__ void gemm_tc_body(const CUtensorMap &tmap_a, const CU
       }
       release_acc(acc);
     }
-    if (g.tma_epi && lane == 0) bulk_wait<0>();  // all stores have left shared memory and landed
+    if ((g.tma_epi || (GROUP2 && p1.g->tma_epi)) && lane == 0) bulk_wait<0>();  // all stores have left shared memory and landed
   }
 
   // ── teardown ─────────────────────────────────────────────────────────────
@@ -559,7 +592,8 @@ template <int BN, bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux, GemmTcArgs g) {
-  gemm_tc_body<BN, A_MN, B_MN, false, false>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
+  const GemmProblem p{&tmap_a, &tmap_b, &tmap_c, &tmap_aux, &g};
+  gemm_tc_body<BN, A_MN, B_MN, false, false>(p, p);
 }
 
 // Pair form: clusters of two CTAs, one 256 x 256 tile per pair and step.
@@ -568,7 +602,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmSmemLayout<256, 
 gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
                     const __grid_constant__ CUtensorMap tmap_c, const __grid_constant__ CUtensorMap tmap_aux,
                     GemmTcArgs g) {
-  gemm_tc_body<256, A_MN, B_MN, true, WIDE>(tmap_a, tmap_b, tmap_c, tmap_aux, g);
+  const GemmProblem p{&tmap_a, &tmap_b, &tmap_c, &tmap_aux, &g};
+  gemm_tc_body<256, A_MN, B_MN, true, WIDE>(p, p);
+}
+
+// Pair form carrying two GEMMs (see GROUP2 above).
+struct GemmTmaps {
+  CUtensorMap a, b, c, aux;
+};
+template <bool A_MN, bool B_MN>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(GemmSmemLayout<256, true, false>::THREADS, 1)
+gemm_tc_pair_group2_kernel(const __grid_constant__ GemmTmaps m0, const __grid_constant__ GemmTmaps m1,
+                           const __grid_constant__ GemmTcArgs g0, const __grid_constant__ GemmTcArgs g1) {
+  const GemmProblem p0{&m0.a, &m0.b, &m0.c, &m0.aux, &g0}, p1{&m1.a, &m1.b, &m1.c, &m1.aux, &g1};
+  gemm_tc_body<256, A_MN, B_MN, true, false, true>(p0, p1);
 }
 
 // C (+)= sum_s ws[s]  — split order is fixed, so the result is reproducible.  ws holds
@@ -844,9 +891,103 @@ int gemm_f32_launch(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M
                     int64_t ldb, int64_t ldc, int epilogue, alpha_buf aux, int64_t ld_aux, int accumulate,
                     int64_t batch, int64_t stride_a, int64_t stride_b, int64_t stride_c);
 
+// Two weight gradients in one launch: C_i (+)= A_i^T B_i with A_i [K, M_i], B_i [K, N_i] bf16 and
+// C_i fp32, i = 0, 1, both over the same K.  Alone, each of the step's MLP weight gradients
+// (3072 x 768 and 768 x 3072 over K = 16384) has 36 tiles for 74 CTA pairs and has to split K
+// in two and add the halves in a second kernel; side by side their 72 tiles fill the device
+// unsplit: one launch instead of four and no partial products.  Returns -1 (nothing launched)
+// when the pair does not qualify; the caller then runs the two GEMMs on their own.
+struct TnProblem {
+  alpha_buf A, B, C;
+  int64_t M, N, lda, ldb, ldc;
+  int accumulate;
+};
+static int prepare_tn_problem(const TnProblem &q, int64_t K, GemmTcArgs &g, GemmTmaps &m) {
+  memset(&g, 0, sizeof(g));
+  memset(&m, 0, sizeof(m));
+  const int tile_m = 2 * GBM, BN = 256;
+  g.M = (int)q.M; g.N = (int)q.N; g.K = (int)K;
+  g.tiles_m = (int)((q.M + tile_m - 1) / tile_m);
+  g.tiles_n = (int)((q.N + BN - 1) / BN);
+  g.kblocks = (int)((K + GBK - 1) / GBK);
+  g.kb_per_split = g.kblocks;
+  g.splits = 1;
+  g.m_pad = g.tiles_m * tile_m;
+  g.err = tc_error_word();
+  g.C = ptr<void>(q.C); g.ldc = q.ldc; g.out_f32 = 1; g.tma_epi = 1;
+  // C += A^T B is the residual-add epilogue with C as its own addend
+  g.epilogue = q.accumulate ? ALPHA_EPI_ADD : ALPHA_EPI_NONE;
+  g.accumulate = 0;
+  g.aux_in = ptr<void>(q.C); g.aux_out = ptr<void>(q.C); g.ld_aux = q.ldc;
+  if (get_tmap(&m.a, ptr<void>(q.A), q.M, K, q.lda, 64, 64)) return 1;
+  if (get_tmap(&m.b, ptr<void>(q.B), q.N, K, q.ldb, 64, 64)) return 1;
+  if (get_tmap_out(&m.c, ptr<void>(q.C), ALPHA_F32, q.N, q.M, q.ldc)) return 1;
+  m.aux = m.c;
+  return 0;
+}
+static bool tn_problem_qualifies(const TnProblem &q, int64_t K) {
+  return q.M > GBM && q.N > 128 && K >= GBK && q.M < (1ll << 31) && q.N < (1ll << 31) && K < (1ll << 31) &&
+         (q.A & 15) == 0 && (q.B & 15) == 0 && (q.C & 15) == 0 && (q.lda * 2) % 16 == 0 && (q.ldb * 2) % 16 == 0 &&
+         (q.ldc * 4) % 16 == 0;
+}
+static int gemm_tn_pair_launch(const TnProblem &q0, const TnProblem &q1, int64_t K) {
+  if (!tn_problem_qualifies(q0, K) || !tn_problem_qualifies(q1, K)) return -1;
+  const int64_t t0 = ((q0.M + 255) / 256) * ((q0.N + 255) / 256), t1 = ((q1.M + 255) / 256) * ((q1.N + 255) / 256);
+  const int slots = g_sm_count / 2;
+  // worth it when each would split K on its own and together they still fit one wave
+  if (t0 + t1 > slots || 2 * t0 > slots + t0 / 2 || 2 * t1 > slots + t1 / 2) return -1;
+  GemmTcArgs g0, g1;
+  GemmTmaps m0, m1;
+  if (prepare_tn_problem(q0, K, g0, m0) || prepare_tn_problem(q1, K, g1, m1)) return 1;
+  ProfScope prof(PROF_GEMM_TC, 2.0 * (double)K * ((double)q0.M * (double)q0.N + (double)q1.M * (double)q1.N));
+  using L = GemmSmemLayout<256, true, false>;
+  static int max_pairs = 0, epoch = -1;
+  if (epoch != g_init_epoch) {
+    epoch = g_init_epoch;
+    ALPHA_CUDA(cudaFuncSetAttribute(gemm_tc_pair_group2_kernel<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, L::DYN));
+    cudaLaunchConfig_t cfg;
+    memset(&cfg, 0, sizeof(cfg));
+    cfg.gridDim = dim3(2 * (g_sm_count / 2));
+    cfg.blockDim = dim3(L::THREADS);
+    cfg.dynamicSmemBytes = L::DYN;
+    cudaLaunchAttribute at;
+    at.id = cudaLaunchAttributeClusterDimension;
+    at.val.clusterDim.x = 2; at.val.clusterDim.y = 1; at.val.clusterDim.z = 1;
+    cfg.attrs = &at;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_group2_kernel<true, true>, &cfg) != cudaSuccess || n < 1) {
+      cudaGetLastError();
+      n = g_sm_count / 2;
+    }
+    max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
+  }
+  const int total = (int)(t0 + t1);
+  const int n = total < max_pairs ? total : max_pairs;
+  ALPHA_CUDA(launch_overlapped(OVL_GEMM, gemm_tc_pair_group2_kernel<true, true>, dim3(2 * n), dim3(L::THREADS), L::DYN, m0, m1,
+                               g0, g1));
+  ALPHA_LAUNCHED();
+  return 0;
+}
+
 }  // namespace alpha
 
 using namespace alpha;
+
+extern "C" int alpha_gemm_tn_pair(alpha_buf A0, alpha_buf B0, alpha_buf C0, int64_t M0, int64_t N0, int64_t lda0,
+                                  int64_t ldb0, int64_t ldc0, int accumulate0, alpha_buf A1, alpha_buf B1, alpha_buf C1,
+                                  int64_t M1, int64_t N1, int64_t lda1, int64_t ldb1, int64_t ldc1, int accumulate1,
+                                  int64_t K) {
+  ALPHA_REQUIRE_INIT();
+  const TnProblem q0{A0, B0, C0, M0, N0, lda0, ldb0, ldc0, accumulate0}, q1{A1, B1, C1, M1, N1, lda1, ldb1, ldc1, accumulate1};
+  const int rc = gemm_tn_pair_launch(q0, q1, K);
+  if (rc >= 0) return rc;
+  // not a pair that gains from sharing a launch: one GEMM each
+  if (gemm_tc_launch(ALPHA_GEMM_TN, A0, B0, C0, M0, N0, K, lda0, ldb0, ldc0, ALPHA_F32, ALPHA_EPI_NONE, 0, 0, accumulate0))
+    return 1;
+  return gemm_tc_launch(ALPHA_GEMM_TN, A1, B1, C1, M1, N1, K, lda1, ldb1, ldc1, ALPHA_F32, ALPHA_EPI_NONE, 0, 0, accumulate1);
+}
+
 
 // dO = G W with the row-dot of attention's backward in the epilogue: besides C = A B (NN,
 // bf16, N = heads * 64) it writes delta[b, h, t] = sum_d C[b*T + t, 64h + d] * O[b*T + t, 64h + d]

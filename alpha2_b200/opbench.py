@@ -149,6 +149,14 @@ def cublas_gemm_ms(b: Bench, layout: str, M: int, N: int, K: int, lda: int, ldb:
     return total / b.iters
 
 
+def dw_pair_case(b: Bench, s0, s1, K):
+    """Two weight gradients A_i^T B_i over one K in one launch (alpha_gemm_tn_pair), as the MLP's backward issues them."""
+    B = b.B
+    ops = [(b.normal((K, M), 0.02), b.normal((K, N), 0.02), B._new((M, N), "f32")) for M, N in (s0, s1)]
+    ms = b.time(lambda: B.matmulTransposedAPair(*ops))
+    return {"ms": ms, "work": 2.0 * K * (s0[0] * s0[1] + s1[0] * s1[1]), "kind": "flop"}
+
+
 def attn_case(b: Bench, Bn=16, H=12, T=1024, D=64, backward=False, dtype="bf16", cap=30.0):
     B = b.B
     E = H * D
@@ -244,6 +252,7 @@ CASES = {
     "gemm_dw_fc1": lambda b: gemm_case(b, "tn", 3072, 768, M, "f32"),
     "gemm_dw_fc2": lambda b: gemm_case(b, "tn", 768, 3072, M, "f32"),
     "gemm_dw_head": lambda b: gemm_case(b, "tn", 50257, 768, M, "f32"),
+    "gemm_dw_fc1_fc2_pair": lambda b: dw_pair_case(b, (3072, 768), (768, 3072), M),
     "attn_fwd": lambda b: attn_case(b),
     "attn_bwd": lambda b: attn_case(b, backward=True),
     "attn_fwd_b8": lambda b: attn_case(b, Bn=8),

@@ -257,6 +257,15 @@ int alpha_gemm(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int
 int alpha_gemm_nn_rowdot(alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N, int64_t K,
                          int64_t lda, int64_t ldb, int64_t ldc, alpha_buf O, int64_t ld_o,
                          alpha_buf delta, int64_t T, int64_t heads);
+/* Two weight gradients in one launch: C_i (+)= A_i^T B_i for i = 0, 1 with A_i [K, M_i] and
+ * B_i [K, N_i] bf16, C_i f32, both over the same K (accumulate_i != 0: added to what C_i holds).
+ * The reference computes every weight gradient with a matmul of its own (packages/autograd/src/
+ * ops.ts:200-234); two that would each fill half of the device share a launch here and need no
+ * split over K.  A pair that does not qualify (shapes, alignment) runs as two alpha_gemm calls. */
+int alpha_gemm_tn_pair(alpha_buf A0, alpha_buf B0, alpha_buf C0, int64_t M0, int64_t N0, int64_t lda0,
+                       int64_t ldb0, int64_t ldc0, int accumulate0, alpha_buf A1, alpha_buf B1,
+                       alpha_buf C1, int64_t M1, int64_t N1, int64_t lda1, int64_t ldb1, int64_t ldc1,
+                       int accumulate1, int64_t K);
 int alpha_gemm_batched_f32(int layout, alpha_buf A, alpha_buf B, alpha_buf C, int64_t M, int64_t N,
                            int64_t K, int64_t lda, int64_t ldb, int64_t ldc, int64_t batch,
                            int64_t stride_a, int64_t stride_b, int64_t stride_c);

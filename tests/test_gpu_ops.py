@@ -499,6 +499,44 @@ def test_gradients_added_inside_the_gemm(B, dtype, shape):
     B.checkAsyncError()
 
 
+PAIRS = [
+    # ((M0, N0), (M1, N1), K): the train step's MLP weight gradients (36 + 36 tiles share the device, unsplit)
+    ((3072, 768), (768, 3072), 16384),
+    ((2304, 768), (768, 768), 8192),          # 27 + 9 tiles
+    ((1000, 520), (312, 264), 4100),          # ragged M, N and K in both (rows stay 16-byte multiples, as TMA needs)
+    ((128, 768), (768, 768), 8192),           # M <= 128 in one of them: runs as two GEMMs inside the library
+    ((4096, 4096), (768, 768), 2048),         # too many tiles to share one wave: two GEMMs as well
+]
+
+
+@pytest.mark.parametrize("shape0,shape1,K", PAIRS)
+@pytest.mark.parametrize("accumulate", [(False, False), (True, False), (True, True)])
+def test_two_weight_gradients_in_one_launch(B, shape0, shape1, K, accumulate):
+    """alpha_gemm_tn_pair: both products against f64, C += where asked, three launches bit for bit."""
+    r = rng(K + shape0[0] + 7 * shape1[1])
+    ops, refs, c0s = [], [], []
+    for (M, N), accu in zip((shape0, shape1), accumulate):
+        a = bf16_round(r.standard_normal((K, M)) * 0.05)
+        b = bf16_round(r.standard_normal((K, N)) * 0.05)
+        c0 = r.standard_normal((M, N)).astype(f32) if accu else None
+        ops.append((B.upload(a, "bf16"), B.upload(b, "bf16")))
+        c0s.append(c0)
+        refs.append(a.astype(np.float64).T @ b.astype(np.float64) + (0 if c0 is None else c0))
+    scale = float(np.sqrt(K)) * 0.05 * 0.05
+    outs = []
+    for rep in range(3):
+        intos = [None if c0 is None else B.upload(c0, "f32") for c0 in c0s]
+        got = B.matmulTransposedAPair((ops[0][0], ops[0][1], intos[0]), (ops[1][0], ops[1][1], intos[1]))
+        outs.append([np.array(t.data) for t in got])
+        for t, into in zip(got, intos):
+            assert into is None or t is into
+    for o, ref in zip(outs[0], refs):
+        assert o.dtype == f32 and float(np.abs(o - ref).max()) < scale * 1e-5 * 16 + 2e-6
+    for o in outs[1:]:
+        assert all(np.array_equal(x, y) for x, y in zip(o, outs[0]))
+    B.checkAsyncError()
+
+
 K_BALANCED = [
     # (layout, M, N, K, out): few output tiles, long K -> K is split
     ("tn", 2304, 768, 16384, "f32"), ("tn", 768, 768, 16384, "f32"), ("tn", 768, 3072, 8192, "f32"),

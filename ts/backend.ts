@@ -501,6 +501,23 @@ export class CudaBackend implements Backend {
     return [out, lse];
   }
 
+  /** Two weight gradients A_i^T B_i over the same K in one launch (each argument as for
+   *  matmulTransposedA: a [K, M], b [K, N] bf16, an existing f32 gradient to add into or
+   *  undefined); two GEMMs that would each fill half of the device need no split over K this way. */
+  matmulTransposedAPair(first: [TensorData, TensorData, TensorData?], second: [TensorData, TensorData, TensorData?]): TensorData[] {
+    const K = sizeOf(first[0].shape) / first[0].shape[first[0].shape.length - 1];
+    const outs: TensorData[] = [];
+    const a: (bigint | number)[] = [];
+    for (const [x, y, into] of [first, second]) {
+      const M = x.shape[x.shape.length - 1], N = y.shape[y.shape.length - 1];
+      const out = into ?? this.make([M, N], "f32");
+      outs.push(out);
+      a.push(this.addr(x), this.addr(y), this.addr(out), BigInt(M), BigInt(N), BigInt(M), BigInt(N), BigInt(N), into ? 1 : 0);
+    }
+    check((C.alpha_gemm_tn_pair as (...args: (bigint | number)[]) => number)(...a, BigInt(K)));
+    outs.forEach((t) => this.invalidate(t));
+    return outs;
+  }
   /** Rotary embedding of `heads` heads of width D in the column block that starts at column
    *  `colOffset` of x [B*T, ld], in place (`inverse`: the transposed rotation, i.e. the backward).
    *  For the fused projection [B*T, 3E]: heads = 2H, ld = 3E, colOffset = 0 rotates q and k. */
