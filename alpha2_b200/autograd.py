@@ -533,12 +533,9 @@ def mlpGelu(ctx, x: Variable, w1: Variable, w2: Variable, residual: Variable) ->
     def bw(g, B, rel, needs, acc):
         dpre = B.matmulGeluBackward(g, w2d, pre)
         dx = B.matmul(dpre, w1d) if needs[0] else None
-        if needs[1] and needs[2] and hasattr(B, "matmulTransposedAPair") and g.dtype == "bf16" and \
-                getattr(B, "param_grads_f32", False) and all(a is None or a.dtype == "f32" for a in (acc[1], acc[2])):
+        if needs[1] and needs[2]:
             # both weight gradients in one launch (each alone would have to split its K)
-            r2, r1 = B.matmulTransposedAPair((g, act, acc[2]), (dpre, xd, acc[1]))
-            dw2 = ACCUMULATED if acc[2] is not None else r2
-            dw1 = ACCUMULATED if acc[1] is not None else r1
+            dw2, dw1 = _pair_dw(B, (g, act, acc[2]), (dpre, xd, acc[1]))
         else:
             dw2 = _dw_gemm(B, g, act, acc[2]) if needs[2] else None
             dw1 = _dw_gemm(B, dpre, xd, acc[1]) if needs[1] else None
@@ -604,6 +601,70 @@ def attentionProj(ctx, qkv: Variable, wo: Variable, residual: Variable, Bn: int,
             rel(dO)
         return [dqkv, dwo, g]
     return _record(ctx, out, [qkv, wo, residual], bw, cleanup, in_place=True)
+
+
+def _pair_dw(B, first, second):
+    """Two weight gradients (g, x, acc) -> g^T @ x, in one launch where the backend offers it
+    (bf16 activations, f32 gradients); otherwise one GEMM each."""
+    (g0, x0, a0), (g1, x1, a1) = first, second
+    if hasattr(B, "matmulTransposedAPair") and g0.dtype == "bf16" and g1.dtype == "bf16" and \
+            getattr(B, "param_grads_f32", False) and all(a is None or a.dtype == "f32" for a in (a0, a1)):
+        r0, r1 = B.matmulTransposedAPair((g0, x0, a0), (g1, x1, a1))
+        return (ACCUMULATED if a0 is not None else r0), (ACCUMULATED if a1 is not None else r1)
+    return _dw_gemm(B, g0, x0, a0), _dw_gemm(B, g1, x1, a1)
+
+
+def attentionBlock(ctx, x: Variable, wqkv: Variable, wo: Variable, residual: Variable, Bn: int, T: int, H: int,
+                   scale_: float, softCap_: float, ropeTheta: float | None = None) -> Variable:
+    """residual + attention(x @ wqkv^T) @ wo^T as one tape entry: the fused projection (with
+    q and k rotated in place when ``ropeTheta`` is given), causal attention read in place from
+    it, the output projection and the residual add in its GEMM's epilogue.  Backward: dO = g @ wo
+    with the row-dots dO.att from that GEMM's epilogue where the backend can, the attention
+    backward, the transposed rotation in place, then both weight gradients — g^T att and
+    dqkv^T x — in one launch (9 + 27 tiles that alone would each leave most of the device idle),
+    and dx = dqkv @ wqkv."""
+    B0 = ctx.backend
+    xd = x.data
+    wqd, wod = _compute_weight(wqkv), _compute_weight(wo)
+    qd = B0.matmulTransposed(xd, wqd)
+    E3 = qd.shape[-1]
+    D = E3 // 3 // H
+    if ropeTheta is not None:
+        B0.rope(qd, Bn, T, 2 * H, D, E3, 0, ropeTheta)            # q and k: 2H heads side by side
+    att, lse = B0.attentionQkv(qd, Bn, T, H, scale_, softCap_)
+    out = B0.matmulTransposedAdd(att, wod, residual.data)
+    state = {"att": att, "lse": lse, "qkv": qd}
+
+    def cleanup(release=None):      # projection, attention output and row statistics live inside this entry
+        for k in ("att", "lse", "qkv"):
+            if state[k] is not None and release:
+                release(state[k])
+            state[k] = None
+
+    def bw(g, B, rel, needs, acc):
+        att, lse, qd = state["att"], state["lse"], state["qkv"]
+        if hasattr(B, "matmulRowdot") and B.rowdotSupported(g, att, H):
+            dO, delta = B.matmulRowdot(g, wod, att, T, H)
+            dqkv = B.attentionQkvBackward(qd, att, dO, lse, Bn, T, H, scale_, softCap_, delta=delta)
+            if rel:
+                rel(delta)
+        else:
+            dO = B.matmul(g, wod)
+            dqkv = B.attentionQkvBackward(qd, att, dO, lse, Bn, T, H, scale_, softCap_)
+        if rel:
+            rel(dO)
+        if ropeTheta is not None:
+            B.rope(dqkv, Bn, T, 2 * H, D, E3, 0, ropeTheta, inverse=True)
+        if needs[1] and needs[2]:
+            dwo, dwq = _pair_dw(B, (g, att, acc[2]), (dqkv, xd, acc[1]))
+        else:
+            dwo = _dw_gemm(B, g, att, acc[2]) if needs[2] else None
+            dwq = _dw_gemm(B, dqkv, xd, acc[1]) if needs[1] else None
+        dx = _dx_gemm(B, dqkv, wqd, acc[0]) if needs[0] else None
+        if rel:
+            rel(dqkv)
+        return [dx, dwq, dwo, g]
+    return _record(ctx, out, [x, wqkv, wo, residual], bw, cleanup, in_place=True)
 
 
 def ropeQk(ctx, qkv: Variable, Bn: int, T: int, H: int, theta: float = 10000.0) -> Variable:

@@ -902,26 +902,35 @@ struct TnProblem {
   int64_t M, N, lda, ldb, ldc;
   int accumulate;
 };
-static int prepare_tn_problem(const TnProblem &q, int64_t K, GemmTcArgs &g, GemmTmaps &m) {
+// `splits` > 1: the problem's K is cut into that many parts whose partial products go to fp32
+// slabs in *ws (allocated here, freed by the caller after the reduce kernel is enqueued).
+static int prepare_tn_problem(const TnProblem &q, int64_t K, int splits, GemmTcArgs &g, GemmTmaps &m, void **ws) {
   memset(&g, 0, sizeof(g));
   memset(&m, 0, sizeof(m));
+  *ws = nullptr;
   const int tile_m = 2 * GBM, BN = 256;
   g.M = (int)q.M; g.N = (int)q.N; g.K = (int)K;
   g.tiles_m = (int)((q.M + tile_m - 1) / tile_m);
   g.tiles_n = (int)((q.N + BN - 1) / BN);
   g.kblocks = (int)((K + GBK - 1) / GBK);
-  g.kb_per_split = g.kblocks;
-  g.splits = 1;
+  g.kb_per_split = (g.kblocks + splits - 1) / splits;
+  g.splits = (g.kblocks + g.kb_per_split - 1) / g.kb_per_split;
   g.m_pad = g.tiles_m * tile_m;
   g.err = tc_error_word();
-  g.C = ptr<void>(q.C); g.ldc = q.ldc; g.out_f32 = 1; g.tma_epi = 1;
-  // C += A^T B is the residual-add epilogue with C as its own addend
-  g.epilogue = q.accumulate ? ALPHA_EPI_ADD : ALPHA_EPI_NONE;
-  g.accumulate = 0;
-  g.aux_in = ptr<void>(q.C); g.aux_out = ptr<void>(q.C); g.ld_aux = q.ldc;
+  g.out_f32 = 1; g.tma_epi = 1; g.accumulate = 0;
   if (get_tmap(&m.a, ptr<void>(q.A), q.M, K, q.lda, 64, 64)) return 1;
   if (get_tmap(&m.b, ptr<void>(q.B), q.N, K, q.ldb, 64, 64)) return 1;
-  if (get_tmap_out(&m.c, ptr<void>(q.C), ALPHA_F32, q.N, q.M, q.ldc)) return 1;
+  if (g.splits > 1) {
+    if (pool_alloc((size_t)g.splits * g.m_pad * q.N * sizeof(float), ws)) return 1;
+    g.C = *ws; g.ldc = q.N; g.epilogue = ALPHA_EPI_NONE;
+    if (get_tmap_out(&m.c, *ws, ALPHA_F32, q.N, (uint64_t)g.splits * g.m_pad, q.N)) return 1;
+  } else {
+    g.C = ptr<void>(q.C); g.ldc = q.ldc;
+    // C += A^T B is the residual-add epilogue with C as its own addend
+    g.epilogue = q.accumulate ? ALPHA_EPI_ADD : ALPHA_EPI_NONE;
+    g.aux_in = ptr<void>(q.C); g.aux_out = ptr<void>(q.C); g.ld_aux = q.ldc;
+    if (get_tmap_out(&m.c, ptr<void>(q.C), ALPHA_F32, q.N, q.M, q.ldc)) return 1;
+  }
   m.aux = m.c;
   return 0;
 }
@@ -936,9 +945,20 @@ static int gemm_tn_pair_launch(const TnProblem &q0, const TnProblem &q1, int64_t
   const int slots = g_sm_count / 2;
   // worth it when each would split K on its own and together they still fit one wave
   if (t0 + t1 > slots || 2 * t0 > slots + t0 / 2 || 2 * t1 > slots + t1 / 2) return -1;
+  // a pair that fills less than half of the device splits K as well (both problems alike),
+  // which still halves the launches and lets the two share every wave
+  const int kblocks = (int)((K + GBK - 1) / GBK);
+  int splits = (int)(slots / (t0 + t1));
+  if (splits > kblocks / 16) splits = kblocks / 16;
+  if (splits < 1 || q0.N % 4 != 0 || q1.N % 4 != 0) splits = 1;
   GemmTcArgs g0, g1;
   GemmTmaps m0, m1;
-  if (prepare_tn_problem(q0, K, g0, m0) || prepare_tn_problem(q1, K, g1, m1)) return 1;
+  void *ws0 = nullptr, *ws1 = nullptr;
+  if (prepare_tn_problem(q0, K, splits, g0, m0, &ws0) || prepare_tn_problem(q1, K, splits, g1, m1, &ws1)) {
+    if (ws0) pool_free(ws0);
+    if (ws1) pool_free(ws1);
+    return 1;
+  }
   ProfScope prof(PROF_GEMM_TC, 2.0 * (double)K * ((double)q0.M * (double)q0.N + (double)q1.M * (double)q1.N));
   using L = GemmSmemLayout<256, true, false>;
   static int max_pairs = 0, epoch = -1;
@@ -962,12 +982,28 @@ static int gemm_tn_pair_launch(const TnProblem &q0, const TnProblem &q1, int64_t
     }
     max_pairs = n < g_sm_count / 2 ? n : g_sm_count / 2;
   }
-  const int total = (int)(t0 + t1);
+  const int total = (int)(t0 * g0.splits + t1 * g1.splits);
   const int n = total < max_pairs ? total : max_pairs;
-  ALPHA_CUDA(launch_overlapped(OVL_GEMM, gemm_tc_pair_group2_kernel<true, true>, dim3(2 * n), dim3(L::THREADS), L::DYN, m0, m1,
-                               g0, g1));
-  ALPHA_LAUNCHED();
-  return 0;
+  cudaError_t e = launch_overlapped(OVL_GEMM, gemm_tc_pair_group2_kernel<true, true>, dim3(2 * n), dim3(L::THREADS), L::DYN, m0,
+                                    m1, g0, g1);
+  int rc = 0;
+  if (e != cudaSuccess) rc = set_error("alpha_gemm_tn_pair: launch -> %s", cudaGetErrorString(e));
+  else g_launches++;
+  const TnProblem *qs[2] = {&q0, &q1};
+  const GemmTcArgs *gs[2] = {&g0, &g1};
+  void *wss[2] = {ws0, ws1};
+  for (int i = 0; i < 2 && rc == 0; i++) {
+    if (gs[i]->splits <= 1) continue;
+    const int rgrid = grid_for(qs[i]->M * qs[i]->N / 4 + 1, 256, 8);
+    e = launch_overlapped(OVL_SPLITK, splitk_reduce_kernel<float>, dim3(rgrid), dim3(256), 0, (const float *)wss[i],
+                          ptr<float>(qs[i]->C), qs[i]->M, qs[i]->N, qs[i]->ldc, gs[i]->splits, qs[i]->accumulate, 1,
+                          (int64_t)gs[i]->m_pad * qs[i]->N);
+    if (e != cudaSuccess) rc = set_error("alpha_gemm_tn_pair: reduce launch -> %s", cudaGetErrorString(e));
+    else g_launches++;
+  }
+  if (ws0) pool_free(ws0);
+  if (ws1) pool_free(ws1);
+  return rc;
 }
 
 }  // namespace alpha

@@ -223,10 +223,8 @@ def _block_fused(ctx: Ctx, cfg: ModelConfig, x: Variable, P: GPTParams, i: int, 
     pre = f"layer.{i}"
     cap = 30.0 if cfg.softCap is None else cfg.softCap
     ln1 = _norm(ctx, cfg, x, P, f"{pre}.ln1")
-    qkv = ag.linear(ctx, ln1, P[f"{pre}.attn.wqkv"])
-    if cfg.rope:
-        qkv = ag.ropeQk(ctx, qkv, Bn, T, H)
-    x = ag.attentionProj(ctx, qkv, P[f"{pre}.attn.wo"], x, Bn, T, H, 1 / math.sqrt(D), cap)
+    x = ag.attentionBlock(ctx, ln1, P[f"{pre}.attn.wqkv"], P[f"{pre}.attn.wo"], x, Bn, T, H, 1 / math.sqrt(D), cap,
+                          ropeTheta=10000.0 if cfg.rope else None)
     ln2 = _norm(ctx, cfg, x, P, f"{pre}.ln2")
     if cfg.ffnActivation == "swiglu":
         gate = ag.linear(ctx, ln2, P[f"{pre}.mlp.fc_gate"])
