@@ -566,43 +566,6 @@ def attentionQkv(ctx, qkv: Variable, Bn: int, T: int, H: int, scale_: float, sof
                    lambda g, B, rel, n: [B.attentionQkvBackward(qd, out, g, lse, Bn, T, H, scale_, softCap_)])
 
 
-def attentionProj(ctx, qkv: Variable, wo: Variable, residual: Variable, Bn: int, T: int, H: int, scale_: float,
-                  softCap_: float) -> Variable:
-    """residual + attention(qkv) @ wo^T as one tape entry: causal attention on the fused
-    projection, the output projection and the residual add (in the GEMM epilogue).  Its backward
-    is dWo = g^T att, then dO = g @ wo — on a backend that can, with the row-dots dO.att that
-    attention's backward needs taken in that GEMM's epilogue instead of in a pass of their own —
-    and the attention backward."""
-    B0 = ctx.backend
-    qd = qkv.data
-    wd = _compute_weight(wo)
-    att, lse = B0.attentionQkv(qd, Bn, T, H, scale_, softCap_)
-    out = B0.matmulTransposedAdd(att, wd, residual.data)
-    state = {"att": att, "lse": lse}
-
-    def cleanup(release=None):      # the attention output and its row statistics live inside this entry
-        for k in ("att", "lse"):
-            if state[k] is not None and release:
-                release(state[k])
-            state[k] = None
-
-    def bw(g, B, rel, needs, acc):
-        att, lse = state["att"], state["lse"]
-        dwo = _dw_gemm(B, g, att, acc[1]) if needs[1] else None
-        if hasattr(B, "matmulRowdot") and B.rowdotSupported(g, att, H):
-            dO, delta = B.matmulRowdot(g, wd, att, T, H)
-            dqkv = B.attentionQkvBackward(qd, att, dO, lse, Bn, T, H, scale_, softCap_, delta=delta)
-            if rel:
-                rel(delta)
-        else:
-            dO = B.matmul(g, wd)
-            dqkv = B.attentionQkvBackward(qd, att, dO, lse, Bn, T, H, scale_, softCap_)
-        if rel:
-            rel(dO)
-        return [dqkv, dwo, g]
-    return _record(ctx, out, [qkv, wo, residual], bw, cleanup, in_place=True)
-
-
 def _pair_dw(B, first, second):
     """Two weight gradients (g, x, acc) -> g^T @ x, in one launch where the backend offers it
     (bf16 activations, f32 gradients); otherwise one GEMM each."""
