@@ -568,10 +568,9 @@ def attentionQkv(ctx, qkv: Variable, Bn: int, T: int, H: int, scale_: float, sof
 
 def _pair_dw(B, first, second):
     """Two weight gradients (g, x, acc) -> g^T @ x, in one launch where the backend offers it
-    (bf16 activations, f32 gradients); otherwise one GEMM each."""
+    for these operands (``pairSupported``); otherwise one GEMM each."""
     (g0, x0, a0), (g1, x1, a1) = first, second
-    if hasattr(B, "matmulTransposedAPair") and g0.dtype == "bf16" and g1.dtype == "bf16" and \
-            getattr(B, "param_grads_f32", False) and all(a is None or a.dtype == "f32" for a in (a0, a1)):
+    if hasattr(B, "matmulTransposedAPair") and B.pairSupported(first, second):
         r0, r1 = B.matmulTransposedAPair((g0, x0, a0), (g1, x1, a1))
         return (ACCUMULATED if a0 is not None else r0), (ACCUMULATED if a1 is not None else r1)
     return _dw_gemm(B, g0, x0, a0), _dw_gemm(B, g1, x1, a1)

@@ -516,6 +516,12 @@ class CudaBackend:
             return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype, out=into, accumulate=True)
         return self._gemm(L.GEMM_TN, a, b, M, N, K, M, N, out_dtype=out_dtype)
 
+    def pairSupported(self, first, second) -> bool:
+        """Whether matmulTransposedAPair takes these two (a, b, into) triples: bf16 operands whose
+        weight gradients are kept in f32."""
+        return self.param_grads_f32 and all(a.dtype == "bf16" and b.dtype == "bf16" and (into is None or into.dtype == "f32")
+                                            for a, b, into in (first, second))
+
     def matmulTransposedAPair(self, first, second) -> list:
         """Two weight gradients A_i^T @ B_i over the same K in one launch: each argument is
         (a [K, M], b [K, N], into or None) as for ``matmulTransposedA``; returns the two results.

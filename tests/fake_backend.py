@@ -119,6 +119,15 @@ class NumpyBackend:
             return into
         return self._o(A.T @ Bm)
 
+    def pairSupported(self, first, second):
+        return True
+
+    def matmulTransposedAPair(self, first, second):
+        """Both weight gradients "in one launch": the host logic around it (ACCUMULATED, hand-off)
+        is what the CPU tests exercise."""
+        self.pair_calls = getattr(self, "pair_calls", 0) + 1
+        return [self.matmulTransposedA(a, b, into) for a, b, into in (first, second)]
+
     def matmulInto(self, a, b, into):
         self.ops += 1
         into._host = (into.data.astype(f64) + (a.data.astype(f64) @ b.data.astype(f64)).reshape(into.shape)).astype(f32)

@@ -164,3 +164,32 @@ def test_fused_step_with_non_finite_gradients_changes_nothing():
     for n, t in tr.opt._m.items():
         assert np.array_equal(t.data, m_before[n]), n
     assert (tr.opt._step, tr.opt._beta1Pow, tr.opt._beta2Pow) == state
+
+
+def test_paired_weight_gradients_equal_the_single_ones():
+    """The MLP's and the attention block's weight gradients go to the backend two at a time
+    (``matmulTransposedAPair``) where it offers that; losses and parameters must not depend on
+    it, with accumulated micro-steps (the gradient then exists and is added to) and without."""
+    from alpha2_b200.data import uniform_batches
+    from alpha2_b200.gpt import ModelConfig
+    from alpha2_b200.trainer import TrainConfig, Trainer
+    from tests.fake_backend import NumpyBackend, T
+
+    class NoPair(NumpyBackend):                           # a backend without the hook
+        def __getattribute__(self, name):
+            if name == "matmulTransposedAPair":
+                raise AttributeError(name)
+            return super().__getattribute__(name)
+
+    mc = ModelConfig(vocabSize=64, blockSize=16, nLayer=2, nEmbd=32, nHead=2, tied=True, init="plain")
+    batches = uniform_batches(9, 4, 2, 16, 64)
+    runs = []
+    for cls in (NumpyBackend, NoPair):
+        B = cls()
+        tr = Trainer(B, mc, TrainConfig(iters=10, batchSize=2, gradClip=0.5, seed=3))
+        losses = [tr.train_step([(T(t, "i32"), T(g, "i32")) for t, g in batches[i:i + 2]])["loss"] for i in (0, 2)]
+        runs.append((losses, {n: np.array(v.data.data) for n, v in tr.entries}, getattr(B, "pair_calls", 0)))
+    assert runs[0][2] == 2 * 2 * 2 * 2 and runs[1][2] == 0      # 2 steps x 2 micro-steps x 2 layers x (MLP, attention)
+    assert runs[0][0] == runs[1][0]
+    for n in runs[0][1]:
+        assert np.array_equal(runs[0][1][n], runs[1][1][n]), n
